@@ -1,0 +1,142 @@
+/**
+ * @file params.hpp
+ * Plain-data structures shared between the host runtime and the device
+ * kernels: the per-communicator workspace description, the arguments of one
+ * collective launch and the status record a kernel fills when a wait runs out.
+ *
+ * Device protocol in one paragraph.  Every rank owns, in peer-mapped
+ * ("symmetric") memory, a staging area of two halves and a flag area.  A
+ * collective with sequence number k proceeds in chunks; in chunk c every rank
+ * (1) copies ("publishes") its contribution into staging half (k+c)&1 with
+ * all of its CTAs; the CTA that finishes last (2) stores the epoch
+ * (k<<24 | c+1) into slot A[me] of every rank's flag area with release
+ * semantics at system scope; every CTA then (3) waits, with a time budget,
+ * until slots A[r] of its own flag area reached that epoch for every r, and
+ * (4) pulls or reduces what it needs from the peers' staging halves with
+ * ordinary 16-byte loads over NVLink.  Two-phase algorithms repeat the
+ * handshake on the B flags.  Every chunk makes every rank wait for every
+ * rank, so two halves suffice; a multi-chunk launch ends with a C-flag
+ * barrier so that the next launch may start on either half.  Epochs only
+ * grow, so flags are never reset.
+ */
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include "al/config.hpp"
+
+namespace Al {
+namespace internal {
+namespace device {
+
+constexpr int kMaxRanks = AL_MAX_DEVICE_RANKS;
+constexpr int kMaxCtas = AL_MAX_CTAS;
+
+/**
+ * Layout of one rank's flag area in units of uint64_t.  Every remotely
+ * written word sits in its own 32-byte sector (stride 4 words).
+ */
+struct FlagLayout {
+  static constexpr size_t stride = 4;
+  static constexpr size_t off_A = 0;                                       // [kMaxRanks]
+  static constexpr size_t off_B = off_A + kMaxRanks * stride;              // [kMaxRanks]
+  static constexpr size_t off_C = off_B + kMaxRanks * stride;              // [kMaxRanks]
+  static constexpr size_t off_meta = off_C + kMaxRanks * stride;           // [2][kMaxRanks]
+  static constexpr size_t off_p2p_sent = off_meta + 2 * kMaxRanks * stride;   // [kMaxRanks], written by the sender
+  static constexpr size_t off_p2p_acked = off_p2p_sent + kMaxRanks * stride;  // [kMaxRanks], written by the receiver
+  static constexpr size_t off_rma = off_p2p_acked + kMaxRanks * stride;       // [kMaxRanks] notify counters
+  static constexpr size_t off_halo = off_rma + kMaxRanks * stride;         // [4] ready-from-lo, ready-from-hi, data-from-lo, data-from-hi
+  // Words below are only touched by the owning GPU.
+  static constexpr size_t off_arrive = off_halo + 4 * stride;              // [4] CTA arrival counters (A, B, C, spare)
+  static constexpr size_t off_status = off_arrive + 4 * stride;            // device-local copy of the status code
+  static constexpr size_t off_p2p_arrive = off_status + stride;            // [16] per-item CTA arrival counters
+  static constexpr size_t words = off_p2p_arrive + 16 * stride;
+  static constexpr size_t bytes = (words * 8 + 4095) / 4096 * 4096;
+};
+
+/** Why a kernel gave up. */
+enum StatusCode : uint32_t {
+  kStatusOk = 0,
+  kStatusTimeout = 1,      ///< a flag wait exceeded its time budget
+  kStatusPoisoned = 2      ///< an earlier kernel of this communicator had failed; this one did nothing
+};
+
+/** Written by a kernel into pinned host memory; read by the host in Wait/Test and before each launch. */
+struct DeviceStatus {
+  uint32_t code;    ///< StatusCode
+  uint32_t rank;    ///< rank that gave up
+  uint32_t peer;    ///< rank it was waiting for
+  uint32_t where;   ///< 0: A flags, 1: B flags, 2: C flags, 3: p2p credit, 4: p2p data, 5: rma
+  uint64_t epoch;   ///< epoch it was waiting for
+  uint64_t seen;    ///< value it last saw
+};
+
+/** Workspace of one communicator as seen from the launching process. */
+struct Workspace {
+  char* stage[kMaxRanks];        ///< staging base (two halves, contiguous) of every rank
+  uint64_t* flags[kMaxRanks];    ///< flag area of every rank
+  char* mbox[kMaxRanks];         ///< p2p mailbox area of every rank: [src][2 slots]
+  char* mc_stage;                ///< NVLink-multicast alias of the staging area, or nullptr
+  DeviceStatus* status;          ///< pinned host record (device-visible address)
+  size_t half_bytes;             ///< size of one staging half
+  size_t mbox_slot_bytes;        ///< size of one mailbox slot
+  int p;                         ///< communicator size
+};
+
+/** Operation selector of the collective kernels. */
+enum class DevColl : int {
+  allreduce = 0, reduce, reduce_scatter, allgather, alltoall, bcast, gather, scatter, barrier
+};
+
+/** Per-rank element counts and displacements (vector collectives; uniform ones are synthesised). */
+struct CountTable {
+  size_t send_counts[kMaxRanks];
+  size_t send_displs[kMaxRanks];
+  size_t recv_counts[kMaxRanks];
+  size_t recv_displs[kMaxRanks];
+};
+
+/**
+ * Arguments of one launch.  A launch normally executes one rank (grid.y == 1).
+ * When several ranks of a communicator live in one process on one device
+ * (single-GPU emulation used by tests), one cooperative launch executes all
+ * of them: grid.y == number of local ranks and block (x, y) works for rank
+ * rank0 + y.
+ */
+struct CollParams {
+  Workspace ws;
+  const void* send[kMaxRanks];   ///< indexed by rank; nullptr = contributes nothing
+  void* recv[kMaxRanks];         ///< indexed by rank; nullptr = receives nothing
+  CountTable tab[kMaxRanks];     ///< indexed by rank (only local ranks are filled)
+  uint64_t local_chunks[kMaxRanks];
+  uint64_t seq;
+  uint64_t timeout_ns;
+  size_t count;                  ///< uniform count (allreduce / reduce / bcast)
+  double scale;                  ///< multiplies the result of a reduction (1/p for avg); 1 = none
+  int int_div;                   ///< integer types: divide the result by this (avg); 1 = none
+  int kind;                      ///< DevColl
+  int op;                        ///< ReductionOperator
+  int root;
+  int rank0;
+  int two_phase;                 ///< allreduce: 1 = reduce-scatter + allgather, 0 = every rank reduces everything
+};
+
+/** Arguments of one point-to-point launch (any mix of sends and receives). */
+struct P2PParams {
+  static constexpr int kMaxItems = 16;
+  Workspace ws;
+  const void* sbuf[kMaxItems];
+  void* rbuf[kMaxItems];
+  size_t bytes[kMaxItems];
+  int peer[kMaxItems];
+  int is_send[kMaxItems];
+  int owner[kMaxItems];          ///< rank executing this item (emulation: several ranks per launch)
+  uint64_t base[kMaxItems];      ///< pieces already moved between this pair in this direction (host-tracked)
+  int ctas_per_item;
+  int nitems;
+  uint64_t timeout_ns;
+};
+
+}  // namespace device
+}  // namespace internal
+}  // namespace Al

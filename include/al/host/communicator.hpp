@@ -1,0 +1,108 @@
+/**
+ * @file communicator.hpp
+ * Communicator and type-erased operations of the host (CPU) backend.
+ *
+ * Role: what the reference's MPI backend provides - collectives and
+ * point-to-point on host memory, blocking and non-blocking through the
+ * progress engine (include/aluminum/mpi_impl.hpp, include/aluminum/mpi/*.hpp,
+ * communicator at include/aluminum/mpi/communicator.hpp:49-97).  There is no
+ * MPI underneath: ranks of one host share a POSIX shared-memory workspace per
+ * communicator and run the same flag protocol the device kernels use
+ * (publish into own staging half -> post epoch flag to every peer -> wait for
+ * every peer's flag -> pull / reduce), so the CPU ranks double as a model of
+ * the device protocol that can be tested without a GPU.
+ */
+#pragma once
+#include <atomic>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "al/base.hpp"
+#include "al/bootstrap.hpp"
+
+namespace Al {
+namespace internal {
+namespace host {
+
+/** Completion record shared by an operation and the request handed to the user. */
+struct ReqState {
+  std::atomic<int> status{0};  ///< 0 pending, 1 done, 2 failed
+  std::string error;           ///< valid once status == 2
+};
+using Request = std::shared_ptr<ReqState>;
+
+class Workspace;  // shared-memory segment + layout
+
+enum class Coll {
+  allreduce, reduce, reduce_scatter, allgather, alltoall, bcast, gather, scatter, barrier
+};
+
+/** One collective call with in-place conventions already resolved. */
+struct CollArgs {
+  Coll kind = Coll::barrier;
+  const void* send = nullptr;   ///< nullptr: this rank contributes nothing
+  void* recv = nullptr;         ///< nullptr: this rank receives nothing
+  DType dt = DType::u8;
+  ReductionOperator op = ReductionOperator::sum;
+  int root = 0;
+  size_t count = 0;             ///< uniform count (meaning depends on the op)
+  bool vector = false;          ///< use the count/displacement vectors below
+  std::vector<size_t> send_counts, send_displs, recv_counts, recv_displs;
+};
+
+/** One transfer of a point-to-point operation. */
+struct P2PItem {
+  bool is_send = false;
+  int peer = -1;
+  const void* sbuf = nullptr;
+  void* rbuf = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace host
+}  // namespace internal
+
+/**
+ * Host communicator.  Move-only, like every communicator of the reference;
+ * `copy()` makes a new communicator over the same ranks.  The "stream" of a
+ * host communicator is a dummy int, kept for interface parity
+ * (include/aluminum/mpi/communicator.hpp:49-60).
+ */
+class HostCommunicator {
+ public:
+  /** World communicator (collective over all ranks). */
+  HostCommunicator();
+  /** Communicator over a subset (collective over the members). */
+  explicit HostCommunicator(const internal::Group& group);
+  ~HostCommunicator();
+  HostCommunicator(HostCommunicator&&) noexcept;
+  HostCommunicator& operator=(HostCommunicator&&) noexcept;
+  HostCommunicator(const HostCommunicator&) = delete;
+  HostCommunicator& operator=(const HostCommunicator&) = delete;
+
+  HostCommunicator copy(int /*stream*/ = 0) const { return HostCommunicator(group_); }
+  /** MPI_Comm_split analogue. */
+  HostCommunicator split(int color, int key) const { return HostCommunicator(group_.split(color, key)); }
+
+  int rank() const { return group_.rank(); }
+  int size() const { return group_.size(); }
+  int local_rank() const { return group_.rank(); }
+  int local_size() const { return group_.size(); }
+  int get_stream() const { return 0; }
+  const internal::Group& group() const { return group_; }
+
+  /** Start a collective; returns when done if `req` is null, else hands back a request. */
+  void collective(internal::host::CollArgs&& args, internal::host::Request* req);
+  /** Start a set of sends/receives that progress together. */
+  void p2p(std::vector<internal::host::P2PItem>&& items, internal::host::Request* req, const char* name);
+
+  struct Impl;
+  Impl* impl() const { return impl_.get(); }
+
+ private:
+  internal::Group group_;
+  std::unique_ptr<Impl> impl_;
+};
+
+}  // namespace Al

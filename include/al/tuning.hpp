@@ -1,0 +1,59 @@
+/**
+ * @file tuning.hpp
+ * Run-time tuning table: progress-engine limits, pool sizes, staging sizes,
+ * algorithm cross-over points and CTA budgets of the device kernels.
+ *
+ * The reference fixes these at configure time (CMakeLists.txt:166-215 ->
+ * cmake/tuning_params.hpp.in:36-89).  Here every value has an environment
+ * variable of the same spirit (AL_<NAME>) read once at Initialize(), and can
+ * be changed programmatically through Al::tuning() before communicators are
+ * created.
+ */
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "al/config.hpp"
+
+namespace Al {
+
+struct Tuning {
+  // ---- progress engine ------------------------------------------------------
+  int pe_num_concurrent_ops = AL_PE_NUM_CONCURRENT_OPS_DEFAULT;  ///< AL_PE_NUM_CONCURRENT_OPS
+  bool pe_start_on_demand = true;                                ///< AL_PE_START_ON_DEMAND
+  bool pe_bind_thread = true;                                    ///< AL_PE_BIND (pin the PE thread to a core)
+  double pe_hang_seconds = 10.0;                                 ///< AL_PE_HANG_SECONDS (watchdog threshold, <=0 off)
+  // ---- pools ----------------------------------------------------------------
+  int sync_mem_prealloc = AL_SYNC_MEM_PREALLOC_DEFAULT;          ///< AL_SYNC_MEM_PREALLOC
+  int stream_pool_size = AL_CUDA_STREAM_POOL_SIZE_DEFAULT;       ///< AL_CUDA_STREAM_POOL_SIZE
+  bool disable_background_streams = false;                       ///< AL_DISABLE_BACKGROUND_STREAMS
+  // ---- host (shared-memory) backend -----------------------------------------
+  size_t host_stage_bytes = size_t{4} << 20;   ///< AL_HOST_STAGE_BYTES: one staging half per rank
+  size_t host_mailbox_bytes = size_t{128} << 10;  ///< AL_HOST_MAILBOX_BYTES: one p2p slot per ordered pair
+  double host_wait_timeout_s = 120.0;          ///< AL_HOST_WAIT_TIMEOUT_S: a peer that never arrives raises
+  // ---- device backend ---------------------------------------------------------
+  size_t dev_stage_bytes = size_t{64} << 20;   ///< AL_DEV_STAGE_BYTES: one staging half per rank per communicator
+  size_t dev_mailbox_bytes = size_t{4} << 20;  ///< AL_DEV_MAILBOX_BYTES: p2p slot per ordered pair (2 slots each)
+  double dev_wait_timeout_ms = 20000.0;        ///< AL_DEV_WAIT_TIMEOUT_MS: bound of every device-side flag wait
+  bool dev_enable_nvls = true;                 ///< AL_DEV_NVLS: bind staging to an NVLink multicast object when supported
+  size_t ar_oneshot_max_bytes = size_t{256} << 10;   ///< AL_AR_ONESHOT_MAX: one-shot allreduce up to this size
+  size_t ar_nvls_min_bytes = size_t{512} << 10;      ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on
+  int max_ctas = 64;                           ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
+  int max_ctas_nvls = 32;                      ///< AL_MAX_CTAS_NVLS
+  int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
+  // ---- diagnostics ------------------------------------------------------------
+  bool trace = false;                          ///< AL_TRACE: record every API call
+  bool debug_checks = false;                   ///< AL_DEBUG: argument checks on every call
+  bool signal_handler = true;                  ///< !AL_DISABLE_SIGNAL_HANDLER
+
+  /** Re-read every AL_* environment variable. */
+  void load_from_env();
+  /** One "name = value" line per entry, for al_info. */
+  std::string describe() const;
+};
+
+/** The process-wide table. */
+Tuning& tuning();
+
+}  // namespace Al

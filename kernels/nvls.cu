@@ -1,0 +1,182 @@
+// NVLS (NVLink SHARP) allreduce: the NVSwitch reduces and replicates.
+//
+// Each rank owns 1/p of the vector.  For its slice it issues
+// multimem.ld_reduce on the multicast address - the switch fetches the 16
+// bytes from every GPU bound to the multicast object, reduces them and
+// returns one result - applies the scale, and writes the result back with
+// multimem.st, which the switch replicates into every GPU's memory.  Per GPU
+// the links carry about S(1+1/p) bytes instead of the 2S(p-1)/p of a
+// peer-to-peer two-shot.
+//
+// Two flavours share the kernel:
+//   staged     - user buffers are private: copy into the multicast-bound
+//                staging half, reduce in place there, copy out;
+//   zero-copy  - user buffers come from the library's symmetric allocator and
+//                have their own multicast alias: no copies at all.
+// No TMA is involved anywhere; remote data moves only through multimem
+// instructions.
+#include "al/cuda/cuda.hpp"
+#include "al/device/kernels.hpp"
+#include "datamove.cuh"
+
+namespace Al {
+namespace internal {
+namespace device {
+
+namespace {
+
+enum class NvOp { add, min, max };
+
+template <typename T, NvOp OP> struct MM;
+
+template <> struct MM<float, NvOp::add> {
+  static __device__ __forceinline__ uint4 ld(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+  }
+};
+#define AL_MM_16(T, TOK, OP, OPTOK)                                                                       \
+  template <> struct MM<T, NvOp::OP> {                                                                    \
+    static __device__ __forceinline__ uint4 ld(const void* mc) {                                          \
+      uint4 v;                                                                                            \
+      asm volatile("multimem.ld_reduce.relaxed.sys.global." OPTOK ".v4." TOK " {%0,%1,%2,%3}, [%4];"      \
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");                    \
+      return v;                                                                                           \
+    }                                                                                                     \
+  };
+AL_MM_16(__nv_bfloat16, "bf16x2", add, "add.acc::f32")
+AL_MM_16(__nv_bfloat16, "bf16x2", min, "min")
+AL_MM_16(__nv_bfloat16, "bf16x2", max, "max")
+AL_MM_16(__half, "f16x2", add, "add.acc::f32")
+AL_MM_16(__half, "f16x2", min, "min")
+AL_MM_16(__half, "f16x2", max, "max")
+#undef AL_MM_16
+
+__device__ __forceinline__ void mm_st(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 scale_pack(uint4 v, float s) {
+  union { uint4 u; T e[16 / sizeof(T)]; } x;
+  x.u = v;
+#pragma unroll
+  for (int k = 0; k < (int)(16 / sizeof(T)); ++k) x.e[k] = Elem<T>::down(Elem<T>::up(x.e[k]) * s);
+  return x.u;
+}
+
+/** Reduce-and-replicate the 16-byte vectors [v_lo, v_hi) of the multicast range. */
+template <typename T, NvOp OP>
+__device__ __forceinline__ void reduce_vectors(const char* mc_in, char* mc_out, size_t v_lo, size_t v_hi,
+                                               float scale) {
+  const size_t stride = (size_t)blockDim.x * gridDim.x;
+  size_t v = v_lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; v + stride < v_hi; v += 2 * stride) {
+    uint4 a = MM<T, OP>::ld(mc_in + (v << 4));
+    uint4 b = MM<T, OP>::ld(mc_in + ((v + stride) << 4));
+    if (scale != 1.f) { a = scale_pack<T>(a, scale); b = scale_pack<T>(b, scale); }
+    mm_st(mc_out + (v << 4), a);
+    mm_st(mc_out + ((v + stride) << 4), b);
+  }
+  if (v < v_hi) {
+    uint4 a = MM<T, OP>::ld(mc_in + (v << 4));
+    if (scale != 1.f) a = scale_pack<T>(a, scale);
+    mm_st(mc_out + (v << 4), a);
+  }
+}
+
+template <typename T, NvOp OP>
+__global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_constant__ NvlsParams P) {
+  const Workspace& ws = P.ws;
+  const int p = ws.p, rank = P.rank;
+  if (poisoned(ws, rank)) return;
+  const float scale = (float)P.scale;
+
+  if (P.mc_in != nullptr) {
+    // ---- zero-copy: operate on the user's symmetric buffers --------------------
+    const uint64_t e = make_epoch(P.seq, 1);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, e, true, (int)(P.seq & 1), 1);
+    if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
+    const size_t nvec = (P.count * sizeof(T) + 15) >> 4;  // symmetric allocations are padded to 16 bytes
+    size_t s_lo, s_hi;
+    split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
+    reduce_vectors<T, OP>(P.mc_in, P.mc_out, s_lo, s_hi, scale);
+    __threadfence_system();
+    arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
+    (void)wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns);
+    return;
+  }
+
+  // ---- staged ------------------------------------------------------------------
+  const size_t half = ws.half_bytes;
+  const size_t full_e = half / sizeof(T);
+  const T* send = (const T*)P.send;
+  T* recv = (T*)P.recv;
+  const uint64_t G = P.chunks;
+  for (uint64_t c = 0; c < G; ++c) {
+    const int par = (int)((P.seq + c) & 1);
+    char* mystage = ws.stage[rank] + (size_t)par * half;
+    char* mc = ws.mc_stage + (size_t)par * half;
+    const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
+    size_t lo, hi;
+    split_range(len, blockIdx.x, gridDim.x, 16 / sizeof(T), lo, hi);
+    if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
+
+    const uint64_t e = make_epoch(P.seq, c + 1);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, e, c == 0, (int)(P.seq & 1), G);
+    if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
+
+    const size_t nvec = (len * sizeof(T) + 15) >> 4;  // the tail vector may include stale bytes: harmless
+    size_t s_lo, s_hi;
+    split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
+    reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale);
+    __threadfence_system();
+    arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
+    if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
+
+    if (hi > lo) cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(T), (hi - lo) * sizeof(T), true);
+  }
+  if (G > 1) {
+    const uint64_t e = make_epoch(P.seq, 1);
+    arrive_and_post(ws, rank, FlagLayout::off_C, 2, e, false, 0, 0);
+    (void)wait_all(ws, rank, FlagLayout::off_C, 2, e, P.timeout_ns);
+  }
+}
+
+template <typename T, NvOp OP>
+void launch(const NvlsParams& P, int ctas, int threads, cudaStream_t s) {
+  nvls_allreduce_kernel<T, OP><<<ctas, threads, 0, s>>>(P);
+  AL_CHECK_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+bool nvls_allreduce_supported(DType dt, ReductionOperator op) {
+  const bool add = op == ReductionOperator::sum || op == ReductionOperator::avg;
+  if (dt == DType::f32) return add;
+  if (dt == DType::bf16 || dt == DType::f16)
+    return add || op == ReductionOperator::min || op == ReductionOperator::max;
+  return false;
+}
+
+void launch_nvls_allreduce(const NvlsParams& P, DType dt, ReductionOperator op, int ctas, int threads,
+                           cudaStream_t s) {
+  if (!nvls_allreduce_supported(dt, op)) throw_al_exception("NVLS allreduce does not support this type/operator");
+  const bool add = op == ReductionOperator::sum || op == ReductionOperator::avg;
+  if (dt == DType::f32) return launch<float, NvOp::add>(P, ctas, threads, s);
+  if (dt == DType::bf16) {
+    if (add) return launch<__nv_bfloat16, NvOp::add>(P, ctas, threads, s);
+    if (op == ReductionOperator::min) return launch<__nv_bfloat16, NvOp::min>(P, ctas, threads, s);
+    return launch<__nv_bfloat16, NvOp::max>(P, ctas, threads, s);
+  }
+  if (add) return launch<__half, NvOp::add>(P, ctas, threads, s);
+  if (op == ReductionOperator::min) return launch<__half, NvOp::min>(P, ctas, threads, s);
+  return launch<__half, NvOp::max>(P, ctas, threads, s);
+}
+
+}  // namespace device
+}  // namespace internal
+}  // namespace Al

@@ -1,0 +1,454 @@
+// Device communicator: workspace set-up, algorithm / grid selection, launch
+// ordering and failure reporting (see al/device/communicator.hpp).
+#include "al/device/communicator.hpp"
+
+#include <algorithm>
+#include <mutex>
+
+#include "al/device/kernels.hpp"
+#include "al/runtime.hpp"
+#include "al/trace.hpp"
+#include "al/tuning.hpp"
+#include "al/util/meta.hpp"
+
+namespace Al {
+
+using namespace internal;
+using namespace internal::device;
+
+struct DeviceCommunicator::Impl {
+  int p = 1, rank0 = 0, nlocal = 1;
+  bool emulated = false;
+  int device = 0, sm_count = 148;
+  std::unique_ptr<SymmBlock> block;
+  Workspace ws{};
+  DeviceStatus* status_host = nullptr;
+  uint64_t seq = 0;
+  uint64_t halo_epoch = 0;
+  uint64_t timeout_ns = 0;
+  cudaStream_t last_stream = nullptr;
+  bool have_last = false;
+  cudaEvent_t chain_event = nullptr;
+  std::vector<uint64_t> p2p_sent, p2p_recvd;  // [nlocal][p]
+  std::vector<std::unique_ptr<SymmBlock>> user_blocks;
+  CommStats stats;
+  std::mutex mu;
+
+  size_t off_stage() const { return FlagLayout::bytes; }
+  size_t off_mbox() const { return FlagLayout::bytes + 2 * ws.half_bytes; }
+
+  void setup(std::unique_ptr<SymmBlock> b, int p_, int rank0_, int nlocal_) {
+    p = p_; rank0 = rank0_; nlocal = nlocal_;
+    block = std::move(b);
+    AL_CHECK_CUDA(cudaGetDevice(&device));
+    AL_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    ws.p = p;
+    for (int r = 0; r < p; ++r) {
+      char* base = (char*)block->peer(r);
+      ws.flags[r] = (uint64_t*)base;
+      ws.stage[r] = base + off_stage();
+      ws.mbox[r] = base + off_mbox();
+    }
+    ws.mc_stage = block->mc() ? (char*)block->mc() + off_stage() : nullptr;
+    void* hp = nullptr;
+    AL_CHECK_CUDA(cudaHostAlloc(&hp, sizeof(DeviceStatus), cudaHostAllocMapped | cudaHostAllocPortable));
+    memset(hp, 0, sizeof(DeviceStatus));
+    status_host = (DeviceStatus*)hp;
+    void* dp = nullptr;
+    AL_CHECK_CUDA(cudaHostGetDevicePointer(&dp, hp, 0));
+    ws.status = (DeviceStatus*)dp;
+    timeout_ns = (uint64_t)(tuning().dev_wait_timeout_ms * 1e6);
+    AL_CHECK_CUDA(cudaEventCreateWithFlags(&chain_event, cudaEventDisableTiming));
+    p2p_sent.assign((size_t)nlocal * (size_t)p, 0);
+    p2p_recvd.assign((size_t)nlocal * (size_t)p, 0);
+  }
+
+  ~Impl() {
+    if (chain_event) AL_WARN_CUDA(cudaEventDestroy(chain_event));
+    if (status_host) AL_WARN_CUDA(cudaFreeHost(status_host));
+  }
+
+  static size_t block_bytes(int p, size_t half, size_t slot) {
+    return FlagLayout::bytes + 2 * half + (size_t)p * 2 * slot;
+  }
+
+  /** Make `stream` wait for the communicator's previous operation if that ran on another stream. */
+  void order_after_previous(cudaStream_t stream) {
+    if (have_last && last_stream != stream) {
+      AL_CHECK_CUDA(cudaEventRecord(chain_event, last_stream));
+      AL_CHECK_CUDA(cudaStreamWaitEvent(stream, chain_event, 0));
+    }
+    last_stream = stream;
+    have_last = true;
+  }
+};
+
+namespace {
+
+size_t half_bytes_cfg() { return tuning().dev_stage_bytes / 4096 * 4096; }
+size_t slot_bytes_cfg() { return std::max<size_t>(4096, tuning().dev_mailbox_bytes / 4096 * 4096); }
+
+void require_device() {
+  if (!cuda::device_usable()) throw_al_exception("the device backend needs a CUDA device, none is usable in this process");
+}
+
+size_t max_of(const std::vector<size_t>& v) { return v.empty() ? 0 : *std::max_element(v.begin(), v.end()); }
+
+}  // namespace
+
+DeviceCommunicator::DeviceCommunicator() : DeviceCommunicator((cudaStream_t) nullptr) {}
+
+DeviceCommunicator::DeviceCommunicator(cudaStream_t stream)
+    : DeviceCommunicator(Group::world_group(get_world()), stream) {}
+
+DeviceCommunicator::DeviceCommunicator(const Group& group, cudaStream_t stream)
+    : group_(group), stream_(stream), impl_(std::make_shared<Impl>()) {
+  require_device();
+  const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
+  auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot), true);
+  impl_->ws.half_bytes = half;
+  impl_->ws.mbox_slot_bytes = slot;
+  impl_->setup(std::move(block), group.size(), group.rank(), 1);
+}
+
+DeviceCommunicator::DeviceCommunicator(std::shared_ptr<Impl> impl, const Group& g, cudaStream_t s)
+    : group_(g), stream_(s), impl_(std::move(impl)) {}
+
+DeviceCommunicator DeviceCommunicator::emulated(int p, cudaStream_t stream) {
+  require_device();
+  auto impl = std::make_shared<Impl>();
+  const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
+  auto block = SymmBlock::create_emulated(p, Impl::block_bytes(p, half, slot));
+  impl->ws.half_bytes = half;
+  impl->ws.mbox_slot_bytes = slot;
+  impl->emulated = true;
+  impl->setup(std::move(block), p, 0, p);
+  return DeviceCommunicator(std::move(impl), Group(), stream);
+}
+
+DeviceCommunicator::~DeviceCommunicator() = default;
+DeviceCommunicator::DeviceCommunicator(DeviceCommunicator&&) noexcept = default;
+DeviceCommunicator& DeviceCommunicator::operator=(DeviceCommunicator&&) noexcept = default;
+
+DeviceCommunicator DeviceCommunicator::copy(cudaStream_t stream) const {
+  if (impl_->emulated) return emulated(impl_->p, stream);
+  return DeviceCommunicator(group_, stream);
+}
+
+DeviceCommunicator DeviceCommunicator::split(int color, int key, cudaStream_t stream) const {
+  if (impl_->emulated) throw_al_exception("split is not available on an emulated communicator");
+  return DeviceCommunicator(group_.split(color, key), stream);
+}
+
+int DeviceCommunicator::rank() const { return impl_->emulated ? 0 : impl_->rank0; }
+int DeviceCommunicator::size() const { return impl_->p; }
+bool DeviceCommunicator::is_emulated() const { return impl_->emulated; }
+bool DeviceCommunicator::has_multicast() const { return impl_->ws.mc_stage != nullptr; }
+const char* DeviceCommunicator::memory_backing() const { return impl_->block->backing(); }
+const Workspace& DeviceCommunicator::workspace() const { return impl_->ws; }
+uint64_t DeviceCommunicator::next_halo_epoch() { return ++impl_->halo_epoch; }
+
+void DeviceCommunicator::set_wait_timeout_ms(double ms) {
+  impl_->timeout_ns = (uint64_t)(std::max(0.001, ms) * 1e6);
+}
+
+DeviceStatus DeviceCommunicator::status() const {
+  DeviceStatus s;
+  memcpy(&s, (const void*)impl_->status_host, sizeof(s));
+  s.code = __atomic_load_n(&impl_->status_host->code, __ATOMIC_ACQUIRE);
+  return s;
+}
+
+void DeviceCommunicator::check_status() const {
+  const uint32_t code = __atomic_load_n(&impl_->status_host->code, __ATOMIC_ACQUIRE);
+  if (code == kStatusOk) return;
+  DeviceStatus s = status();
+  static const char* where[] = {"data-ready flags", "reduced-slice flags", "closing barrier", "send credit",
+                                "incoming data", "RMA / halo signal"};
+  impl_->stats.timeouts++;
+  throw_al_exception("device communicator failed: rank ", s.rank, " timed out waiting for rank ", s.peer, " (",
+                     where[s.where < 6 ? s.where : 0], ", epoch ", s.epoch, ", last seen ", s.seen,
+                     "); the communicator is unusable, create a new one");
+}
+
+CommStats DeviceCommunicator::stats() const { return impl_->stats; }
+
+// ---------------------------------------------------------------------------
+// collectives
+// ---------------------------------------------------------------------------
+void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArgs>& ranks, cudaStream_t stream) {
+  Impl& I = *impl_;
+  std::lock_guard<std::mutex> lock(I.mu);
+  check_status();
+  if ((int)ranks.size() != I.nlocal)
+    throw_al_exception("expected arguments for ", I.nlocal, " local rank(s), got ", ranks.size());
+  const int p = I.p;
+  if (d.root < 0 || d.root >= p) throw_al_exception("root ", d.root, " out of range");
+
+  const bool reduces = d.kind == DevColl::allreduce || d.kind == DevColl::reduce || d.kind == DevColl::reduce_scatter;
+  DType in = d.in, wire = d.wire, out = d.out;
+  size_t unit = 1;  // multiplier turning element counts into kernel counts
+  if (!reduces && in == wire && wire == out) {
+    unit = dtype_size(in);
+    in = wire = out = DType::u8;  // pure data movement: count bytes
+  }
+  if (reduces && !collective_supported(in, wire, out, d.op))
+    throw_al_exception("device backend: ", reduction_name(d.op), " on (", dtype_name(in), ", ", dtype_name(wire), ", ",
+                       dtype_name(out), ") is not supported");
+  if (!reduces && !(in == wire && wire == out) && !collective_supported(in, wire, out, ReductionOperator::sum))
+    throw_al_exception("device backend: no kernel for this datatype conversion");
+
+  CollParams P{};
+  P.ws = I.ws;
+  P.seq = ++I.seq;
+  P.timeout_ns = I.timeout_ns;
+  P.kind = (int)d.kind;
+  P.op = (int)d.op;
+  P.root = d.root;
+  P.rank0 = I.rank0;
+  P.count = d.count * unit;
+  P.scale = d.scale;
+  P.int_div = 1;
+  if (d.op == ReductionOperator::avg) {
+    if (dtype_is_float(wire)) P.scale *= 1.0 / p;
+    else P.int_div = p;
+  }
+
+  const size_t esz = dtype_size(wire);
+  const size_t half = I.ws.half_bytes;
+  const size_t full_e = half / esz;
+  const size_t cap_e = ((half / (size_t)p) / 256 * 256) / esz;
+  size_t max_work_bytes = 0;
+
+  for (int lr = 0; lr < I.nlocal; ++lr) {
+    const int r = I.rank0 + lr;
+    const RankArgs& a = ranks[(size_t)lr];
+    P.send[r] = a.send;
+    P.recv[r] = a.recv;
+    CountTable& T = P.tab[r];
+    if (d.vector) {
+      auto fill = [&](size_t* dst, const std::vector<size_t>& src, const char* what) {
+        if (src.empty()) { for (int i = 0; i < p; ++i) dst[i] = 0; return; }
+        if ((int)src.size() != p) throw_al_exception(what, " must have one entry per rank");
+        for (int i = 0; i < p; ++i) dst[i] = src[(size_t)i] * unit;
+      };
+      fill(T.send_counts, a.send_counts, "send counts");
+      fill(T.send_displs, a.send_displs, "send displacements");
+      fill(T.recv_counts, a.recv_counts, "receive counts");
+      fill(T.recv_displs, a.recv_displs, "receive displacements");
+    } else {
+      for (int i = 0; i < p; ++i) {
+        T.send_counts[i] = T.recv_counts[i] = d.count * unit;
+        T.send_displs[i] = T.recv_displs[i] = (size_t)i * d.count * unit;
+      }
+    }
+    size_t need = 0, chunk_unit = full_e, work = 0;
+    auto mx = [&](const size_t* v) { size_t m = 0; for (int i = 0; i < p; ++i) m = std::max(m, v[i]); return m; };
+    switch (d.kind) {
+      case DevColl::allreduce: case DevColl::reduce: case DevColl::bcast:
+        need = P.count; chunk_unit = full_e; work = P.count; break;
+      case DevColl::reduce_scatter: need = mx(T.recv_counts); chunk_unit = cap_e; work = need * (size_t)p; break;
+      case DevColl::allgather: need = mx(T.recv_counts); chunk_unit = full_e; work = need * (size_t)p; break;
+      case DevColl::alltoall:
+        need = std::max(mx(T.send_counts), mx(T.recv_counts)); chunk_unit = cap_e; work = need * (size_t)p; break;
+      case DevColl::gather:
+        need = r == d.root ? mx(T.recv_counts) : T.send_counts[r];
+        chunk_unit = full_e; work = r == d.root ? need * (size_t)p : need; break;
+      case DevColl::scatter:
+        need = r == d.root ? mx(T.send_counts) : T.recv_counts[r];
+        chunk_unit = cap_e; work = r == d.root ? need * (size_t)p : need; break;
+      case DevColl::barrier: need = 0; break;
+    }
+    P.local_chunks[r] = std::max<uint64_t>(1, ceil_div(need, chunk_unit));
+    if (P.local_chunks[r] >= (1u << 24) - 2) throw_al_exception("message too large for the configured staging size");
+    max_work_bytes = std::max(max_work_bytes, std::min(work * esz, half));
+  }
+
+  // ---- algorithm -----------------------------------------------------------------
+  const Tuning& tn = tuning();
+  const size_t bytes = P.count * esz;
+  AllreduceAlgo algo = d.algo;
+  bool zero_copy = false;
+  const SymmBlock* sb_in = nullptr;
+  const SymmBlock* sb_out = nullptr;
+  size_t off_in = 0, off_out = 0;
+  if (d.kind == DevColl::allreduce) {
+    const bool nvls_ok = !I.emulated && p > 1 && I.ws.mc_stage != nullptr && in == wire && wire == out &&
+                         nvls_allreduce_supported(wire, d.op);
+    if (algo == AllreduceAlgo::nvls && !nvls_ok)
+      throw_al_exception("NVLS allreduce requested but unavailable (no multicast, or type/operator unsupported)");
+    if (nvls_ok && (algo == AllreduceAlgo::automatic || algo == AllreduceAlgo::nvls)) {
+      const RankArgs& a = ranks[0];
+      sb_in = find_symm(a.send, bytes, &off_in);
+      sb_out = find_symm(a.recv, bytes, &off_out);
+      zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0);
+    }
+    if (algo == AllreduceAlgo::automatic) {
+      if (nvls_ok && (bytes >= tn.ar_nvls_min_bytes || (zero_copy && bytes >= 65536))) algo = AllreduceAlgo::nvls;
+      else if (bytes <= tn.ar_oneshot_max_bytes || p == 1) algo = AllreduceAlgo::one_shot;
+      else algo = AllreduceAlgo::two_shot;
+    }
+    P.two_phase = algo == AllreduceAlgo::two_shot ? 1 : 0;
+  }
+
+  // ---- grid ------------------------------------------------------------------------
+  int threads = std::min(512, tn.threads_per_cta);
+  int ctas = d.ctas > 0 ? d.ctas : (int)std::max<size_t>(1, ceil_div(max_work_bytes, (size_t)32768));
+  int cap = (d.kind == DevColl::allreduce && algo == AllreduceAlgo::nvls) ? tn.max_ctas_nvls : tn.max_ctas;
+  if (I.nlocal > 1) cap = std::min(cap, std::max(1, I.sm_count / I.nlocal));  // cooperative launch must be co-resident
+  ctas = std::max(1, std::min(ctas, cap));
+  if (max_work_bytes <= 4096) threads = std::min(threads, 256);
+
+  I.order_after_previous(stream);
+  I.stats.ops++;
+  I.stats.bytes += bytes ? bytes : max_work_bytes;
+  I.stats.kernels++;
+
+  if (d.kind == DevColl::allreduce && algo == AllreduceAlgo::nvls) {
+    NvlsParams N{};
+    N.ws = I.ws;
+    N.send = ranks[0].send;
+    N.recv = ranks[0].recv;
+    N.count = P.count;
+    N.chunks = P.local_chunks[I.rank0];
+    N.seq = P.seq;
+    N.timeout_ns = P.timeout_ns;
+    N.scale = P.scale;
+    N.rank = I.rank0;
+    if (zero_copy) {
+      N.mc_in = (const char*)sb_in->mc() + off_in;
+      N.mc_out = (char*)sb_out->mc() + off_out;
+      I.stats.ar_nvls_zero_copy++;
+    }
+    I.stats.ar_nvls++;
+    launch_nvls_allreduce(N, wire, d.op, ctas, threads, stream);
+    return;
+  }
+  if (d.kind == DevColl::allreduce) {
+    if (algo == AllreduceAlgo::one_shot) I.stats.ar_one_shot++;
+    else I.stats.ar_two_shot++;
+  }
+  launch_collective(P, in, wire, out, ctas, threads, I.nlocal, stream);
+}
+
+// ---------------------------------------------------------------------------
+// point-to-point
+// ---------------------------------------------------------------------------
+void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items, cudaStream_t stream) {
+  Impl& I = *impl_;
+  std::lock_guard<std::mutex> lock(I.mu);
+  check_status();
+  if (items.empty()) return;
+  const size_t slot = I.ws.mbox_slot_bytes;
+  // Transfers of the same (owner, peer, direction) must not share a launch:
+  // their pieces are numbered consecutively and have to land in order.
+  std::vector<char> placed(items.size(), 0);
+  size_t remaining = items.size();
+  I.order_after_previous(stream);
+  while (remaining) {
+    P2PParams P{};
+    P.ws = I.ws;
+    P.timeout_ns = I.timeout_ns;
+    std::vector<uint64_t> used;  // keys taken in this launch
+    size_t biggest = 0;
+    for (size_t i = 0; i < items.size() && P.nitems < P2PParams::kMaxItems; ++i) {
+      if (placed[i]) continue;
+      const P2PDesc& it = items[i];
+      const int owner = I.emulated ? it.owner : I.rank0;
+      if (owner < I.rank0 || owner >= I.rank0 + I.nlocal) throw_al_exception("p2p: owner rank ", owner, " is not local");
+      if (it.peer < 0 || it.peer >= I.p) throw_al_exception("p2p: peer ", it.peer, " out of range");
+      const uint64_t key = ((uint64_t)owner << 32) | ((uint64_t)it.peer << 1) | (it.is_send ? 1u : 0u);
+      if (std::find(used.begin(), used.end(), key) != used.end()) continue;
+      used.push_back(key);
+      const int k = P.nitems++;
+      P.sbuf[k] = it.sbuf;
+      P.rbuf[k] = it.rbuf;
+      P.bytes[k] = it.bytes;
+      P.peer[k] = it.peer;
+      P.is_send[k] = it.is_send ? 1 : 0;
+      P.owner[k] = owner;
+      auto& ctr = it.is_send ? I.p2p_sent : I.p2p_recvd;
+      uint64_t& c = ctr[(size_t)(owner - I.rank0) * (size_t)I.p + (size_t)it.peer];
+      P.base[k] = c;
+      c += std::max<size_t>(1, ceil_div(it.bytes, slot));
+      biggest = std::max(biggest, it.bytes);
+      placed[i] = 1;
+      --remaining;
+      I.stats.bytes += it.bytes;
+    }
+    int per = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(std::min(biggest, slot), (size_t)65536), 16));
+    if (I.nlocal > 1) per = std::max(1, std::min(per, I.sm_count / P.nitems));
+    P.ctas_per_item = per;
+    I.stats.ops++;
+    I.stats.kernels++;
+    launch_p2p(P, 512, I.nlocal > 1 ? 1 : 0, stream);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// symmetric user memory
+// ---------------------------------------------------------------------------
+void* DeviceCommunicator::symm_alloc(size_t bytes) {
+  Impl& I = *impl_;
+  std::unique_ptr<SymmBlock> b;
+  const size_t padded = round_up(std::max<size_t>(bytes, 16), 16);
+  if (I.emulated) b = SymmBlock::create_emulated(I.p, padded);
+  else b = SymmBlock::create(group_, padded, true);
+  void* ptr = b->peer(I.emulated ? 0 : I.rank0);
+  std::lock_guard<std::mutex> lock(I.mu);
+  I.user_blocks.push_back(std::move(b));
+  return ptr;
+}
+
+void DeviceCommunicator::symm_free(void* ptr) {
+  Impl& I = *impl_;
+  std::unique_ptr<SymmBlock> victim;
+  {
+    std::lock_guard<std::mutex> lock(I.mu);
+    for (auto it = I.user_blocks.begin(); it != I.user_blocks.end(); ++it) {
+      if ((*it)->peer(I.emulated ? 0 : I.rank0) == ptr) {
+        victim = std::move(*it);
+        I.user_blocks.erase(it);
+        break;
+      }
+    }
+  }
+  if (!victim) throw_al_exception("symm_free: pointer was not returned by symm_alloc of this communicator");
+  AL_CHECK_CUDA(cudaDeviceSynchronize());
+  if (!I.emulated) group_.barrier();  // nobody may still be addressing the block
+  victim.reset();
+}
+
+const SymmBlock* DeviceCommunicator::find_symm(const void* ptr, size_t bytes, size_t* offset) const {
+  const Impl& I = *impl_;
+  const int me = I.emulated ? 0 : I.rank0;
+  for (const auto& b : I.user_blocks) {
+    const char* base = (const char*)b->peer(me);
+    if ((const char*)ptr >= base && (const char*)ptr + bytes <= base + b->bytes()) {
+      if (offset) *offset = (size_t)((const char*)ptr - base);
+      return b.get();
+    }
+  }
+  return nullptr;
+}
+
+int DeviceCommunicator::symm_index(const void* ptr) const {
+  const Impl& I = *impl_;
+  const int me = I.emulated ? 0 : I.rank0;
+  for (size_t i = 0; i < I.user_blocks.size(); ++i) {
+    const char* base = (const char*)I.user_blocks[i]->peer(me);
+    if ((const char*)ptr >= base && (const char*)ptr < base + I.user_blocks[i]->bytes()) return (int)i;
+  }
+  return -1;
+}
+
+void* DeviceCommunicator::symm_peer_ptr(int index, int peer, size_t offset) const {
+  const Impl& I = *impl_;
+  if (index < 0 || (size_t)index >= I.user_blocks.size() || peer < 0 || peer >= I.p) return nullptr;
+  if (offset >= I.user_blocks[(size_t)index]->bytes()) return nullptr;
+  return (char*)I.user_blocks[(size_t)index]->peer(peer) + offset;
+}
+
+uint64_t DeviceCommunicator::wait_timeout_ns() const { return impl_->timeout_ns; }
+
+}  // namespace Al

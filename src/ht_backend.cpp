@@ -1,0 +1,176 @@
+// Host-transfer backend: staging copies, flags and the engine state (see al/ht_backend.hpp).
+#include "al/ht_backend.hpp"
+
+#include <algorithm>
+
+#include "al/cuda/gpu_status_flag.hpp"
+#include "al/cuda/gpu_wait.hpp"
+#include "al/mempool.hpp"
+#include "al/progress.hpp"
+#include "al/runtime.hpp"
+
+namespace Al {
+namespace internal {
+namespace ht {
+
+namespace {
+
+struct Extent { size_t send_elems = 0, recv_elems = 0; };
+
+/** How many elements of the (resolved) send and receive buffers the operation touches. */
+Extent extent_of(const Resolved& r, int rank, int size) {
+  Extent e;
+  const size_t p = (size_t)size;
+  auto span = [&](const std::vector<size_t>& c, const std::vector<size_t>& d) {
+    size_t m = 0;
+    for (size_t i = 0; i < c.size(); ++i) m = std::max(m, (d.empty() ? 0 : d[i]) + c[i]);
+    return m;
+  };
+  switch (r.kind) {
+    case OpKind::allreduce: case OpKind::reduce: e.send_elems = e.recv_elems = r.count; break;
+    case OpKind::bcast: e.send_elems = rank == r.root ? r.count : 0; e.recv_elems = rank == r.root ? 0 : r.count; break;
+    case OpKind::reduce_scatter:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
+      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
+      break;
+    case OpKind::allgather:
+      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
+      break;
+    case OpKind::alltoall:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = e.recv_elems = r.count * p; }
+      break;
+    case OpKind::gather:
+      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
+      break;
+    case OpKind::scatter:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
+      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
+      break;
+    case OpKind::barrier: break;
+  }
+  if (!r.send) e.send_elems = 0;
+  if (!r.recv) e.recv_elems = 0;
+  return e;
+}
+
+/** Engine state shared by collectives and point-to-point: stage 0 waits for the D2H flag. */
+class HTState final : public AlState {
+ public:
+  HTState(cudaStream_t stream, const char* name) : stream_(stream), name_(name) {}
+  ~HTState() override {
+    for (void* p : pinned_) mempool.release_bytes(MemoryType::CUDA_PINNED_HOST, p);
+  }
+  const void* get_compute_stream() const override { return stream_; }
+  const char* get_name() const override { return name_; }
+  RunType get_run_type() const override { return unbounded_ ? RunType::unbounded : RunType::bounded; }
+
+  PEAction step() override {
+    switch (phase_) {
+      case 0:
+        if (!start_flag.query()) return PEAction::cont;
+        phase_ = 1;
+        return PEAction::advance;
+      case 1:
+        launch_host();  // non-blocking host operation driven by the same engine
+        phase_ = 2;
+        return PEAction::cont;
+      case 2:
+        try {
+          if (!HostBackend::test(host_req)) return PEAction::cont;
+        } catch (const al_exception& e) {
+          std::cerr << "[al] host-transfer operation failed: " << e.what() << "\n";
+        }
+        wait.signal();  // release the stream: H2D copy and end flag follow
+        phase_ = 3;
+        return PEAction::cont;
+      default:
+        return end_flag.query() ? PEAction::complete : PEAction::cont;
+    }
+  }
+
+  void* pinned(size_t bytes) {
+    void* p = mempool.allocate_bytes(MemoryType::CUDA_PINNED_HOST, std::max<size_t>(bytes, 1));
+    pinned_.push_back(p);
+    return p;
+  }
+
+  cuda::GPUStatusFlag start_flag, end_flag;
+  cuda::GPUWait wait;
+  HostBackend::req_type host_req;
+  std::function<void(HostBackend::req_type*)> launcher;
+  bool unbounded_ = false;
+
+ private:
+  void launch_host() { launcher(&host_req); }
+  cudaStream_t stream_;
+  const char* name_;
+  int phase_ = 0;
+  std::vector<void*> pinned_;
+};
+
+}  // namespace
+
+void run_collective(Resolved&& r, HostTransferCommunicator& comm, cudaStream_t stream) {
+  const Extent e = extent_of(r, comm.rank(), comm.size());
+  const size_t esz = dtype_size(r.dt);
+  auto* st = new HTState(stream, "HTCollective");
+  void* hsend = e.send_elems ? st->pinned(e.send_elems * esz) : nullptr;
+  void* hrecv = e.recv_elems ? st->pinned(e.recv_elems * esz) : nullptr;
+  const void* dsend = r.send;
+  void* drecv = r.recv;
+  if (hsend) AL_CHECK_CUDA(cudaMemcpyAsync(hsend, dsend, e.send_elems * esz, cudaMemcpyDeviceToHost, stream));
+  // Vector forms may leave gaps in the receive buffer: start from its current contents.
+  if (hrecv && r.vector) AL_CHECK_CUDA(cudaMemcpyAsync(hrecv, drecv, e.recv_elems * esz, cudaMemcpyDeviceToHost, stream));
+  st->start_flag.record(stream);
+  st->wait.wait(stream);
+  if (hrecv) AL_CHECK_CUDA(cudaMemcpyAsync(drecv, hrecv, e.recv_elems * esz, cudaMemcpyHostToDevice, stream));
+  st->end_flag.record(stream);
+
+  auto shared = std::make_shared<Resolved>(std::move(r));
+  shared->send = hsend;
+  shared->recv = hrecv;
+  if (shared->kind == OpKind::bcast) { shared->send = shared->recv = hsend ? hsend : hrecv; }
+  HostCommunicator* hc = &comm.host();
+  st->launcher = [shared, hc](HostBackend::req_type* req) {
+    Resolved copy = *shared;
+    HostBackend::run(std::move(copy), *hc, req);
+  };
+  get_progress_engine()->enqueue(st);
+}
+
+void run_p2p(std::vector<host::P2PItem>&& items, HostTransferCommunicator& comm, cudaStream_t stream, const char* name) {
+  auto* st = new HTState(stream, name);
+  st->unbounded_ = true;
+  struct Back { void* host; void* dev; size_t bytes; };
+  std::vector<Back> backs;
+  for (auto& it : items) {
+    if (it.is_send) {
+      void* h = st->pinned(it.bytes);
+      if (it.bytes) AL_CHECK_CUDA(cudaMemcpyAsync(h, it.sbuf, it.bytes, cudaMemcpyDeviceToHost, stream));
+      it.sbuf = h;
+    } else {
+      void* h = st->pinned(it.bytes);
+      backs.push_back({h, it.rbuf, it.bytes});
+      it.rbuf = h;
+    }
+  }
+  st->start_flag.record(stream);
+  st->wait.wait(stream);
+  for (auto& b : backs)
+    if (b.bytes) AL_CHECK_CUDA(cudaMemcpyAsync(b.dev, b.host, b.bytes, cudaMemcpyHostToDevice, stream));
+  st->end_flag.record(stream);
+  auto shared = std::make_shared<std::vector<host::P2PItem>>(std::move(items));
+  HostCommunicator* hc = &comm.host();
+  st->launcher = [shared, hc, name](HostBackend::req_type* req) {
+    std::vector<host::P2PItem> copy = *shared;
+    HostBackend::run_p2p(std::move(copy), *hc, req, name);
+  };
+  get_progress_engine()->enqueue(st);
+}
+
+}  // namespace ht
+}  // namespace internal
+}  // namespace Al

@@ -1,0 +1,84 @@
+// Run-time tuning table (see al/tuning.hpp).
+#include "al/tuning.hpp"
+
+#include <sstream>
+
+#include "al/util/utils.hpp"
+
+namespace Al {
+
+Tuning& tuning() {
+  static Tuning t = [] { Tuning x; x.load_from_env(); return x; }();
+  return t;
+}
+
+void Tuning::load_from_env() {
+  using internal::env_long;
+  pe_num_concurrent_ops = (int)env_long("AL_PE_NUM_CONCURRENT_OPS", pe_num_concurrent_ops);
+  pe_start_on_demand = env_long("AL_PE_START_ON_DEMAND", pe_start_on_demand) != 0;
+  pe_bind_thread = env_long("AL_PE_BIND", pe_bind_thread) != 0;
+  pe_hang_seconds = (double)env_long("AL_PE_HANG_SECONDS", (long)pe_hang_seconds);
+  sync_mem_prealloc = (int)env_long("AL_SYNC_MEM_PREALLOC", sync_mem_prealloc);
+  stream_pool_size = (int)env_long("AL_CUDA_STREAM_POOL_SIZE", stream_pool_size);
+  disable_background_streams = env_long("AL_DISABLE_BACKGROUND_STREAMS", disable_background_streams) != 0;
+  host_stage_bytes = (size_t)env_long("AL_HOST_STAGE_BYTES", (long)host_stage_bytes);
+  host_mailbox_bytes = (size_t)env_long("AL_HOST_MAILBOX_BYTES", (long)host_mailbox_bytes);
+  host_wait_timeout_s = (double)env_long("AL_HOST_WAIT_TIMEOUT_S", (long)host_wait_timeout_s);
+  dev_stage_bytes = (size_t)env_long("AL_DEV_STAGE_BYTES", (long)dev_stage_bytes);
+  dev_mailbox_bytes = (size_t)env_long("AL_DEV_MAILBOX_BYTES", (long)dev_mailbox_bytes);
+  dev_wait_timeout_ms = (double)env_long("AL_DEV_WAIT_TIMEOUT_MS", (long)dev_wait_timeout_ms);
+  dev_enable_nvls = env_long("AL_DEV_NVLS", dev_enable_nvls) != 0;
+  ar_oneshot_max_bytes = (size_t)env_long("AL_AR_ONESHOT_MAX", (long)ar_oneshot_max_bytes);
+  ar_nvls_min_bytes = (size_t)env_long("AL_AR_NVLS_MIN", (long)ar_nvls_min_bytes);
+  max_ctas = (int)env_long("AL_MAX_CTAS_PER_OP", max_ctas);
+  max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
+  threads_per_cta = (int)env_long("AL_THREADS_PER_CTA", threads_per_cta);
+  trace = env_long("AL_TRACE", trace) != 0;
+  debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
+  signal_handler = env_long("AL_DISABLE_SIGNAL_HANDLER", 0) == 0;
+  if (max_ctas < 1) max_ctas = 1;
+  if (max_ctas > AL_MAX_CTAS) max_ctas = AL_MAX_CTAS;
+  if (max_ctas_nvls < 1) max_ctas_nvls = 1;
+  if (max_ctas_nvls > AL_MAX_CTAS) max_ctas_nvls = AL_MAX_CTAS;
+  if (threads_per_cta < 64) threads_per_cta = 64;
+  if (threads_per_cta > 1024) threads_per_cta = 1024;
+  threads_per_cta = threads_per_cta / 32 * 32;
+  // staging halves must stay 16-byte divisible for every rank count up to 8
+  dev_stage_bytes = dev_stage_bytes / 4096 * 4096;
+  if (dev_stage_bytes < 65536) dev_stage_bytes = 65536;
+  host_stage_bytes = host_stage_bytes / 4096 * 4096;
+  if (host_stage_bytes < 4096) host_stage_bytes = 4096;
+  if (host_mailbox_bytes < 256) host_mailbox_bytes = 256;
+}
+
+std::string Tuning::describe() const {
+  std::ostringstream ss;
+  ss << "pe_num_concurrent_ops = " << pe_num_concurrent_ops << "\n"
+     << "pe_start_on_demand = " << pe_start_on_demand << "\n"
+     << "pe_bind_thread = " << pe_bind_thread << "\n"
+     << "pe_hang_seconds = " << pe_hang_seconds << "\n"
+     << "pe_num_streams = " << AL_PE_NUM_STREAMS << "\n"
+     << "pe_num_pipeline_stages = " << AL_PE_NUM_PIPELINE_STAGES << "\n"
+     << "pe_input_queue_size = " << AL_PE_INPUT_QUEUE_SIZE << "\n"
+     << "sync_mem_prealloc = " << sync_mem_prealloc << "\n"
+     << "stream_pool_size = " << stream_pool_size << "\n"
+     << "disable_background_streams = " << disable_background_streams << "\n"
+     << "host_stage_bytes = " << host_stage_bytes << "\n"
+     << "host_mailbox_bytes = " << host_mailbox_bytes << "\n"
+     << "host_wait_timeout_s = " << host_wait_timeout_s << "\n"
+     << "dev_stage_bytes = " << dev_stage_bytes << "\n"
+     << "dev_mailbox_bytes = " << dev_mailbox_bytes << "\n"
+     << "dev_wait_timeout_ms = " << dev_wait_timeout_ms << "\n"
+     << "dev_enable_nvls = " << dev_enable_nvls << "\n"
+     << "ar_oneshot_max_bytes = " << ar_oneshot_max_bytes << "\n"
+     << "ar_nvls_min_bytes = " << ar_nvls_min_bytes << "\n"
+     << "max_ctas = " << max_ctas << "\n"
+     << "max_ctas_nvls = " << max_ctas_nvls << "\n"
+     << "threads_per_cta = " << threads_per_cta << "\n"
+     << "trace = " << trace << "\n"
+     << "debug_checks = " << debug_checks << "\n"
+     << "signal_handler = " << signal_handler << "\n";
+  return ss.str();
+}
+
+}  // namespace Al

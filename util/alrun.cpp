@@ -1,0 +1,90 @@
+// alrun - minimal single-host launcher: forks N copies of a program with the
+// rank environment the library's bootstrap understands.
+//
+//   alrun -n 4 [--timeout SECONDS] program [args...]
+//
+// Each child gets AL_RANK, AL_WORLD_SIZE, AL_LOCAL_RANK and a fresh AL_JOB_KEY.
+// If a child fails or the time limit passes, the remaining children are
+// terminated (by the process ids this launcher created) and alrun exits
+// non-zero.  It stands in for mpirun / jsrun / srun of the reference's test
+// and benchmark drivers (test/run_tests.py:109-143).
+#include <signal.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+int main(int argc, char** argv) {
+  int n = 1;
+  double timeout = 0;
+  int i = 1;
+  for (; i < argc; ++i) {
+    if (!strcmp(argv[i], "-n") && i + 1 < argc) n = atoi(argv[++i]);
+    else if (!strcmp(argv[i], "--timeout") && i + 1 < argc) timeout = atof(argv[++i]);
+    else break;
+  }
+  if (i >= argc || n < 1) {
+    fprintf(stderr, "usage: alrun -n N [--timeout SECONDS] program [args...]\n");
+    return 2;
+  }
+  const std::string key = "alrun-" + std::to_string(getpid()) + "-" +
+                          std::to_string(std::chrono::steady_clock::now().time_since_epoch().count());
+  std::vector<pid_t> kids;
+  for (int r = 0; r < n; ++r) {
+    pid_t pid = fork();
+    if (pid < 0) { perror("fork"); return 2; }
+    if (pid == 0) {
+      setenv("AL_RANK", std::to_string(r).c_str(), 1);
+      setenv("AL_WORLD_SIZE", std::to_string(n).c_str(), 1);
+      setenv("AL_LOCAL_RANK", std::to_string(r).c_str(), 1);
+      setenv("AL_JOB_KEY", key.c_str(), 1);
+      execvp(argv[i], argv + i);
+      perror("execvp");
+      _exit(127);
+    }
+    kids.push_back(pid);
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  int failures = 0;
+  size_t left = kids.size();
+  std::vector<bool> done(kids.size(), false);
+  while (left) {
+    bool progressed = false;
+    for (size_t k = 0; k < kids.size(); ++k) {
+      if (done[k]) continue;
+      int st = 0;
+      pid_t w = waitpid(kids[k], &st, WNOHANG);
+      if (w == kids[k]) {
+        done[k] = true;
+        --left;
+        progressed = true;
+        const bool ok = WIFEXITED(st) && WEXITSTATUS(st) == 0;
+        if (!ok) {
+          ++failures;
+          fprintf(stderr, "alrun: rank %zu %s %d\n", k, WIFSIGNALED(st) ? "killed by signal" : "exited with",
+                  WIFSIGNALED(st) ? WTERMSIG(st) : WEXITSTATUS(st));
+        }
+      }
+    }
+    const double el = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if ((failures && left) || (timeout > 0 && el > timeout && left)) {
+      if (!failures) fprintf(stderr, "alrun: time limit of %.0f s exceeded\n", timeout);
+      // give the others a moment to notice and exit on their own, then end them
+      std::this_thread::sleep_for(std::chrono::milliseconds(failures ? 2000 : 0));
+      for (size_t k = 0; k < kids.size(); ++k)
+        if (!done[k] && waitpid(kids[k], nullptr, WNOHANG) == 0) kill(kids[k], SIGKILL);
+      for (size_t k = 0; k < kids.size(); ++k)
+        if (!done[k]) { waitpid(kids[k], nullptr, 0); done[k] = true; }
+      left = 0;
+      if (!failures) failures = 1;
+    }
+    if (!progressed) std::this_thread::sleep_for(std::chrono::milliseconds(5));
+  }
+  return failures ? 1 : 0;
+}

@@ -71,18 +71,20 @@ void launch_wait_word(const uint64_t* word, uint64_t value, uint64_t timeout_ns,
  */
 struct HaloParams {
   Workspace ws;
-  const float* local;      ///< this rank's tensor including halo planes: (NC, D_local + 2*depth, H*W)
-  float* peer_lo;          ///< lower neighbour's tensor (peer-mapped) or nullptr at the boundary
-  float* peer_hi;          ///< upper neighbour's tensor or nullptr
-  size_t nc;               ///< N*C
-  size_t d_local;          ///< interior planes per rank
-  size_t plane;            ///< H*W elements
-  size_t depth;            ///< halo depth in planes
-  uint64_t epoch;          ///< value signalled to / expected from the neighbours
+  float* tensor[kMaxRanks]; ///< every rank's tensor (incl. halo planes) as mapped here: (NC, D_local + 2*depth, H*W);
+                            ///< only the executing rank(s) and their neighbours need valid entries
+  int lo[kMaxRanks];        ///< lower neighbour of each rank, -1 at the boundary
+  int hi[kMaxRanks];        ///< upper neighbour, -1 at the boundary
+  size_t nc;                ///< N*C
+  size_t d_local;           ///< interior planes per rank
+  size_t plane;             ///< H*W elements
+  size_t depth;             ///< halo depth in planes
+  uint64_t epoch;           ///< value signalled to / expected from the neighbours
   uint64_t timeout_ns;
-  int rank, lo_rank, hi_rank;
+  int rank0;                ///< block (x, y) works for rank rank0 + y
 };
-void launch_halo_exchange(const HaloParams& P, int ctas, int threads, cudaStream_t stream);
+/** local_ranks > 1 launches cooperatively (single-GPU emulation of all ranks). */
+void launch_halo_exchange(const HaloParams& P, int ctas, int threads, int local_ranks, cudaStream_t stream);
 /** Stand-alone pack / unpack of boundary planes (for the unfused comparison path). */
 void launch_halo_pack(float* packed, const float* tensor, size_t nc, size_t d_total, size_t plane,
                       size_t d_first, size_t depth, cudaStream_t stream);

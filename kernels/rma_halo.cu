@@ -59,17 +59,21 @@ __device__ __forceinline__ void copy_planes(float* dst, const float* src, size_t
 
 __global__ void __launch_bounds__(512) halo_exchange_kernel(const __grid_constant__ HaloParams P) {
   const Workspace& ws = P.ws;
-  const int rank = P.rank;
+  const int rank = P.rank0 + (int)blockIdx.y;
   if (poisoned(ws, rank)) return;
   uint64_t* mine = ws.flags[rank];
   const size_t d_total = P.d_local + 2 * P.depth;
-  const bool has_lo = P.peer_lo != nullptr, has_hi = P.peer_hi != nullptr;
+  const int lo_rank = P.lo[rank], hi_rank = P.hi[rank];
+  const bool has_lo = lo_rank >= 0, has_hi = hi_rank >= 0;
+  const float* local = P.tensor[rank];
+  float* peer_lo = has_lo ? P.tensor[lo_rank] : nullptr;
+  float* peer_hi = has_hi ? P.tensor[hi_rank] : nullptr;
 
   // 1. Tell both neighbours that my halo planes may be overwritten (this
   //    kernel is stream-ordered after whatever consumed them last).
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    if (has_lo) st_release_sys(flag_slot(ws.flags[P.lo_rank], FlagLayout::off_halo, 1), P.epoch);  // I am its "hi"
-    if (has_hi) st_release_sys(flag_slot(ws.flags[P.hi_rank], FlagLayout::off_halo, 0), P.epoch);  // I am its "lo"
+    if (has_lo) st_release_sys(flag_slot(ws.flags[lo_rank], FlagLayout::off_halo, 1), P.epoch);  // I am its "hi"
+    if (has_hi) st_release_sys(flag_slot(ws.flags[hi_rank], FlagLayout::off_halo, 0), P.epoch);  // I am its "lo"
   }
   // 2. Wait until the neighbours said the same.
   __shared__ int s_ok;
@@ -80,7 +84,7 @@ __global__ void __launch_bounds__(512) halo_exchange_kernel(const __grid_constan
     if (need) {
       uint64_t seen = 0;
       if (!wait_flag(flag_slot(mine, FlagLayout::off_halo, threadIdx.x), P.epoch, P.timeout_ns, &seen)) {
-        report_timeout(ws, rank, threadIdx.x == 0 ? P.lo_rank : P.hi_rank, 5, P.epoch, seen);
+        report_timeout(ws, rank, threadIdx.x == 0 ? lo_rank : hi_rank, 5, P.epoch, seen);
         s_ok = 0;
       }
     }
@@ -94,12 +98,12 @@ __global__ void __launch_bounds__(512) halo_exchange_kernel(const __grid_constan
   if (has_lo && has_hi && n >= 2) {
     const unsigned h = n / 2;
     if (blockIdx.x < h)
-      copy_planes(P.peer_lo, P.local, P.nc, d_total, P.plane, P.depth, P.depth + P.d_local, P.depth, blockIdx.x, h);
+      copy_planes(peer_lo, local, P.nc, d_total, P.plane, P.depth, P.depth + P.d_local, P.depth, blockIdx.x, h);
     else
-      copy_planes(P.peer_hi, P.local, P.nc, d_total, P.plane, P.d_local, 0, P.depth, blockIdx.x - h, n - h);
+      copy_planes(peer_hi, local, P.nc, d_total, P.plane, P.d_local, 0, P.depth, blockIdx.x - h, n - h);
   } else {
-    if (has_lo) copy_planes(P.peer_lo, P.local, P.nc, d_total, P.plane, P.depth, P.depth + P.d_local, P.depth, blockIdx.x, n);
-    if (has_hi) copy_planes(P.peer_hi, P.local, P.nc, d_total, P.plane, P.d_local, 0, P.depth, blockIdx.x, n);
+    if (has_lo) copy_planes(peer_lo, local, P.nc, d_total, P.plane, P.depth, P.depth + P.d_local, P.depth, blockIdx.x, n);
+    if (has_hi) copy_planes(peer_hi, local, P.nc, d_total, P.plane, P.d_local, 0, P.depth, blockIdx.x, n);
   }
 
   // 4. The last CTA to finish publishes "data landed" to both neighbours.
@@ -110,8 +114,8 @@ __global__ void __launch_bounds__(512) halo_exchange_kernel(const __grid_constan
     if (n > 1) last = atomicInc((unsigned*)flag_slot(mine, FlagLayout::off_arrive, 3), n - 1) == n - 1;
     if (last) {
       __threadfence_system();
-      if (has_lo) st_release_sys(flag_slot(ws.flags[P.lo_rank], FlagLayout::off_halo, 3), P.epoch);
-      if (has_hi) st_release_sys(flag_slot(ws.flags[P.hi_rank], FlagLayout::off_halo, 2), P.epoch);
+      if (has_lo) st_release_sys(flag_slot(ws.flags[lo_rank], FlagLayout::off_halo, 3), P.epoch);
+      if (has_hi) st_release_sys(flag_slot(ws.flags[hi_rank], FlagLayout::off_halo, 2), P.epoch);
     }
   }
   __syncthreads();
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(512) halo_exchange_kernel(const __grid_constan
     if (need) {
       uint64_t seen = 0;
       if (!wait_flag(flag_slot(mine, FlagLayout::off_halo, 2 + threadIdx.x), P.epoch, P.timeout_ns, &seen))
-        report_timeout(ws, rank, threadIdx.x == 0 ? P.lo_rank : P.hi_rank, 5, P.epoch, seen);
+        report_timeout(ws, rank, threadIdx.x == 0 ? lo_rank : hi_rank, 5, P.epoch, seen);
     }
   }
 }
@@ -164,9 +168,13 @@ void launch_wait_word(const uint64_t* word, uint64_t value, uint64_t timeout_ns,
   AL_CHECK_CUDA(cudaGetLastError());
 }
 
-void launch_halo_exchange(const HaloParams& P, int ctas, int threads, cudaStream_t stream) {
-  halo_exchange_kernel<<<ctas, threads, 0, stream>>>(P);
-  AL_CHECK_CUDA(cudaGetLastError());
+void launch_halo_exchange(const HaloParams& P, int ctas, int threads, int local_ranks, cudaStream_t stream) {
+  dim3 grid((unsigned)ctas, (unsigned)local_ranks);
+  void* args[] = {(void*)&P};
+  if (local_ranks > 1)
+    AL_CHECK_CUDA(cudaLaunchCooperativeKernel((const void*)halo_exchange_kernel, grid, dim3((unsigned)threads), args, 0, stream));
+  else
+    AL_CHECK_CUDA(cudaLaunchKernel((const void*)halo_exchange_kernel, grid, dim3((unsigned)threads), args, 0, stream));
 }
 
 void launch_halo_pack(float* packed, const float* tensor, size_t nc, size_t d_total, size_t plane, size_t d_first,

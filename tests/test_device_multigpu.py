@@ -1,0 +1,28 @@
+"""Multi-process device backend (one process per GPU).  Needs at least two GPUs; on a
+single-GPU box these tests skip and the emulated tests cover the same kernels."""
+import os
+import subprocess
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("op", ["allreduce", "reduce", "reduce_scatter", "reduce_scatterv", "allgather", "allgatherv",
+                                "alltoall", "alltoallv", "bcast", "gather", "scatterv", "barrier", "send", "sendrecv",
+                                "multisendrecv"])
+def test_ops_device_backend(bin_dir, op):
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    env = {**os.environ, "NCCL_NVLS_ENABLE": "0"}
+    for extra in ([], ["--inplace", "--nonblocking"]):
+        r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "180", str(bin_dir / "test_ops"),
+                            "--backend", "device", "--op", op, "--max-size", str(1 << 20), "--odd-sizes", "--zero"] + extra,
+                           capture_output=True, text=True, timeout=240, env=env)
+        assert r.returncode == 0, r.stdout + r.stderr

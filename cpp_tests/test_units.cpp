@@ -1,0 +1,257 @@
+// Unit tests of the host runtime pieces that need no second rank: integer
+// helpers, the lock-free queues (with a concurrent stress), the caching
+// allocator, the resource pool, the progress engine's ordering / concurrency
+// rules, tracing, host reductions and the life cycle.  The reference has no
+// unit tests for these components; they are covered here because every backend
+// stands on them.
+#include <algorithm>
+#include <cmath>
+#include <sstream>
+#include <atomic>
+#include <cstdio>
+#include <thread>
+
+#include "Al.hpp"
+#include "al/host/reduce.hpp"
+#include "al/mempool.hpp"
+#include "al/util/caching_allocator.hpp"
+#include "al/util/mpsc_queue.hpp"
+#include "al/util/resource_pool.hpp"
+#include "al/util/spsc_queue.hpp"
+
+using namespace Al;
+using namespace Al::internal;
+
+static int g_fail = 0;
+#define CHECK(c) do { if (!(c)) { fprintf(stderr, "FAIL %s:%d: %s\n", __FILE__, __LINE__, #c); ++g_fail; } } while (0)
+
+static void test_meta() {
+  CHECK(is_pow2(1) && is_pow2(64) && !is_pow2(0) && !is_pow2(48));
+  CHECK(floor_log2(1) == 0 && floor_log2(1023) == 9 && ceil_log2(1025) == 11 && ceil_log2(1024) == 10);
+  CHECK(next_highest_pow2(17) == 32 && next_highest_pow2(32) == 32);
+  CHECK(num_pow2s_between(1, 64) == 7 && num_pow2s_between(3, 5) == 1);
+  auto a = pow2_ar<4>(8);
+  CHECK(a[0] == 8 && a[3] == 64);
+  std::vector<size_t> v{3, 0, 5};
+  auto ps = excl_prefix_sum(v);
+  CHECK(ps[0] == 0 && ps[1] == 3 && ps[2] == 3);
+}
+
+static void test_spsc() {
+  SPSCQueue<int*> q(8);
+  int vals[16];
+  for (int i = 0; i < 8; ++i) CHECK(q.try_push(&vals[i]));
+  CHECK(!q.try_push(&vals[8]));
+  int* out = nullptr;
+  CHECK(q.peek(out) && out == &vals[0]);
+  q.pop_always();
+  CHECK(q.pop(out) && out == &vals[1]);
+  // concurrent: order and completeness
+  SPSCQueue<size_t> big(1024);
+  const size_t N = 2000000;
+  std::thread prod([&] { for (size_t i = 1; i <= N;) if (big.try_push(i)) ++i; });
+  size_t expect = 1, got;
+  while (expect <= N) if (big.pop(got)) { CHECK(got == expect); ++expect; }
+  prod.join();
+}
+
+static void test_mpsc() {
+  MPSCQueue<size_t> q(4096);
+  const int P = 4;
+  const size_t N = 300000;
+  std::vector<std::thread> prods;
+  for (int t = 0; t < P; ++t)
+    prods.emplace_back([&, t] { for (size_t i = 0; i < N;) if (q.try_push((size_t)t * N + i)) ++i; });
+  std::vector<size_t> next(P, 0);
+  size_t total = 0, v;
+  while (total < P * N) {
+    if (q.pop(v)) {
+      const size_t t = v / N, i = v % N;
+      CHECK(i == next[t]);  // per-producer order is preserved
+      next[t] = i + 1;
+      ++total;
+    }
+  }
+  for (auto& th : prods) th.join();
+  CHECK(!q.pop(v));
+}
+
+struct CountingRaw {
+  static int live;
+  void* allocate(size_t b) { ++live; return malloc(b); }
+  void deallocate(void* p, size_t) { --live; free(p); }
+};
+int CountingRaw::live = 0;
+
+static void test_allocator() {
+  CHECK(SizeClasses::bin_size(SizeClasses::bin_of(100)) >= 100);
+  for (size_t s : {1ul, 64ul, 65ul, 1000ul, 4097ul, 1000000ul, (1ul << 28)})
+    CHECK(SizeClasses::bin_size(SizeClasses::bin_of(s)) >= s && SizeClasses::bin_size(SizeClasses::bin_of(s)) < s * 5 / 4 + 65);
+  CachingAllocator<CountingRaw> a;
+  void* p = a.allocate(1000);
+  a.release(p);
+  void* q = a.allocate(900);  // same class: must be served from the cache
+  CHECK(q == p && a.hits() == 1);
+  void* huge = a.allocate((1ul << 28) + 5);
+  a.release(huge);  // above the largest class: returned immediately
+  a.release(q);
+  CHECK(CountingRaw::live == 1);
+  a.clear();
+  CHECK(CountingRaw::live == 0);
+  bool threw = false;
+  try { int x; a.release(&x); } catch (const al_exception&) { threw = true; }
+  CHECK(threw);
+  int* hp = mempool.allocate<MemoryType::HOST, int>(100);
+  hp[99] = 7;
+  mempool.release<MemoryType::HOST>(hp);
+}
+
+struct IntFactory {
+  int next = 0;
+  int create() { return ++next; }
+  void destroy(int) {}
+};
+
+static void test_pool() {
+  LockedResourcePool<int, IntFactory> pool;
+  pool.preallocate(3);
+  CHECK(pool.idle() == 3);
+  int a = pool.get(), b = pool.get(), c = pool.get(), d = pool.get();
+  CHECK(pool.idle() == 0 && d == 4 && a != b && b != c);
+  pool.release(a);
+  CHECK(pool.get() == a);
+  pool.clear();
+}
+
+// A state that records when it ran and finishes after a number of steps.
+struct ProbeState : AlState {
+  ProbeState(const void* key, int id, int steps, std::vector<int>* log, std::atomic<int>* running, std::atomic<int>* peak,
+             RunType rt = RunType::bounded, bool advance = false)
+      : key_(key), id_(id), left_(steps), log_(log), running_(running), peak_(peak), rt_(rt), adv_(advance) {}
+  void start() override {
+    int r = ++*running_;
+    int p = peak_->load();
+    while (r > p && !peak_->compare_exchange_weak(p, r)) {}
+  }
+  PEAction step() override {
+    if (adv_ && !advanced_) { advanced_ = true; return PEAction::advance; }
+    if (--left_ > 0) return PEAction::cont;
+    log_->push_back(id_);
+    --*running_;
+    return PEAction::complete;
+  }
+  const void* get_compute_stream() const override { return key_; }
+  RunType get_run_type() const override { return rt_; }
+  const char* get_name() const override { return "Probe"; }
+  const void* key_;
+  int id_, left_;
+  std::vector<int>* log_;
+  std::atomic<int>*running_, *peak_;
+  RunType rt_;
+  bool adv_, advanced_ = false;
+};
+
+static void test_progress_engine() {
+  ProgressEngine pe;
+  std::vector<int> log;
+  std::atomic<int> running{0}, peak{0};
+  int k1, k2;
+  // Same stream: bounded states beyond the limit wait; completion order of equal-length states is FIFO.
+  for (int i = 0; i < 12; ++i) pe.enqueue(new ProbeState(&k1, i, 200, &log, &running, &peak));
+  while (pe.in_flight() || log.size() < 12) std::this_thread::yield();
+  CHECK(peak.load() <= std::max(1, tuning().pe_num_concurrent_ops));
+  for (int i = 0; i < 12; ++i) CHECK(log[(size_t)i] == i);
+  // Unbounded states are all admitted at once.
+  log.clear(); peak = 0;
+  for (int i = 0; i < 10; ++i) pe.enqueue(new ProbeState(&k2, i, 2000, &log, &running, &peak, RunType::unbounded));
+  while (log.size() < 10) std::this_thread::yield();
+  CHECK(peak.load() == 10);
+  // Pipeline: states advance to stage 1 in order.
+  log.clear();
+  for (int i = 0; i < 4; ++i) pe.enqueue(new ProbeState(&k1, i, 10 * (4 - i), &log, &running, &peak, RunType::bounded, true));
+  while (log.size() < 4) std::this_thread::yield();
+  std::ostringstream ss;
+  pe.dump_state(ss);
+  CHECK(ss.str().find("Progress engine") != std::string::npos);
+  pe.stop();
+  CHECK(!pe.is_running());
+}
+
+static void test_reduce_and_halves() {
+  using namespace Al::internal::host;
+  for (float f : {0.f, 1.f, -2.5f, 65504.f, 6.1e-5f, 1e-7f, 0.333f}) {
+    const float back = half_to_float(float_to_half(f));
+    CHECK(std::fabs(back - f) <= std::fabs(f) * 1e-3f + 1e-7f);
+    const float b2 = bf16_to_float(float_to_bf16(f));
+    CHECK(std::fabs(b2 - f) <= std::fabs(f) * 8e-3f + 1e-30f);
+  }
+  CHECK(float_to_half(1e6f) == 0x7c00);
+  int a[4] = {1, 2, 3, 4}, b[4] = {4, 3, 2, 1}, out[4];
+  const void* srcs[2] = {a, b};
+  reduce_multi(DType::i32, ReductionOperator::max, out, srcs, 2, 4);
+  CHECK(out[0] == 4 && out[1] == 3 && out[2] == 3 && out[3] == 4);
+  reduce_multi(DType::i32, ReductionOperator::bxor, out, srcs, 2, 4);
+  CHECK(out[0] == 5 && out[3] == 5);
+  reduce_multi(DType::i32, ReductionOperator::avg, out, srcs, 2, 4);
+  CHECK(out[0] == 2 && out[1] == 2);
+  CHECK(!Al::internal::host::reduction_supported(DType::f32, ReductionOperator::band));
+  bool threw = false;
+  float fa[1] = {1}, fo[1];
+  const void* fs[1] = {fa};
+  try { reduce_multi(DType::f32, ReductionOperator::bor, fo, fs, 1, 1); } catch (const al_exception&) { threw = true; }
+  CHECK(threw);
+}
+
+static void test_lifecycle_and_trace() {
+  CHECK(!Initialized());
+  Initialize();
+  Initialize();  // idempotent
+  CHECK(Initialized());
+  trace::enable(true);
+  {
+    HostCommunicator comm;
+    CHECK(comm.size() == 1 && comm.rank() == 0);
+    float x[8] = {1, 2, 3, 4, 5, 6, 7, 8};
+    Allreduce<HostBackend>(x, 8, ReductionOperator::sum, comm);
+    CHECK(x[7] == 8);
+    HostBackend::req_type req;
+    NonblockingAllreduce<HostBackend>(x, 8, ReductionOperator::sum, comm, req);
+    Wait<HostBackend>(req);
+    CHECK(req == nullptr);
+    NonblockingBarrier<HostBackend>(comm, req);
+    while (!Test<HostBackend>(req)) {}
+    CHECK(Test<HostBackend>(req));  // a null request tests as complete
+    float y[4] = {9, 9, 9, 9};
+    SendRecv<HostBackend>(y, 4, 0, 0, comm);  // self exchange in place
+    CHECK(y[0] == 9);
+  }
+  auto lines = trace::snapshot();
+  bool saw = false, saw_pe = false;
+  for (auto& l : lines) {
+    if (l.find("HostBackend float allreduce 0 1") != std::string::npos) saw = true;
+    if (l.find("PE START") != std::string::npos) saw_pe = true;
+  }
+  CHECK(saw && saw_pe);
+  trace::enable(false);
+  trace::clear();
+  Finalize();
+  Finalize();
+  CHECK(!Initialized());
+  bool threw = false;
+  try { HostCommunicator c; } catch (const al_exception&) { threw = true; }
+  CHECK(threw);
+}
+
+int main() {
+  test_meta();
+  test_spsc();
+  test_mpsc();
+  test_allocator();
+  test_pool();
+  test_progress_engine();
+  test_reduce_and_halves();
+  test_lifecycle_and_trace();
+  if (g_fail) { fprintf(stderr, "%d check(s) failed\n", g_fail); return 1; }
+  printf("all unit tests passed\n");
+  return 0;
+}

@@ -599,6 +599,7 @@ HostCommunicator& HostCommunicator::operator=(HostCommunicator&&) noexcept = def
 void HostCommunicator::collective(CollArgs&& args, Request* req) {
   Impl* ci = impl_.get();
   if (ci->failed.load()) throw_al_exception("communicator is in a failed state: ", ci->fail_msg);
+  if (args.root < 0 || args.root >= ci->p) throw_al_exception("root ", args.root, " out of range for ", ci->p, " rank(s)");
   if (args.kind == Coll::allreduce || args.kind == Coll::reduce || args.kind == Coll::reduce_scatter) {
     if (!reduction_supported(args.dt, args.op))
       throw_al_exception("reduction ", reduction_name(args.op), " is not defined for ", dtype_name(args.dt));

@@ -42,6 +42,8 @@ def rand(n, dtype, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     if dtype.is_floating_point:
         return (torch.randint(-16, 17, (n,), generator=g, device="cuda").float() / 8).to(dtype)
+    if dtype == torch.uint8:
+        return torch.randint(0, 7, (n,), generator=g, device="cuda").to(dtype)
     return torch.randint(-6, 7, (n,), generator=g, device="cuda").to(dtype)
 
 
@@ -87,7 +89,7 @@ def test_allreduce_types_ops(comm, dtype, op):
         xs = [(torch.randint(0, 2, (n,), device="cuda") * 2 - 1).to(dtype) if dtype != torch.uint8
               else torch.ones(n, device="cuda", dtype=dtype) for _ in range(p)]
     else:
-        xs = [rand(n, dtype, 20 + r).abs() if dtype == torch.uint8 else rand(n, dtype, 20 + r) for r in range(p)]
+        xs = [rand(n, dtype, 20 + r) for r in range(p)]
     if op == "avg" and not dtype.is_floating_point:
         want = torch.stack([x.to(torch.int64) for x in xs]).sum(0)
         want = torch.div(want, p, rounding_mode="trunc").float()

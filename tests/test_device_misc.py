@@ -70,15 +70,14 @@ def test_halo_exchange_emulated(al):
         hx.exchange()
         torch.cuda.synchronize()
         for r in range(p):
-            lo, hi = r - 1, r + 1
-            if periodic:
-                lo, hi = lo % p, hi % p
-            if 0 <= lo < p and lo != r or (periodic and p > 1):
-                if lo >= 0:
-                    assert torch.equal(hx.tensors[r][:, :, :depth], snap[lo][:, :, d:d + depth])
+            has_lo = p > 1 and (periodic or r > 0)
+            has_hi = p > 1 and (periodic or r < p - 1)
+            lo, hi = (r - 1) % p, (r + 1) % p
+            if has_lo:   # my lower halo = the lower neighbour's last interior planes
+                assert torch.equal(hx.tensors[r][:, :, :depth], snap[lo][:, :, d:d + depth])
             else:
                 assert torch.all(hx.tensors[r][:, :, :depth] == -1.0)
-            if hi < p:
+            if has_hi:   # my upper halo = the upper neighbour's first interior planes
                 assert torch.equal(hx.tensors[r][:, :, depth + d:], snap[hi][:, :, depth:2 * depth])
             else:
                 assert torch.all(hx.tensors[r][:, :, depth + d:] == -1.0)

@@ -1,0 +1,107 @@
+"""CPU tests (no GPU): C++ unit tests, the op-vs-serial-oracle driver on the host backend over
+several rank counts, the world-size-2 plumbing configuration, launcher environments, tracing and
+host-side failure detection."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+W = ROOT / "tests" / "workers"
+
+
+def run(cmd, env=None, timeout=300):
+    e = {**os.environ, **(env or {})}
+    return subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=timeout, env=e)
+
+
+def test_cpp_unit_tests(bin_dir):
+    r = run([bin_dir / "test_units"])
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_al_info(bin_dir):
+    r = run([bin_dir / "al_info"])
+    assert r.returncode == 0 and "Aluminum-B200" in r.stdout and "dev_stage_bytes" in r.stdout
+
+
+OPS = ["allreduce", "reduce", "reduce_scatter", "reduce_scatterv", "allgather", "allgatherv", "gather", "gatherv",
+       "scatter", "scatterv", "alltoall", "alltoallv", "bcast", "barrier", "send", "sendrecv", "multisendrecv"]
+
+
+@pytest.mark.parametrize("op", OPS)
+@pytest.mark.parametrize("ranks", [2, 3])
+def test_ops_host(bin_dir, op, ranks):
+    for extra in ([], ["--inplace", "--nonblocking", "--root", "1"]):
+        r = run([bin_dir / "alrun", "-n", ranks, "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", op,
+                 "--max-size", "4096", "--odd-sizes", "--zero", "--quiet"] + extra)
+        assert r.returncode == 0, f"{op} {extra}: {r.stdout}{r.stderr}"
+
+
+@pytest.mark.parametrize("dtype,rop", [("double", "prod"), ("int", "band"), ("uchar", "max"), ("llong", "min"),
+                                       ("half", "sum"), ("bfloat16", "sum"), ("int", "lxor"), ("float", "avg"),
+                                       ("short", "bor")])
+def test_ops_host_types(bin_dir, dtype, rop):
+    r = run([bin_dir / "alrun", "-n", "4", "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", "allreduce",
+             "--datatype", dtype, "--reduction-op", rop, "--max-size", "2048", "--odd-sizes", "--quiet"])
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_multichunk_small_staging(bin_dir):
+    env = {"AL_HOST_STAGE_BYTES": "4096", "AL_HOST_MAILBOX_BYTES": "256"}
+    for op in ("allreduce", "alltoallv", "reduce_scatterv", "multisendrecv", "gatherv"):
+        r = run([bin_dir / "alrun", "-n", "4", "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", op,
+                 "--min-size", "1024", "--max-size", "32768", "--odd-sizes", "--nonblocking", "--quiet"], env=env)
+        assert r.returncode == 0, op + r.stdout + r.stderr
+
+
+def test_config1_world2_python(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "2", "--timeout", "200", sys.executable, W / "host_config1.py"])
+    assert r.returncode == 0 and r.stdout.count("ok") == 2, r.stdout + r.stderr
+
+
+def test_torchrun_style_environment(bin_dir):
+    """RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT are understood without the library's own launcher."""
+    procs = []
+    for rank in range(2):
+        env = {**os.environ, "RANK": str(rank), "WORLD_SIZE": "2", "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
+               "MASTER_PORT": str(29000 + os.getpid() % 2000)}
+        for k in ("AL_RANK", "AL_WORLD_SIZE", "AL_JOB_KEY"):
+            env.pop(k, None)
+        procs.append(subprocess.Popen([str(bin_dir / "test_ops"), "--backend", "host", "--op", "allreduce", "--max-size", "512"],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+
+
+def test_rank_that_never_joins_is_detected(bin_dir):
+    env = {"AL_HOST_WAIT_TIMEOUT_S": "1"}
+    r = run([bin_dir / "alrun", "-n", "2", "--timeout", "60", sys.executable, W / "host_fault.py"], env=env, timeout=120)
+    assert "rank 0 detected the failure" in r.stdout, r.stdout + r.stderr
+
+
+def test_bootstrap_times_out_when_a_rank_is_missing(bin_dir):
+    env = {"AL_RANK": "0", "AL_WORLD_SIZE": "2", "AL_JOB_KEY": f"lonely-{os.getpid()}", "AL_BOOTSTRAP_TIMEOUT_S": "1"}
+    r = run([bin_dir / "test_ops", "--backend", "host", "--op", "barrier"], env=env, timeout=60)
+    assert r.returncode != 0 and "timed out" in r.stderr
+
+
+def test_trace_file_is_written(bin_dir, tmp_path):
+    env = {"AL_TRACE": "1", "AL_TRACE_DIR": str(tmp_path)}
+    r = run([bin_dir / "alrun", "-n", "2", bin_dir / "test_ops", "--backend", "host", "--op", "bcast", "--size", "64",
+             "--nonblocking"], env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    files = list(tmp_path.glob("*.trace.txt"))
+    assert len(files) == 2
+    text = files[0].read_text()
+    assert "HostBackend float nonblocking-bcast" in text and "PE START HostBcast" in text and "PE DONE HostBcast" in text
+
+
+def test_debug_checks_reject_bad_arguments(bin_dir):
+    code = ("import sys; sys.path.insert(0, %r); import numpy as np, aluminum_b200 as al; c = al.HostComm();\n"
+            "x = np.ones(4, dtype=np.float32)\n"
+            "try:\n    c.bcast(x, root=5)\n    print('no error')\nexcept al.AlError as e:\n    print('rejected')\n") % str(ROOT)
+    r = run([sys.executable, "-c", code], env={"AL_DEBUG": "1"})
+    assert "rejected" in r.stdout, r.stdout + r.stderr

@@ -1,0 +1,281 @@
+// benchmark_ops - times one operation of one backend over a sweep of message sizes.
+//
+//   alrun -n 8 benchmark_ops --backend device|nccl|host|ht --op allreduce --datatype float
+//         [--algo auto|one_shot|two_shot|nvls] [--inplace] [--nonblocking] [--symmetric]
+//         [--min-bytes 8 --max-bytes 1073741824] [--num-warmup 20] [--num-iters 100]
+//         [--reduction-op sum] [--out FILE] [--summarize]
+//
+// Protocol (that of the reference's benchmark/benchmark_ops.cpp:184-195 and
+// benchmark_utils_nccl.hpp:46-58): a host barrier before every iteration, a
+// cudaEvent pair on the communicator's stream around the operation (+ Wait for
+// non-blocking), event synchronise.  Every iteration's time is reduced with max
+// over ranks (a multi-GPU time is the slowest rank's time); rank 0 reports
+// median / mean / min / max per size together with the bus bandwidth
+// (allreduce S/t*2(p-1)/p, reduce_scatter / allgather / alltoall S/t*(p-1)/p with S the
+// full buffer).  `--backend nccl` runs the reference backend's NCCL call sequence.
+//
+// Output columns follow the reference's schema (benchmark/benchmark_utils.hpp:155-181)
+// with the statistics appended:
+//   Backend Type Operation Algo NonBlocking InPlace Root CommSize Bytes Median_us Mean_us Min_us Max_us BusGBs
+#include <algorithm>
+#include <fstream>
+#include <numeric>
+
+#include "../baseline/nccl_equiv.hpp"
+#include "../cpp_tests/test_common.hpp"
+
+using namespace altest;
+using Al::ReductionOperator;
+
+namespace {
+
+struct Stats { double median, mean, min, max; };
+Stats summarize(std::vector<double> v) {
+  std::sort(v.begin(), v.end());
+  Stats s;
+  s.median = v.empty() ? 0 : v[v.size() / 2];
+  s.mean = v.empty() ? 0 : std::accumulate(v.begin(), v.end(), 0.0) / (double)v.size();
+  s.min = v.empty() ? 0 : v.front();
+  s.max = v.empty() ? 0 : v.back();
+  return s;
+}
+
+double bus_factor(const std::string& op, int p) {
+  if (op == "allreduce") return 2.0 * (p - 1) / p;
+  if (op == "reduce_scatter" || op == "allgather" || op == "alltoall") return (double)(p - 1) / p;
+  return 1.0;
+}
+
+struct Timer {
+  cudaEvent_t a, b;
+  Timer() { cudaEventCreate(&a); cudaEventCreate(&b); }
+  ~Timer() { cudaEventDestroy(a); cudaEventDestroy(b); }
+};
+
+int nccl_dtype(Al::DType d) {
+  switch (d) {
+    case Al::DType::f32: return nccl_equiv::Float32;
+    case Al::DType::bf16: return nccl_equiv::Bfloat16;
+    case Al::DType::f16: return nccl_equiv::Float16;
+    case Al::DType::f64: return nccl_equiv::Float64;
+    case Al::DType::i32: return nccl_equiv::Int32;
+    default: return nccl_equiv::Uint8;
+  }
+}
+int nccl_op(ReductionOperator op) {
+  switch (op) {
+    case ReductionOperator::prod: return nccl_equiv::Prod;
+    case ReductionOperator::min: return nccl_equiv::Min;
+    case ReductionOperator::max: return nccl_equiv::Max;
+    case ReductionOperator::avg: return nccl_equiv::Avg;
+    default: return nccl_equiv::Sum;
+  }
+}
+
+template <typename T>
+void fill_device(T* p, size_t n, int rank) {
+  std::minstd_rand rng((unsigned)rank + 1);
+  std::vector<T> h(std::min<size_t>(n, 1 << 20));
+  for (auto& v : h) v = from_double<T>(((double)(rng() % 20001) - 10000.0) / 10000.0);  // U(-1, 1)
+  for (size_t off = 0; off < n; off += h.size())
+    cudaMemcpy(p + off, h.data(), std::min(h.size(), n - off) * sizeof(T), cudaMemcpyHostToDevice);
+}
+
+/** One benchmark run for element type T on GPU buffers. */
+template <typename T>
+int run_gpu(const Args& a, const std::string& backend) {
+  const std::string op = a.str("op", "allreduce");
+  const ReductionOperator rop = parse_redop(a.str("reduction-op", "sum"));
+  const bool inplace = a.has("inplace"), nb = a.has("nonblocking"), symmetric = a.has("symmetric");
+  const long warm = a.num("num-warmup", 20), iters = a.num("num-iters", 100);
+  const size_t min_b = (size_t)a.num("min-bytes", 8), max_b = (size_t)a.num("max-bytes", 1 << 26);
+  const std::string algo_s = a.str("algo", "auto");
+  Al::DeviceAllreduceAlgo algo = Al::DeviceAllreduceAlgo::automatic;
+  if (algo_s == "one_shot") algo = Al::DeviceAllreduceAlgo::one_shot;
+  else if (algo_s == "two_shot") algo = Al::DeviceAllreduceAlgo::two_shot;
+  else if (algo_s == "nvls") algo = Al::DeviceAllreduceAlgo::nvls;
+
+  cudaStream_t stream;
+  AL_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  Al::HostCommunicator hcomm;  // host barrier + max-over-ranks of the timings
+  const int p = hcomm.size(), me = hcomm.rank();
+  std::unique_ptr<Al::DeviceCommunicator> dcomm;
+  std::unique_ptr<Al::HostTransferCommunicator> htcomm;
+  std::unique_ptr<nccl_equiv::Communicator> ncomm;
+  if (backend == "device") dcomm.reset(new Al::DeviceCommunicator(stream));
+  else if (backend == "ht") htcomm.reset(new Al::HostTransferCommunicator(stream));
+  else ncomm.reset(new nccl_equiv::Communicator(hcomm.group(), stream));
+
+  // S = bytes of the full buffer (the larger side of the operation)
+  const size_t max_elems = std::max<size_t>(1, max_b / sizeof(T));
+  T *sbuf = nullptr, *rbuf = nullptr;
+  const size_t alloc = (max_elems + (size_t)p) * sizeof(T);
+  if (symmetric && dcomm) {
+    sbuf = (T*)dcomm->symm_alloc(alloc);
+    rbuf = (T*)dcomm->symm_alloc(alloc);
+  } else {
+    AL_CHECK_CUDA(cudaMalloc((void**)&sbuf, alloc));
+    AL_CHECK_CUDA(cudaMalloc((void**)&rbuf, alloc));
+  }
+  fill_device(sbuf, max_elems, me);
+  AL_CHECK_CUDA(cudaMemset(rbuf, 0, alloc));
+
+  std::ofstream file;
+  if (me == 0 && a.has("out")) file.open(a.str("out", ""), std::ios::app);
+  std::ostream& os = file.is_open() ? (std::ostream&)file : (std::ostream&)std::cout;
+  if (me == 0 && !a.has("no-header"))
+    os << "Backend Type Operation Algo NonBlocking InPlace Root CommSize Bytes Median_us Mean_us Min_us Max_us BusGBs\n";
+
+  Timer tm;
+  HangWatchdog dog((double)a.num("hang-timeout", 120));
+  for (size_t bytes = std::max(min_b, sizeof(T)); bytes <= max_b; bytes *= 2) {
+    const size_t total = bytes / sizeof(T);                 // elements of the full buffer
+    const size_t per = std::max<size_t>(1, total / (size_t)p);  // per-rank slice for the scattered ops
+    const bool sliced = op == "reduce_scatter" || op == "allgather" || op == "alltoall";
+    if (sliced && total < (size_t)p) continue;
+    const T* s = inplace ? (const T*)rbuf : sbuf;
+    auto launch = [&](Al::DeviceBackend::req_type& req) {
+      if (dcomm) {
+        Al::DeviceCommunicator& c = *dcomm;
+        if (op == "allreduce") {
+          if (nb) inplace ? Al::NonblockingAllreduce<Al::DeviceBackend>(rbuf, total, rop, c, req, algo) : Al::NonblockingAllreduce<Al::DeviceBackend>(s, rbuf, total, rop, c, req, algo);
+          else inplace ? Al::Allreduce<Al::DeviceBackend>(rbuf, total, rop, c, algo) : Al::Allreduce<Al::DeviceBackend>(s, rbuf, total, rop, c, algo);
+        } else if (op == "reduce_scatter") {
+          inplace ? Al::Reduce_scatter<Al::DeviceBackend>(rbuf, per, rop, c) : Al::Reduce_scatter<Al::DeviceBackend>(s, rbuf, per, rop, c);
+        } else if (op == "allgather") {
+          inplace ? Al::Allgather<Al::DeviceBackend>(rbuf, per, c) : Al::Allgather<Al::DeviceBackend>(s, rbuf, per, c);
+        } else if (op == "alltoall") {
+          inplace ? Al::Alltoall<Al::DeviceBackend>(rbuf, per, c) : Al::Alltoall<Al::DeviceBackend>(s, rbuf, per, c);
+        } else if (op == "bcast") {
+          Al::Bcast<Al::DeviceBackend>(rbuf, total, 0, c);
+        } else if (op == "reduce") {
+          Al::Reduce<Al::DeviceBackend>(s, rbuf, total, rop, 0, c);
+        } else if (op == "sendrecv") {
+          Al::SendRecv<Al::DeviceBackend>(s, total, (me + 1) % p, rbuf, total, (me + p - 1) % p, c);
+        } else if (op == "barrier") {
+          Al::Barrier<Al::DeviceBackend>(c);
+        } else throw_al_exception("benchmark_ops: unsupported op ", op);
+      } else if (htcomm) {
+        Al::HostTransferCommunicator& c = *htcomm;
+        if (op == "allreduce") Al::Allreduce<Al::HostTransferBackend>(s, rbuf, total, rop, c);
+        else if (op == "allgather") Al::Allgather<Al::HostTransferBackend>(s, rbuf, per, c);
+        else if (op == "alltoall") Al::Alltoall<Al::HostTransferBackend>(s, rbuf, per, c);
+        else if (op == "reduce_scatter") Al::Reduce_scatter<Al::HostTransferBackend>(s, rbuf, per, rop, c);
+        else if (op == "bcast") Al::Bcast<Al::HostTransferBackend>(rbuf, total, 0, c);
+        else throw_al_exception("benchmark_ops: unsupported op ", op);
+      } else {
+        nccl_equiv::Communicator& c = *ncomm;
+        const int dt = nccl_dtype(Al::TypeMap<T>::value), o = nccl_op(rop);
+        if (op == "allreduce") c.allreduce(s, rbuf, total, dt, o);
+        else if (op == "reduce_scatter") c.reduce_scatter(s, rbuf, per, dt, o);
+        else if (op == "allgather") c.allgather(inplace ? rbuf + (size_t)me * per : s, rbuf, per, dt);
+        else if (op == "alltoall") {
+          if (inplace) {  // the reference copies the whole buffer to a temporary first (nccl_impl.hpp:1228-1234)
+            AL_CHECK_CUDA(cudaMemcpyAsync(sbuf, rbuf, per * (size_t)p * sizeof(T), cudaMemcpyDeviceToDevice, stream));
+            c.alltoall(sbuf, rbuf, per, dt, sizeof(T));
+          } else c.alltoall(s, rbuf, per, dt, sizeof(T));
+        } else if (op == "bcast") c.bcast(rbuf, total, dt, 0);
+        else if (op == "reduce") c.reduce(s, rbuf, total, dt, o, 0);
+        else if (op == "sendrecv") c.sendrecv(s, total, (me + 1) % p, rbuf, total, (me + p - 1) % p, dt);
+        else if (op == "barrier") {  // the reference's barrier is a 1-byte allreduce (nccl_impl.hpp:1080-1090)
+          c.allreduce(rbuf, rbuf, 1, nccl_equiv::Uint8, nccl_equiv::Sum);
+        } else throw_al_exception("benchmark_ops: unsupported op ", op);
+      }
+    };
+    std::vector<double> times;
+    dog.arm(op + " " + std::to_string(bytes) + " bytes");
+    for (long it = 0; it < warm + iters; ++it) {
+      Al::Barrier<Al::HostBackend>(hcomm);
+      Al::DeviceBackend::req_type req = nullptr;
+      AL_CHECK_CUDA(cudaEventRecord(tm.a, stream));
+      launch(req);
+      if (req) Al::Wait<Al::DeviceBackend>(req);
+      AL_CHECK_CUDA(cudaEventRecord(tm.b, stream));
+      AL_CHECK_CUDA(cudaEventSynchronize(tm.b));
+      float ms = 0;
+      AL_CHECK_CUDA(cudaEventElapsedTime(&ms, tm.a, tm.b));
+      if (it >= warm) times.push_back((double)ms * 1e3);
+    }
+    dog.disarm();
+    if (dcomm) dcomm->check_status();
+    // max over ranks, iteration by iteration
+    std::vector<double> worst(times.size());
+    Al::Allreduce<Al::HostBackend>((const double*)times.data(), worst.data(), times.size(), ReductionOperator::max, hcomm);
+    if (me == 0) {
+      const Stats st = summarize(worst);
+      const double gbs = st.median > 0 ? (double)bytes / (st.median * 1e-6) * bus_factor(op, p) / 1e9 : 0;
+      os << backend << ' ' << a.str("datatype", "float") << ' ' << op << ' ' << (dcomm ? algo_s : "-") << ' ' << nb << ' '
+         << inplace << " 0 " << p << ' ' << bytes << ' ' << st.median << ' ' << st.mean << ' ' << st.min << ' ' << st.max
+         << ' ' << gbs << std::endl;
+    }
+  }
+  AL_CHECK_CUDA(cudaStreamSynchronize(stream));
+  Al::Barrier<Al::HostBackend>(hcomm);
+  if (symmetric && dcomm) { dcomm->symm_free(sbuf); dcomm->symm_free(rbuf); }
+  else { cudaFree(sbuf); cudaFree(rbuf); }
+  dcomm.reset(); htcomm.reset(); ncomm.reset();
+  cudaStreamDestroy(stream);
+  return 0;
+}
+
+/** Host backend: steady-clock timing (benchmark/benchmark_utils_mpi.hpp:35-45 of the reference). */
+template <typename T>
+int run_host(const Args& a) {
+  const std::string op = a.str("op", "allreduce");
+  const ReductionOperator rop = parse_redop(a.str("reduction-op", "sum"));
+  const long warm = a.num("num-warmup", 10), iters = a.num("num-iters", 100);
+  const size_t min_b = (size_t)a.num("min-bytes", 8), max_b = (size_t)a.num("max-bytes", 1 << 22);
+  Al::HostCommunicator comm;
+  const int p = comm.size(), me = comm.rank();
+  std::vector<T> s(max_b / sizeof(T) + (size_t)p), r(max_b / sizeof(T) + (size_t)p);
+  for (size_t i = 0; i < s.size(); ++i) s[i] = from_double<T>((double)((i * 7 + (size_t)me) % 13) / 13.0);
+  if (me == 0 && !a.has("no-header"))
+    std::cout << "Backend Type Operation Algo NonBlocking InPlace Root CommSize Bytes Median_us Mean_us Min_us Max_us BusGBs\n";
+  for (size_t bytes = std::max(min_b, sizeof(T)); bytes <= max_b; bytes *= 2) {
+    const size_t total = bytes / sizeof(T), per = std::max<size_t>(1, total / (size_t)p);
+    std::vector<double> times;
+    for (long it = 0; it < warm + iters; ++it) {
+      Al::Barrier<Al::HostBackend>(comm);
+      const double t0 = Al::get_time();
+      if (op == "allreduce") Al::Allreduce<Al::HostBackend>((const T*)s.data(), r.data(), total, rop, comm);
+      else if (op == "allgather") Al::Allgather<Al::HostBackend>((const T*)s.data(), r.data(), per, comm);
+      else if (op == "alltoall") Al::Alltoall<Al::HostBackend>((const T*)s.data(), r.data(), per, comm);
+      else if (op == "reduce_scatter") Al::Reduce_scatter<Al::HostBackend>((const T*)s.data(), r.data(), per, rop, comm);
+      else if (op == "bcast") Al::Bcast<Al::HostBackend>(r.data(), total, 0, comm);
+      else throw_al_exception("benchmark_ops: unsupported op ", op);
+      if (it >= warm) times.push_back((Al::get_time() - t0) * 1e6);
+    }
+    std::vector<double> worst(times.size());
+    Al::Allreduce<Al::HostBackend>((const double*)times.data(), worst.data(), times.size(), ReductionOperator::max, comm);
+    if (me == 0) {
+      const Stats st = summarize(worst);
+      std::cout << "host " << a.str("datatype", "float") << ' ' << op << " - 0 0 0 " << p << ' ' << bytes << ' ' << st.median
+                << ' ' << st.mean << ' ' << st.min << ' ' << st.max << ' '
+                << (double)bytes / (st.median * 1e-6) * bus_factor(op, p) / 1e9 << std::endl;
+    }
+  }
+  return 0;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Args a(argc, argv);
+  try {
+    Al::Initialize(argc, argv);
+    const std::string b = a.str("backend", "device"), t = a.str("datatype", "float");
+    int rc;
+    if (b == "host") rc = t == "double" ? run_host<double>(a) : run_host<float>(a);
+    else if (t == "float") rc = run_gpu<float>(a, b);
+    else if (t == "bfloat16") rc = run_gpu<bf16_t>(a, b);
+    else if (t == "half") rc = run_gpu<half_t>(a, b);
+    else if (t == "double") rc = run_gpu<double>(a, b);
+    else if (t == "int") rc = run_gpu<int>(a, b);
+    else throw_al_exception("unsupported datatype ", t);
+    Al::Finalize();
+    return rc;
+  } catch (const std::exception& e) {
+    fprintf(stderr, "benchmark_ops: %s\n", e.what());
+    return 1;
+  }
+}

@@ -84,16 +84,24 @@ void fill_device(T* p, size_t n, int rank) {
 /** One benchmark run for element type T on GPU buffers. */
 template <typename T>
 int run_gpu(const Args& a, const std::string& backend) {
-  const std::string op = a.str("op", "allreduce");
   const ReductionOperator rop = parse_redop(a.str("reduction-op", "sum"));
   const bool inplace = a.has("inplace"), nb = a.has("nonblocking"), symmetric = a.has("symmetric");
   const long warm = a.num("num-warmup", 20), iters = a.num("num-iters", 100);
   const size_t min_b = (size_t)a.num("min-bytes", 8), max_b = (size_t)a.num("max-bytes", 1 << 26);
-  const std::string algo_s = a.str("algo", "auto");
-  Al::DeviceAllreduceAlgo algo = Al::DeviceAllreduceAlgo::automatic;
-  if (algo_s == "one_shot") algo = Al::DeviceAllreduceAlgo::one_shot;
-  else if (algo_s == "two_shot") algo = Al::DeviceAllreduceAlgo::two_shot;
-  else if (algo_s == "nvls") algo = Al::DeviceAllreduceAlgo::nvls;
+  auto split_list = [](const std::string& v) {
+    std::vector<std::string> out;
+    size_t i = 0;
+    while (i <= v.size()) {
+      size_t j = v.find(',', i);
+      if (j == std::string::npos) j = v.size();
+      if (j > i) out.push_back(v.substr(i, j - i));
+      i = j + 1;
+    }
+    return out;
+  };
+  const std::vector<std::string> ops = split_list(a.str("op", "allreduce"));
+  const std::vector<std::string> algos = split_list(a.str("algo", "auto"));
+  const std::vector<std::string> cta_caps = split_list(a.str("ctas", "0"));
 
   cudaStream_t stream;
   AL_CHECK_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
@@ -128,6 +136,19 @@ int run_gpu(const Args& a, const std::string& backend) {
 
   Timer tm;
   HangWatchdog dog((double)a.num("hang-timeout", 120));
+  const int default_cap = Al::tuning().max_ctas, default_cap_nvls = Al::tuning().max_ctas_nvls;
+  for (const std::string& op : ops)
+  for (const std::string& algo_name : (op == "allreduce" && dcomm ? algos : std::vector<std::string>{"auto"}))
+  for (const std::string& cap_s : cta_caps) {
+  const int cap = atoi(cap_s.c_str());
+  Al::tuning().max_ctas = cap > 0 ? cap : default_cap;
+  Al::tuning().max_ctas_nvls = cap > 0 ? cap : default_cap_nvls;
+  Al::DeviceAllreduceAlgo algo = Al::DeviceAllreduceAlgo::automatic;
+  if (algo_name == "one_shot") algo = Al::DeviceAllreduceAlgo::one_shot;
+  else if (algo_name == "two_shot") algo = Al::DeviceAllreduceAlgo::two_shot;
+  else if (algo_name == "nvls") algo = Al::DeviceAllreduceAlgo::nvls;
+  const std::string algo_s = algo_name + (cap > 0 ? "/c" + cap_s : "");
+  if (algo == Al::DeviceAllreduceAlgo::nvls && dcomm && !dcomm->has_multicast()) continue;
   for (size_t bytes = std::max(min_b, sizeof(T)); bytes <= max_b; bytes *= 2) {
     const size_t total = bytes / sizeof(T);                 // elements of the full buffer
     const size_t per = std::max<size_t>(1, total / (size_t)p);  // per-rank slice for the scattered ops
@@ -208,6 +229,7 @@ int run_gpu(const Args& a, const std::string& backend) {
          << inplace << " 0 " << p << ' ' << bytes << ' ' << st.median << ' ' << st.mean << ' ' << st.min << ' ' << st.max
          << ' ' << gbs << std::endl;
     }
+  }
   }
   AL_CHECK_CUDA(cudaStreamSynchronize(stream));
   Al::Barrier<Al::HostBackend>(hcomm);

@@ -68,20 +68,28 @@ __device__ __forceinline__ uint4 scale_pack(uint4 v, float s) {
   return x.u;
 }
 
-/** Reduce-and-replicate the 16-byte vectors [v_lo, v_hi) of the multicast range. */
+/**
+ * Reduce-and-replicate the 16-byte vectors [v_lo, v_hi) of the multicast range.
+ * Each thread keeps U switch reductions in flight before it stores, so that a
+ * modest number of CTAs covers the NVLink latency-bandwidth product.
+ */
 template <typename T, NvOp OP>
 __device__ __forceinline__ void reduce_vectors(const char* mc_in, char* mc_out, size_t v_lo, size_t v_hi,
                                                float scale) {
+  constexpr int U = 4;
   const size_t stride = (size_t)blockDim.x * gridDim.x;
   size_t v = v_lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; v + stride < v_hi; v += 2 * stride) {
-    uint4 a = MM<T, OP>::ld(mc_in + (v << 4));
-    uint4 b = MM<T, OP>::ld(mc_in + ((v + stride) << 4));
-    if (scale != 1.f) { a = scale_pack<T>(a, scale); b = scale_pack<T>(b, scale); }
-    mm_st(mc_out + (v << 4), a);
-    mm_st(mc_out + ((v + stride) << 4), b);
+  for (; v + (U - 1) * stride < v_hi; v += U * stride) {
+    uint4 a[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[u] = MM<T, OP>::ld(mc_in + ((v + u * stride) << 4));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (scale != 1.f) a[u] = scale_pack<T>(a[u], scale);
+      mm_st(mc_out + ((v + u * stride) << 4), a[u]);
+    }
   }
-  if (v < v_hi) {
+  for (; v < v_hi; v += stride) {
     uint4 a = MM<T, OP>::ld(mc_in + (v << 4));
     if (scale != 1.f) a = scale_pack<T>(a, scale);
     mm_st(mc_out + (v << 4), a);

@@ -92,8 +92,6 @@ void require_device() {
   if (!cuda::device_usable()) throw_al_exception("the device backend needs a CUDA device, none is usable in this process");
 }
 
-size_t max_of(const std::vector<size_t>& v) { return v.empty() ? 0 : *std::max_element(v.begin(), v.end()); }
-
 }  // namespace
 
 DeviceCommunicator::DeviceCommunicator() : DeviceCommunicator((cudaStream_t) nullptr) {}
@@ -334,17 +332,39 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
 // ---------------------------------------------------------------------------
 // point-to-point
 // ---------------------------------------------------------------------------
-void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items, cudaStream_t stream) {
+void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t stream) {
   Impl& I = *impl_;
   std::lock_guard<std::mutex> lock(I.mu);
   check_status();
-  if (items.empty()) return;
+  if (items_in.empty()) return;
   const size_t slot = I.ws.mbox_slot_bytes;
   // Transfers of the same (owner, peer, direction) must not share a launch:
   // their pieces are numbered consecutively and have to land in order.
-  std::vector<char> placed(items.size(), 0);
-  size_t remaining = items.size();
+  std::vector<char> placed(items_in.size(), 0);
+  size_t remaining = items_in.size();
   I.order_after_previous(stream);
+  // A buffer that is both sent and received by the same rank (in-place SendRecv /
+  // MultiSendRecv) is sent from a stream-ordered temporary copy, so that arriving
+  // data cannot overwrite bytes that have not left yet.
+  std::vector<P2PDesc> staged(items_in);
+  std::vector<void*> temps;
+  for (auto& s : staged) {
+    if (!s.is_send || s.bytes == 0) continue;
+    for (const auto& r : items_in) {
+      if (r.is_send || r.bytes == 0 || r.owner != s.owner) continue;
+      const char* sb = (const char*)s.sbuf;
+      const char* rb = (const char*)r.rbuf;
+      if (sb < rb + r.bytes && rb < sb + s.bytes) {
+        void* t = nullptr;
+        AL_CHECK_CUDA(cudaMallocAsync(&t, s.bytes, stream));
+        AL_CHECK_CUDA(cudaMemcpyAsync(t, s.sbuf, s.bytes, cudaMemcpyDeviceToDevice, stream));
+        s.sbuf = t;
+        temps.push_back(t);
+        break;
+      }
+    }
+  }
+  const std::vector<P2PDesc>& items = staged;
   while (remaining) {
     P2PParams P{};
     P.ws = I.ws;
@@ -383,6 +403,7 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items, cudaStream_t str
     I.stats.kernels++;
     launch_p2p(P, 512, I.nlocal > 1 ? 1 : 0, stream);
   }
+  for (void* t : temps) AL_CHECK_CUDA(cudaFreeAsync(t, stream));
 }
 
 // ---------------------------------------------------------------------------

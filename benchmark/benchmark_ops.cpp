@@ -136,13 +136,14 @@ int run_gpu(const Args& a, const std::string& backend) {
 
   Timer tm;
   HangWatchdog dog((double)a.num("hang-timeout", 120));
-  const int default_cap = Al::tuning().max_ctas, default_cap_nvls = Al::tuning().max_ctas_nvls;
+  const int default_cap = Al::tuning().max_ctas, default_cap_nvls = Al::tuning().max_ctas_nvls, default_cap_zc = Al::tuning().max_ctas_zero_copy;
   for (const std::string& op : ops)
   for (const std::string& algo_name : (op == "allreduce" && dcomm ? algos : std::vector<std::string>{"auto"}))
   for (const std::string& cap_s : cta_caps) {
   const int cap = atoi(cap_s.c_str());
   Al::tuning().max_ctas = cap > 0 ? cap : default_cap;
   Al::tuning().max_ctas_nvls = cap > 0 ? cap : default_cap_nvls;
+  Al::tuning().max_ctas_zero_copy = cap > 0 ? cap : default_cap_zc;
   Al::DeviceAllreduceAlgo algo = Al::DeviceAllreduceAlgo::automatic;
   if (algo_name == "one_shot") algo = Al::DeviceAllreduceAlgo::one_shot;
   else if (algo_name == "two_shot") algo = Al::DeviceAllreduceAlgo::two_shot;

@@ -38,9 +38,10 @@ struct Tuning {
   double dev_wait_timeout_ms = 20000.0;        ///< AL_DEV_WAIT_TIMEOUT_MS: bound of every device-side flag wait
   bool dev_enable_nvls = true;                 ///< AL_DEV_NVLS: bind staging to an NVLink multicast object when supported
   size_t ar_oneshot_max_bytes = size_t{256} << 10;   ///< AL_AR_ONESHOT_MAX: one-shot allreduce up to this size
-  size_t ar_nvls_min_bytes = size_t{512} << 10;      ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on
-  int max_ctas = 64;                           ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
-  int max_ctas_nvls = 32;                      ///< AL_MAX_CTAS_NVLS
+  size_t ar_nvls_min_bytes = 0;                      ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on (measured best at every size on 8 GPUs)
+  int max_ctas = 128;                          ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
+  int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
+  int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
   // ---- diagnostics ------------------------------------------------------------
   bool trace = false;                          ///< AL_TRACE: record every API call

@@ -1,5 +1,14 @@
-// The generic collective kernel: publish -> handshake -> pull/reduce, chunked
-// through the double-buffered staging area.  One template serves all nine
+// The generic collective kernel: push -> handshake -> local consume, chunked
+// through the double-buffered staging area.
+//
+// Every rank's staging half is divided into p slots of `cap_b` bytes, one per
+// source rank.  In the publish step a rank reads its contribution once from the
+// user's send buffer and STORES it into slot [me] of the destination rank's
+// staging half over NVLink (remote stores are posted and do not stall the
+// issuing threads the way remote loads do; measured on 8 GPUs, pulling with
+// loads reached a third of the pushed bandwidth).  After the epoch handshake a
+// rank finds everything it needs in its own memory and reduces / copies it to
+// the user's receive buffer with local loads.  One template serves all nine
 // collectives; Ti/Tw/To are the user-input, wire (staging) and user-output
 // element types and Red the reduction functor.  Pure data-movement collectives
 // instantiate it once with byte elements.
@@ -22,8 +31,11 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   const CountTable& T = P.tab[rank];
   const size_t half = ws.half_bytes;
   const size_t full_e = half / sizeof(Tw);
-  const size_t cap_b = (half / (size_t)p) / 256 * 256;
+  const size_t cap_b = (half / (size_t)p) / 256 * 256;           // one slot per source rank
   const size_t cap_e = cap_b / sizeof(Tw);
+  const size_t cap2_b = (half / 2 / (size_t)p) / 256 * 256;      // two-phase allreduce: two areas of p slots
+  const size_t cap2_e = cap2_b / sizeof(Tw);
+  const size_t area_b = half / 2 / 256 * 256;                    // byte offset of the second area
   constexpr size_t VEC = 16 / sizeof(Tw);  // split boundaries stay 16-byte aligned in staging
   const Ti* send = (const Ti*)P.send[rank];
   To* recv = (To*)P.recv[rank];
@@ -35,42 +47,77 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   for (uint64_t c = 0; c < G; ++c) {
     const int par = (int)((P.seq + c) & 1);
     char* mystage = ws.stage[rank] + (size_t)par * half;
+    char* all_stage[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) all_stage[r] = r < p ? ws.stage[r] + (size_t)par * half : nullptr;
     size_t lo, hi;
 
-    // ------------------------------ publish --------------------------------
+    // ------------------------------ publish (remote stores) ----------------
     switch (kind) {
-      case DevColl::allreduce:
+      case DevColl::allreduce: {
+        if (!P.two_phase) {  // every rank gets every rank's whole chunk
+          const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
+          split_range(len, cta, nct, VEC, lo, hi);
+          if (send && hi > lo)
+            cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+        } else {             // rank d gets slice d of every rank's chunk
+          const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
+          for (int d = 0; d < p; ++d) {
+            size_t s_lo, s_hi;
+            split_range(len, (unsigned)d, (unsigned)p, VEC, s_lo, s_hi);
+            split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
+            if (send && hi > lo)
+              cta_publish<Ti, Tw>(&all_stage[d], 1, (size_t)rank * cap2_b + lo * sizeof(Tw), send + base + s_lo + lo, hi - lo);
+          }
+        }
+        break;
+      }
       case DevColl::reduce: {
-        const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
+        const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
         split_range(len, cta, nct, VEC, lo, hi);
-        if (send && hi > lo) cta_convert<Ti, Tw>((Tw*)mystage + lo, send + base + lo, hi - lo);
+        if (send && hi > lo)
+          cta_publish<Ti, Tw>(&all_stage[root], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
       }
       case DevColl::bcast: {
         if (rank != root) break;
         const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
         split_range(len, cta, nct, VEC, lo, hi);
-        if (send && hi > lo) cta_convert<Ti, Tw>((Tw*)mystage + lo, send + base + lo, hi - lo);
+        if (send && hi > lo) cta_publish<Ti, Tw>(all_stage, p, lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
       }
       case DevColl::allgather:
       case DevColl::gather: {
-        const size_t base = c * full_e, len = clamp_len(T.send_counts[rank], base, full_e);
+        const size_t base = c * cap_e, len = clamp_len(T.send_counts[rank], base, cap_e);
         split_range(len, cta, nct, VEC, lo, hi);
-        if (send && hi > lo) cta_convert<Ti, Tw>((Tw*)mystage + lo, send + base + lo, hi - lo);
+        if (send && hi > lo) {
+          if (kind == DevColl::allgather)
+            cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+          else
+            cta_publish<Ti, Tw>(&all_stage[root], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+        }
         break;
       }
       case DevColl::reduce_scatter:
-      case DevColl::alltoall:
-      case DevColl::scatter: {
-        if (kind == DevColl::scatter && rank != root) break;
+      case DevColl::alltoall: {
         const size_t base = c * cap_e;
         for (int d = 0; d < p; ++d) {
           const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
           const size_t len = clamp_len(cnt, base, cap_e);
           split_range(len, cta, nct, VEC, lo, hi);
           if (send && hi > lo)
-            cta_convert<Ti, Tw>((Tw*)(mystage + (size_t)d * cap_b) + lo, send + T.send_displs[d] + base + lo, hi - lo);
+            cta_publish<Ti, Tw>(&all_stage[d], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo);
+        }
+        break;
+      }
+      case DevColl::scatter: {
+        if (rank != root) break;
+        const size_t base = c * full_e;
+        for (int d = 0; d < p; ++d) {
+          const size_t len = clamp_len(T.send_counts[d], base, full_e);
+          split_range(len, cta, nct, VEC, lo, hi);
+          if (send && hi > lo)
+            cta_publish<Ti, Tw>(&all_stage[d], 1, lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo);
         }
         break;
       }
@@ -94,39 +141,49 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       G = s_chunks;
     }
 
-    // ------------------------------ consume --------------------------------
-    char* stage_par[kMaxRanks];
+    // ------------------------------ consume (local loads) ------------------
+    char* slot[kMaxRanks];    // my slots, one per source rank
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r) stage_par[r] = r < p ? ws.stage[r] + (size_t)par * half : nullptr;
+    for (int r = 0; r < kMaxRanks; ++r) slot[r] = mystage + (size_t)r * cap_b;
 
     switch (kind) {
       case DevColl::allreduce: {
-        const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
         if (!P.two_phase) {
+          const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
           split_range(len, cta, nct, VEC, lo, hi);
-          if (recv && hi > lo)
-            cta_reduce<Tw, To, Red>(recv + base + lo, stage_par, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+          if (recv && hi > lo) {
+            To* out = recv + base + lo;
+            cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+          }
           break;
         }
-        // phase 1: reduce the slice this rank owns, in place in its own staging
+        const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
+        // phase 1: reduce the slice this rank owns and push the result to everyone's second area
+        char* slot2[kMaxRanks];
+        Tw* outs[kMaxRanks];
         size_t s_lo, s_hi;
         split_range(len, (unsigned)rank, (unsigned)p, VEC, s_lo, s_hi);
         split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          slot2[r] = mystage + (size_t)r * cap2_b;
+          outs[r] = r < p ? (Tw*)(all_stage[r] + area_b + (size_t)rank * cap2_b) + lo : nullptr;
+        }
         if (hi > lo)
-          cta_reduce<Tw, Tw, Red>((Tw*)mystage + s_lo + lo, stage_par, (s_lo + lo) * sizeof(Tw), p, hi - lo, red,
-                                  P.scale, P.int_div);
+          cta_reduce<Tw, Tw, Red>(outs, p, slot2, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
         arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
         if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
-        // phase 2: collect every owner's slice
+        // phase 2: every owner's reduced slice is now in my second area
         for (int s = 0; s < p; ++s) {
           split_range(len, (unsigned)s, (unsigned)p, VEC, s_lo, s_hi);
           split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
           if (recv && hi > lo) {
+            char* src = mystage + area_b + (size_t)s * cap2_b;
             if constexpr (std::is_same<Tw, To>::value) {
-              cta_copy((char*)(recv + base + s_lo + lo), stage_par[s] + (s_lo + lo) * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
+              cta_copy((char*)(recv + base + s_lo + lo), src + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
             } else {
-              char* one[kMaxRanks] = {stage_par[s]};
-              cta_reduce<Tw, To, RedNone>(recv + base + s_lo + lo, one, (s_lo + lo) * sizeof(Tw), 1, hi - lo, RedNone(), 1.0, 1);
+              To* out = recv + base + s_lo + lo;
+              cta_reduce<Tw, To, RedNone>(&out, 1, &src, lo * sizeof(Tw), 1, hi - lo, RedNone(), 1.0, 1);
             }
           }
         }
@@ -134,43 +191,34 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       }
       case DevColl::reduce: {
         if (rank != root) break;
-        const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
+        const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
         split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo)
-          cta_reduce<Tw, To, Red>(recv + base + lo, stage_par, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+        if (recv && hi > lo) {
+          To* out = recv + base + lo;
+          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+        }
         break;
       }
       case DevColl::reduce_scatter: {
         const size_t base = c * cap_e, len = clamp_len(T.recv_counts[rank], base, cap_e);
         split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo)
-          cta_reduce<Tw, To, Red>(recv + base + lo, stage_par, (size_t)rank * cap_b + lo * sizeof(Tw), p, hi - lo, red,
-                                  P.scale, P.int_div);
-        break;
-      }
-      case DevColl::allgather:
-      case DevColl::gather: {
-        if (kind == DevColl::gather && rank != root) break;
-        const size_t base = c * full_e;
-        for (int r = 0; r < p; ++r) {
-          const size_t len = clamp_len(T.recv_counts[r], base, full_e);
-          split_range(len, cta, nct, VEC, lo, hi);
-          if (recv && hi > lo) {
-            if constexpr (std::is_same<Tw, To>::value)
-              cta_copy((char*)(recv + T.recv_displs[r] + base + lo), stage_par[r] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
-          }
+        if (recv && hi > lo) {
+          To* out = recv + base + lo;
+          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
         }
         break;
       }
+      case DevColl::allgather:
+      case DevColl::gather:
       case DevColl::alltoall: {
+        if (kind == DevColl::gather && rank != root) break;
         const size_t base = c * cap_e;
         for (int r = 0; r < p; ++r) {
           const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
           split_range(len, cta, nct, VEC, lo, hi);
           if (recv && hi > lo) {
             if constexpr (std::is_same<Tw, To>::value)
-              cta_copy((char*)(recv + T.recv_displs[r] + base + lo), stage_par[r] + (size_t)rank * cap_b + lo * sizeof(Tw),
-                       (hi - lo) * sizeof(Tw), true);
+              cta_copy((char*)(recv + T.recv_displs[r] + base + lo), slot[r] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
           }
         }
         break;
@@ -181,17 +229,16 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
         split_range(len, cta, nct, VEC, lo, hi);
         if (recv && hi > lo) {
           if constexpr (std::is_same<Tw, To>::value)
-            cta_copy((char*)(recv + base + lo), stage_par[root] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
+            cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
         }
         break;
       }
       case DevColl::scatter: {
-        const size_t base = c * cap_e, len = clamp_len(T.recv_counts[rank], base, cap_e);
+        const size_t base = c * full_e, len = clamp_len(T.recv_counts[rank], base, full_e);
         split_range(len, cta, nct, VEC, lo, hi);
         if (recv && hi > lo) {
           if constexpr (std::is_same<Tw, To>::value)
-            cta_copy((char*)(recv + base + lo), stage_par[root] + (size_t)rank * cap_b + lo * sizeof(Tw),
-                     (hi - lo) * sizeof(Tw), true);
+            cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
         }
         break;
       }
@@ -200,8 +247,8 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   }
 
   if (G > 1) {
-    // Both halves were used: make sure every peer is done reading before the
-    // next launch (which may start on either half) overwrites them.
+    // Both halves were used: make sure every peer is done with them before the
+    // next launch (which may start on either half) writes into them.
     const uint64_t e = make_epoch(P.seq, 1);
     arrive_and_post(ws, rank, FlagLayout::off_C, 2, e, false, 0, 0);
     (void)wait_all(ws, rank, FlagLayout::off_C, 2, e, P.timeout_ns);

@@ -139,6 +139,79 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t nbyt
   }
 }
 
+// ---------------------------------------------------------------------------
+// publish: one local source, several (possibly remote) destinations
+// ---------------------------------------------------------------------------
+template <typename V>
+__device__ __forceinline__ void fanout_units(char* const* dsts, int ndst, size_t dst_off, const char* src, size_t units) {
+  const V* s = (const V*)src;
+  const size_t stride = blockDim.x;
+  size_t i = threadIdx.x;
+  for (; i + 3 * stride < units; i += 4 * stride) {
+    const V a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
+#pragma unroll
+    for (int d = 0; d < kMaxRanks; ++d) {
+      if (d < ndst) {
+        V* o = (V*)(dsts[d] + dst_off);
+        o[i] = a; o[i + stride] = b; o[i + 2 * stride] = c; o[i + 3 * stride] = e;
+      }
+    }
+  }
+  for (; i < units; i += stride) {
+    const V a = s[i];
+#pragma unroll
+    for (int d = 0; d < kMaxRanks; ++d)
+      if (d < ndst) ((V*)(dsts[d] + dst_off))[i] = a;
+  }
+}
+
+/**
+ * Store `nbytes` read once from local `src` at byte offset `dst_off` of each of
+ * `ndst` staging bases (peer-mapped memory: plain stores over NVLink, which do
+ * not stall the issuing thread the way remote loads do).
+ */
+__device__ __forceinline__ void cta_fanout(char* const* dsts, int ndst, size_t dst_off, const char* src, size_t nbytes) {
+  if (nbytes == 0 || ndst == 0) return;
+  const uintptr_t mis = (uintptr_t)src | (uintptr_t)dst_off;  // staging bases are 256-byte aligned
+  if ((mis & 15) == 0) {
+    const size_t nv = nbytes >> 4;
+    fanout_units<uint4>(dsts, ndst, dst_off, src, nv);
+    const size_t done = nv << 4;
+    if (threadIdx.x < (nbytes - done))
+      for (int d = 0; d < ndst; ++d) dsts[d][dst_off + done + threadIdx.x] = src[done + threadIdx.x];
+  } else if ((mis & 3) == 0) {
+    const size_t nv = nbytes >> 2;
+    fanout_units<uint32_t>(dsts, ndst, dst_off, src, nv);
+    const size_t done = nv << 2;
+    if (threadIdx.x < (nbytes - done))
+      for (int d = 0; d < ndst; ++d) dsts[d][dst_off + done + threadIdx.x] = src[done + threadIdx.x];
+  } else if ((mis & 1) == 0) {
+    const size_t nv = nbytes >> 1;
+    fanout_units<uint16_t>(dsts, ndst, dst_off, src, nv);
+    if ((nbytes & 1) && threadIdx.x == 0)
+      for (int d = 0; d < ndst; ++d) dsts[d][dst_off + nbytes - 1] = src[nbytes - 1];
+  } else {
+    fanout_units<uint8_t>(dsts, ndst, dst_off, src, nbytes);
+  }
+}
+
+/** Publish n elements of user type Ti as wire type Tw into every destination (cast fused in). */
+template <typename Ti, typename Tw>
+__device__ __forceinline__ void cta_publish(char* const* dsts, int ndst, size_t dst_off, const Ti* src, size_t n) {
+  if constexpr (std::is_same<Ti, Tw>::value) {
+    cta_fanout(dsts, ndst, dst_off, (const char*)src, n * sizeof(Ti));
+  } else {
+    using Ai = typename Elem<Ti>::Acc;
+    using Aw = typename Elem<Tw>::Acc;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+      const Tw v = Elem<Tw>::down(acc_cast<Aw, Ai>(Elem<Ti>::up(src[i])));
+#pragma unroll
+      for (int d = 0; d < kMaxRanks; ++d)
+        if (d < ndst) ((Tw*)(dsts[d] + dst_off))[i] = v;
+    }
+  }
+}
+
 /** dst[i] = (Tw)src[i] for i in [0, n): the publish step of an operation whose wire type differs. */
 template <typename Ti, typename Tw>
 __device__ __forceinline__ void cta_convert(Tw* dst, const Ti* src, size_t n) {
@@ -165,22 +238,43 @@ __device__ __forceinline__ A finish_acc(A a, double scale, int int_div) {
 }
 
 /**
- * dst[i] = finish(red(src_0[i], src_1[i], ..., src_{p-1}[i])) for i in [0, n),
- * where src_r = (const Tw*)(bases[r] + byte_off).  Sources are staging memory
+ * out[i] = finish(red(src_0[i], src_1[i], ..., src_{p-1}[i])) for i in [0, n),
+ * where src_r = (const Tw*)(bases[r] + byte_off), written to each of the `ndst`
+ * destinations dsts[d] (all holding To elements; several destinations are used
+ * when a reduced slice is pushed to every peer).  Sources are staging memory
  * (16-byte aligned); contributions are folded in rank order so every rank
- * computes bit-identical results.  `dst` may alias one of the sources.
+ * computes bit-identical results.  A destination may alias one of the sources.
  */
 template <typename Tw, typename To, typename Red>
-__device__ __forceinline__ void cta_reduce(To* dst, char* const* bases, size_t byte_off, int p, size_t n,
-                                           Red red, double scale, int int_div) {
+__device__ __forceinline__ void cta_reduce(To* const* dsts, int ndst, char* const* bases, size_t byte_off, int p,
+                                           size_t n, Red red, double scale, int int_div) {
   using Aw = typename Elem<Tw>::Acc;
   using Ao = typename Elem<To>::Acc;
   constexpr int VEC = 16 / (int)sizeof(Tw);
   constexpr size_t out_bytes = (size_t)VEC * sizeof(To);
   constexpr size_t out_align = out_bytes < 16 ? out_bytes : 16;
-  const size_t nvec = ((uintptr_t)dst % out_align == 0) ? n / VEC : 0;
+  bool aligned = true;
+  for (int d = 0; d < ndst; ++d) aligned = aligned && ((uintptr_t)dsts[d] % out_align == 0);
+  const size_t nvec = aligned ? n / VEC : 0;
   union InPack { uint4 u; Tw e[VEC]; };
   union OutPack { uint4 u[(out_bytes + 15) / 16]; To e[VEC]; };
+
+  auto store = [&](size_t v, const OutPack& o) {
+#pragma unroll
+    for (int d = 0; d < kMaxRanks; ++d) {
+      if (d < ndst) {
+        To* dst = dsts[d];
+        if constexpr (out_bytes >= 16) {
+#pragma unroll
+          for (int q = 0; q < (int)(out_bytes / 16); ++q) ((uint4*)dst)[v * (out_bytes / 16) + q] = o.u[q];
+        } else if constexpr (out_bytes == 8) {
+          ((uint2*)dst)[v] = *(const uint2*)&o.u[0];
+        } else {
+          ((uint32_t*)dst)[v] = *(const uint32_t*)&o.u[0];
+        }
+      }
+    }
+  };
 
   for (size_t v = threadIdx.x; v < nvec; v += 2 * (size_t)blockDim.x) {
     const size_t v2 = v + blockDim.x;
@@ -207,28 +301,14 @@ __device__ __forceinline__ void cta_reduce(To* dst, char* const* bases, size_t b
     OutPack o;
 #pragma unroll
     for (int k = 0; k < VEC; ++k) o.e[k] = Elem<To>::down(acc_cast<Ao, Aw>(finish_acc(acc0[k], scale, int_div)));
-    if constexpr (out_bytes >= 16) {
-#pragma unroll
-      for (int q = 0; q < (int)(out_bytes / 16); ++q) ((uint4*)dst)[v * (out_bytes / 16) + q] = o.u[q];
-    } else if constexpr (out_bytes == 8) {
-      ((uint2*)dst)[v] = *(uint2*)&o.u[0];
-    } else {
-      ((uint32_t*)dst)[v] = *(uint32_t*)&o.u[0];
-    }
+    store(v, o);
     if (has2) {
 #pragma unroll
       for (int k = 0; k < VEC; ++k) o.e[k] = Elem<To>::down(acc_cast<Ao, Aw>(finish_acc(acc1[k], scale, int_div)));
-      if constexpr (out_bytes >= 16) {
-#pragma unroll
-        for (int q = 0; q < (int)(out_bytes / 16); ++q) ((uint4*)dst)[v2 * (out_bytes / 16) + q] = o.u[q];
-      } else if constexpr (out_bytes == 8) {
-        ((uint2*)dst)[v2] = *(uint2*)&o.u[0];
-      } else {
-        ((uint32_t*)dst)[v2] = *(uint32_t*)&o.u[0];
-      }
+      store(v2, o);
     }
   }
-  // scalar remainder (and the whole range when dst is not aligned for vector stores)
+  // scalar remainder (and the whole range when a destination is not aligned for vector stores)
   for (size_t i = nvec * VEC + threadIdx.x; i < n; i += blockDim.x) {
     Aw acc = Aw();
 #pragma unroll
@@ -238,7 +318,8 @@ __device__ __forceinline__ void cta_reduce(To* dst, char* const* bases, size_t b
         acc = r == 0 ? x : red(acc, x);
       }
     }
-    dst[i] = Elem<To>::down(acc_cast<Ao, Aw>(finish_acc(acc, scale, int_div)));
+    const To out = Elem<To>::down(acc_cast<Ao, Aw>(finish_acc(acc, scale, int_div)));
+    for (int d = 0; d < ndst; ++d) dsts[d][i] = out;
   }
 }
 

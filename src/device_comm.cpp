@@ -215,8 +215,37 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   const size_t esz = dtype_size(wire);
   const size_t half = I.ws.half_bytes;
   const size_t full_e = half / esz;
-  const size_t cap_e = ((half / (size_t)p) / 256 * 256) / esz;
+  const size_t cap_e = ((half / (size_t)p) / 256 * 256) / esz;           // one slot per source rank
+  const size_t cap2_e = ((half / 2 / (size_t)p) / 256 * 256) / esz;      // two-phase allreduce
   size_t max_work_bytes = 0;
+
+  // ---- algorithm -----------------------------------------------------------------
+  const Tuning& tn = tuning();
+  const size_t bytes = P.count * esz;
+  AllreduceAlgo algo = d.algo;
+  bool zero_copy = false;
+  const SymmBlock* sb_in = nullptr;
+  const SymmBlock* sb_out = nullptr;
+  size_t off_in = 0, off_out = 0;
+  if (d.kind == DevColl::allreduce) {
+    const bool nvls_ok = !I.emulated && p > 1 && I.ws.mc_stage != nullptr && in == wire && wire == out &&
+                         nvls_allreduce_supported(wire, d.op);
+    if (algo == AllreduceAlgo::nvls && !nvls_ok)
+      throw_al_exception("NVLS allreduce requested but unavailable (no multicast, or type/operator unsupported)");
+    if (nvls_ok && (algo == AllreduceAlgo::automatic || algo == AllreduceAlgo::nvls)) {
+      const RankArgs& a = ranks[0];
+      sb_in = find_symm(a.send, bytes, &off_in);
+      sb_out = find_symm(a.recv, bytes, &off_out);
+      zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0);
+    }
+    if (algo == AllreduceAlgo::automatic) {
+      if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
+      else if (bytes <= tn.ar_oneshot_max_bytes || p == 1) algo = AllreduceAlgo::one_shot;
+      else algo = AllreduceAlgo::two_shot;
+    }
+    P.two_phase = algo == AllreduceAlgo::two_shot ? 1 : 0;
+  }
+
 
   for (int lr = 0; lr < I.nlocal; ++lr) {
     const int r = I.rank0 + lr;
@@ -243,18 +272,22 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     size_t need = 0, chunk_unit = full_e, work = 0;
     auto mx = [&](const size_t* v) { size_t m = 0; for (int i = 0; i < p; ++i) m = std::max(m, v[i]); return m; };
     switch (d.kind) {
-      case DevColl::allreduce: case DevColl::reduce: case DevColl::bcast:
-        need = P.count; chunk_unit = full_e; work = P.count; break;
+      case DevColl::allreduce:
+        need = P.count; work = P.count;
+        chunk_unit = algo == AllreduceAlgo::nvls ? full_e : (algo == AllreduceAlgo::two_shot ? (size_t)p * cap2_e : cap_e);
+        break;
+      case DevColl::reduce: need = P.count; chunk_unit = cap_e; work = P.count; break;
+      case DevColl::bcast: need = P.count; chunk_unit = full_e; work = P.count; break;
       case DevColl::reduce_scatter: need = mx(T.recv_counts); chunk_unit = cap_e; work = need * (size_t)p; break;
-      case DevColl::allgather: need = mx(T.recv_counts); chunk_unit = full_e; work = need * (size_t)p; break;
+      case DevColl::allgather: need = mx(T.recv_counts); chunk_unit = cap_e; work = need * (size_t)p; break;
       case DevColl::alltoall:
         need = std::max(mx(T.send_counts), mx(T.recv_counts)); chunk_unit = cap_e; work = need * (size_t)p; break;
       case DevColl::gather:
         need = r == d.root ? mx(T.recv_counts) : T.send_counts[r];
-        chunk_unit = full_e; work = r == d.root ? need * (size_t)p : need; break;
+        chunk_unit = cap_e; work = r == d.root ? need * (size_t)p : need; break;
       case DevColl::scatter:
         need = r == d.root ? mx(T.send_counts) : T.recv_counts[r];
-        chunk_unit = cap_e; work = r == d.root ? need * (size_t)p : need; break;
+        chunk_unit = full_e; work = r == d.root ? need * (size_t)p : need; break;
       case DevColl::barrier: need = 0; break;
     }
     P.local_chunks[r] = std::max<uint64_t>(1, ceil_div(need, chunk_unit));
@@ -262,37 +295,11 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     max_work_bytes = std::max(max_work_bytes, std::min(work * esz, half));
   }
 
-  // ---- algorithm -----------------------------------------------------------------
-  const Tuning& tn = tuning();
-  const size_t bytes = P.count * esz;
-  AllreduceAlgo algo = d.algo;
-  bool zero_copy = false;
-  const SymmBlock* sb_in = nullptr;
-  const SymmBlock* sb_out = nullptr;
-  size_t off_in = 0, off_out = 0;
-  if (d.kind == DevColl::allreduce) {
-    const bool nvls_ok = !I.emulated && p > 1 && I.ws.mc_stage != nullptr && in == wire && wire == out &&
-                         nvls_allreduce_supported(wire, d.op);
-    if (algo == AllreduceAlgo::nvls && !nvls_ok)
-      throw_al_exception("NVLS allreduce requested but unavailable (no multicast, or type/operator unsupported)");
-    if (nvls_ok && (algo == AllreduceAlgo::automatic || algo == AllreduceAlgo::nvls)) {
-      const RankArgs& a = ranks[0];
-      sb_in = find_symm(a.send, bytes, &off_in);
-      sb_out = find_symm(a.recv, bytes, &off_out);
-      zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0);
-    }
-    if (algo == AllreduceAlgo::automatic) {
-      if (nvls_ok && (bytes >= tn.ar_nvls_min_bytes || (zero_copy && bytes >= 65536))) algo = AllreduceAlgo::nvls;
-      else if (bytes <= tn.ar_oneshot_max_bytes || p == 1) algo = AllreduceAlgo::one_shot;
-      else algo = AllreduceAlgo::two_shot;
-    }
-    P.two_phase = algo == AllreduceAlgo::two_shot ? 1 : 0;
-  }
-
   // ---- grid ------------------------------------------------------------------------
   int threads = std::min(512, tn.threads_per_cta);
   int ctas = d.ctas > 0 ? d.ctas : (int)std::max<size_t>(1, ceil_div(max_work_bytes, (size_t)32768));
-  int cap = (d.kind == DevColl::allreduce && algo == AllreduceAlgo::nvls) ? tn.max_ctas_nvls : tn.max_ctas;
+  int cap = tn.max_ctas;
+  if (d.kind == DevColl::allreduce && algo == AllreduceAlgo::nvls) cap = zero_copy ? tn.max_ctas_zero_copy : tn.max_ctas_nvls;
   if (I.nlocal > 1) cap = std::min(cap, std::max(1, I.sm_count / I.nlocal));  // cooperative launch must be co-resident
   ctas = std::max(1, std::min(ctas, cap));
   if (max_work_bytes <= 4096) threads = std::min(threads, 256);

@@ -32,6 +32,7 @@ void Tuning::load_from_env() {
   ar_nvls_min_bytes = (size_t)env_long("AL_AR_NVLS_MIN", (long)ar_nvls_min_bytes);
   max_ctas = (int)env_long("AL_MAX_CTAS_PER_OP", max_ctas);
   max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
+  max_ctas_zero_copy = (int)env_long("AL_MAX_CTAS_ZERO_COPY", max_ctas_zero_copy);
   threads_per_cta = (int)env_long("AL_THREADS_PER_CTA", threads_per_cta);
   trace = env_long("AL_TRACE", trace) != 0;
   debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
@@ -40,6 +41,8 @@ void Tuning::load_from_env() {
   if (max_ctas > AL_MAX_CTAS) max_ctas = AL_MAX_CTAS;
   if (max_ctas_nvls < 1) max_ctas_nvls = 1;
   if (max_ctas_nvls > AL_MAX_CTAS) max_ctas_nvls = AL_MAX_CTAS;
+  if (max_ctas_zero_copy < 1) max_ctas_zero_copy = 1;
+  if (max_ctas_zero_copy > AL_MAX_CTAS) max_ctas_zero_copy = AL_MAX_CTAS;
   if (threads_per_cta < 64) threads_per_cta = 64;
   if (threads_per_cta > 1024) threads_per_cta = 1024;
   threads_per_cta = threads_per_cta / 32 * 32;
@@ -74,6 +77,7 @@ std::string Tuning::describe() const {
      << "ar_nvls_min_bytes = " << ar_nvls_min_bytes << "\n"
      << "max_ctas = " << max_ctas << "\n"
      << "max_ctas_nvls = " << max_ctas_nvls << "\n"
+     << "max_ctas_zero_copy = " << max_ctas_zero_copy << "\n"
      << "threads_per_cta = " << threads_per_cta << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"

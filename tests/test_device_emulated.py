@@ -314,6 +314,21 @@ def test_p2p_sendrecv_ring(comm):
     assert comm.status()["code"] == 0
 
 
+def test_p2p_in_place_exchange(comm):
+    """The same buffer is sent and then overwritten by what arrives (in-place SendRecv)."""
+    p, n = comm.size, 50001
+    bufs = [rand(n, torch.float32, 170 + r) for r in range(p)]
+    snap = [b.clone() for b in bufs]
+    items = []
+    for r in range(p):
+        items.append((True, (r + 1) % p, bufs[r], r))
+        items.append((False, (r - 1) % p, bufs[r], r))
+    comm.p2p(items)
+    torch.cuda.synchronize()
+    for r in range(p):
+        assert torch.equal(bufs[r], snap[(r - 1) % p])
+
+
 def test_unaligned_buffers(comm):
     p, n = comm.size, 1001
     bases = [rand(n + 3, torch.float32, 160 + r) for r in range(p)]

@@ -119,6 +119,8 @@ struct CollParams {
   int root;
   int rank0;
   int two_phase;                 ///< allreduce: 1 = reduce-scatter + allgather, 0 = every rank reduces everything
+  int pipelined;                 ///< 1: half of the CTAs publish while the other half consumes (large uniform ops)
+  size_t slot_elems;             ///< elements moved per slot and chunk (0 = the slot's capacity)
 };
 
 /** Arguments of one point-to-point launch (any mix of sends and receives). */

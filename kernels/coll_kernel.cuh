@@ -24,7 +24,6 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   const Workspace& ws = P.ws;
   const int p = ws.p;
   const int rank = P.rank0 + (int)blockIdx.y;
-  const unsigned cta = blockIdx.x, nct = gridDim.x;
   if (poisoned(ws, rank)) return;
 
   const DevColl kind = (DevColl)P.kind;
@@ -32,7 +31,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   const size_t half = ws.half_bytes;
   const size_t full_e = half / sizeof(Tw);
   const size_t cap_b = (half / (size_t)p) / 256 * 256;           // one slot per source rank
-  const size_t cap_e = cap_b / sizeof(Tw);
+  const size_t cap_e = P.slot_elems ? P.slot_elems : cap_b / sizeof(Tw);  // elements moved per slot and chunk
   const size_t cap2_b = (half / 2 / (size_t)p) / 256 * 256;      // two-phase allreduce: two areas of p slots
   const size_t cap2_e = cap2_b / sizeof(Tw);
   const size_t area_b = half / 2 / 256 * 256;                    // byte offset of the second area
@@ -40,24 +39,24 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   const Ti* send = (const Ti*)P.send[rank];
   To* recv = (To*)P.recv[rank];
   const int root = P.root;
+  // Small single-CTA messages: the CTA's threads split into p groups that serve all peers at once
+  // instead of one peer after the other.
+  const unsigned grp_lanes = blockDim.x / (unsigned)p;
+  const unsigned grp = threadIdx.x / grp_lanes, lane = threadIdx.x % grp_lanes;
+  constexpr size_t kSmallBytes = 8192;
 
-  __shared__ uint64_t s_chunks;
-  uint64_t G = P.local_chunks[rank];
-
-  for (uint64_t c = 0; c < G; ++c) {
+  // ------------------------------ publish (remote stores) --------------------
+  auto publish = [&](uint64_t c, unsigned part, unsigned nparts) {
     const int par = (int)((P.seq + c) & 1);
-    char* mystage = ws.stage[rank] + (size_t)par * half;
     char* all_stage[kMaxRanks];
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r) all_stage[r] = r < p ? ws.stage[r] + (size_t)par * half : nullptr;
     size_t lo, hi;
-
-    // ------------------------------ publish (remote stores) ----------------
     switch (kind) {
       case DevColl::allreduce: {
         if (!P.two_phase) {  // every rank gets every rank's whole chunk
           const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
-          split_range(len, cta, nct, VEC, lo, hi);
+          split_range(len, part, nparts, VEC, lo, hi);
           if (send && hi > lo)
             cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         } else {             // rank d gets slice d of every rank's chunk
@@ -65,7 +64,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           for (int d = 0; d < p; ++d) {
             size_t s_lo, s_hi;
             split_range(len, (unsigned)d, (unsigned)p, VEC, s_lo, s_hi);
-            split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
+            split_range(s_hi - s_lo, part, nparts, VEC, lo, hi);
             if (send && hi > lo)
               cta_publish<Ti, Tw>(&all_stage[d], 1, (size_t)rank * cap2_b + lo * sizeof(Tw), send + base + s_lo + lo, hi - lo);
           }
@@ -74,7 +73,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       }
       case DevColl::reduce: {
         const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
-        split_range(len, cta, nct, VEC, lo, hi);
+        split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo)
           cta_publish<Ti, Tw>(&all_stage[root], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
@@ -82,14 +81,14 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       case DevColl::bcast: {
         if (rank != root) break;
         const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
-        split_range(len, cta, nct, VEC, lo, hi);
+        split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo) cta_publish<Ti, Tw>(all_stage, p, lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
       }
       case DevColl::allgather:
       case DevColl::gather: {
         const size_t base = c * cap_e, len = clamp_len(T.send_counts[rank], base, cap_e);
-        split_range(len, cta, nct, VEC, lo, hi);
+        split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo) {
           if (kind == DevColl::allgather)
             cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
@@ -99,34 +98,148 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
         break;
       }
       case DevColl::reduce_scatter:
-      case DevColl::alltoall: {
-        const size_t base = c * cap_e;
+      case DevColl::alltoall:
+      case DevColl::scatter: {
+        if (kind == DevColl::scatter && rank != root) break;
+        const bool sc = kind == DevColl::scatter;
+        const size_t unit = sc ? full_e : cap_e, base = c * unit;
+        const size_t slot_off = sc ? 0 : (size_t)rank * cap_b;
+        size_t maxlen = 0;
         for (int d = 0; d < p; ++d) {
           const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
-          const size_t len = clamp_len(cnt, base, cap_e);
-          split_range(len, cta, nct, VEC, lo, hi);
-          if (send && hi > lo)
-            cta_publish<Ti, Tw>(&all_stage[d], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo);
+          const size_t len = clamp_len(cnt, base, unit);
+          maxlen = len > maxlen ? len : maxlen;
         }
-        break;
-      }
-      case DevColl::scatter: {
-        if (rank != root) break;
-        const size_t base = c * full_e;
+        if (nparts == 1 && grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
+          if ((int)grp < p && send) {
+            const int d = (int)grp;
+            const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
+            const size_t len = clamp_len(cnt, base, unit);
+            if (len) group_publish<Ti, Tw>(all_stage[d] + slot_off, send + T.send_displs[d] + base, len, lane, grp_lanes);
+          }
+          break;
+        }
         for (int d = 0; d < p; ++d) {
-          const size_t len = clamp_len(T.send_counts[d], base, full_e);
-          split_range(len, cta, nct, VEC, lo, hi);
+          const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
+          const size_t len = clamp_len(cnt, base, unit);
+          split_range(len, part, nparts, VEC, lo, hi);
           if (send && hi > lo)
-            cta_publish<Ti, Tw>(&all_stage[d], 1, lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo);
+            cta_publish<Ti, Tw>(&all_stage[d], 1, slot_off + lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo);
         }
         break;
       }
       case DevColl::barrier: break;
     }
+  };
 
-    // ------------------------------ handshake A ----------------------------
+  // ------------------------------ consume (local loads), single-phase kinds ---
+  auto consume = [&](uint64_t c, unsigned part, unsigned nparts) {
+    const int par = (int)((P.seq + c) & 1);
+    char* mystage = ws.stage[rank] + (size_t)par * half;
+    char* slot[kMaxRanks];    // my slots, one per source rank
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) slot[r] = mystage + (size_t)r * cap_b;
+    size_t lo, hi;
+    switch (kind) {
+      case DevColl::allreduce:
+      case DevColl::reduce: {
+        if (kind == DevColl::reduce && rank != root) break;
+        const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
+        split_range(len, part, nparts, VEC, lo, hi);
+        if (recv && hi > lo) {
+          To* out = recv + base + lo;
+          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+        }
+        break;
+      }
+      case DevColl::reduce_scatter: {
+        const size_t base = c * cap_e, len = clamp_len(T.recv_counts[rank], base, cap_e);
+        split_range(len, part, nparts, VEC, lo, hi);
+        if (recv && hi > lo) {
+          To* out = recv + base + lo;
+          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+        }
+        break;
+      }
+      case DevColl::allgather:
+      case DevColl::gather:
+      case DevColl::alltoall: {
+        if (kind == DevColl::gather && rank != root) break;
+        const size_t base = c * cap_e;
+        if constexpr (std::is_same<Tw, To>::value) {
+          size_t maxlen = 0;
+          for (int r = 0; r < p; ++r) {
+            const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
+            maxlen = len > maxlen ? len : maxlen;
+          }
+          if (nparts == 1 && grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
+            if ((int)grp < p && recv) {
+              const int r = (int)grp;
+              const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
+              group_copy((char*)(recv + T.recv_displs[r] + base), slot[r], len * sizeof(Tw), true, lane, grp_lanes);
+            }
+            break;
+          }
+          for (int r = 0; r < p; ++r) {
+            const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
+            split_range(len, part, nparts, VEC, lo, hi);
+            if (recv && hi > lo)
+              cta_copy((char*)(recv + T.recv_displs[r] + base + lo), slot[r] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
+          }
+        }
+        break;
+      }
+      case DevColl::bcast:
+      case DevColl::scatter: {
+        if (kind == DevColl::bcast && rank == root) break;
+        const size_t cnt = kind == DevColl::bcast ? P.count : T.recv_counts[rank];
+        const size_t base = c * full_e, len = clamp_len(cnt, base, full_e);
+        split_range(len, part, nparts, VEC, lo, hi);
+        if (recv && hi > lo) {
+          if constexpr (std::is_same<Tw, To>::value)
+            cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
+        }
+        break;
+      }
+      case DevColl::barrier: break;
+    }
+  };
+
+  // =========================== pipelined schedule =============================
+  // Large uniform reduce_scatter / allgather / alltoall: the lower half of the grid
+  // only publishes (NVLink stores), the upper half only consumes (HBM traffic), so
+  // chunk c+1 crosses the links while chunk c is copied out.  A slot is reused
+  // every second chunk; the publisher waits for the consumers' C flag of the chunk
+  // that used it before.
+  if (P.pipelined && gridDim.x >= 2) {
+    const unsigned n_pub = gridDim.x / 2, n_con = gridDim.x - n_pub;
+    const uint64_t G = P.local_chunks[rank];
+    if (blockIdx.x < n_pub) {
+      for (uint64_t c = 0; c < G; ++c) {
+        if (c >= 2 && !wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, c - 1), P.timeout_ns)) return;
+        publish(c, blockIdx.x, n_pub);
+        arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_pub, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G);
+      }
+    } else {
+      for (uint64_t c = 0; c < G; ++c) {
+        if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+        consume(c, blockIdx.x - n_pub, n_con);
+        arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_con, make_epoch(P.seq, c + 1), false, 0, 0);
+      }
+    }
+    // Closing barrier: every peer has consumed every chunk, both halves are free.
+    (void)wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, G), P.timeout_ns);
+    return;
+  }
+
+  // =========================== serial schedule ================================
+  const unsigned cta = blockIdx.x, nct = gridDim.x;
+  __shared__ uint64_t s_chunks;
+  uint64_t G = P.local_chunks[rank];
+  for (uint64_t c = 0; c < G; ++c) {
+    publish(c, cta, nct);
     const uint64_t e = make_epoch(P.seq, c + 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, e, c == 0, (int)(P.seq & 1), P.local_chunks[rank]);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, nct, e, c == 0, (int)(P.seq & 1), P.local_chunks[rank]);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
     if (c == 0) {
       if (threadIdx.x == 0) {
@@ -140,109 +253,41 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       __syncthreads();
       G = s_chunks;
     }
-
-    // ------------------------------ consume (local loads) ------------------
-    char* slot[kMaxRanks];    // my slots, one per source rank
+    if (!(kind == DevColl::allreduce && P.two_phase)) {
+      consume(c, cta, nct);
+      continue;
+    }
+    // ---- two-phase allreduce ---------------------------------------------------
+    const int par = (int)((P.seq + c) & 1);
+    char* mystage = ws.stage[rank] + (size_t)par * half;
+    const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
+    // phase 1: reduce the slice this rank owns and push the result to everyone's second area
+    char* slot2[kMaxRanks];
+    Tw* outs[kMaxRanks];
+    size_t lo, hi, s_lo, s_hi;
+    split_range(len, (unsigned)rank, (unsigned)p, VEC, s_lo, s_hi);
+    split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r) slot[r] = mystage + (size_t)r * cap_b;
-
-    switch (kind) {
-      case DevColl::allreduce: {
-        if (!P.two_phase) {
-          const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
-          split_range(len, cta, nct, VEC, lo, hi);
-          if (recv && hi > lo) {
-            To* out = recv + base + lo;
-            cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
-          }
-          break;
+    for (int r = 0; r < kMaxRanks; ++r) {
+      slot2[r] = mystage + (size_t)r * cap2_b;
+      outs[r] = r < p ? (Tw*)(ws.stage[r] + (size_t)par * half + area_b + (size_t)rank * cap2_b) + lo : nullptr;
+    }
+    if (hi > lo) cta_reduce<Tw, Tw, Red>(outs, p, slot2, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
+    arrive_and_post(ws, rank, FlagLayout::off_B, 1, nct, e, false, 0, 0);
+    if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
+    // phase 2: every owner's reduced slice is now in my second area
+    for (int s = 0; s < p; ++s) {
+      split_range(len, (unsigned)s, (unsigned)p, VEC, s_lo, s_hi);
+      split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
+      if (recv && hi > lo) {
+        char* src = mystage + area_b + (size_t)s * cap2_b;
+        if constexpr (std::is_same<Tw, To>::value) {
+          cta_copy((char*)(recv + base + s_lo + lo), src + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
+        } else {
+          To* out = recv + base + s_lo + lo;
+          cta_reduce<Tw, To, RedNone>(&out, 1, &src, lo * sizeof(Tw), 1, hi - lo, RedNone(), 1.0, 1);
         }
-        const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
-        // phase 1: reduce the slice this rank owns and push the result to everyone's second area
-        char* slot2[kMaxRanks];
-        Tw* outs[kMaxRanks];
-        size_t s_lo, s_hi;
-        split_range(len, (unsigned)rank, (unsigned)p, VEC, s_lo, s_hi);
-        split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          slot2[r] = mystage + (size_t)r * cap2_b;
-          outs[r] = r < p ? (Tw*)(all_stage[r] + area_b + (size_t)rank * cap2_b) + lo : nullptr;
-        }
-        if (hi > lo)
-          cta_reduce<Tw, Tw, Red>(outs, p, slot2, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
-        arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
-        if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
-        // phase 2: every owner's reduced slice is now in my second area
-        for (int s = 0; s < p; ++s) {
-          split_range(len, (unsigned)s, (unsigned)p, VEC, s_lo, s_hi);
-          split_range(s_hi - s_lo, cta, nct, VEC, lo, hi);
-          if (recv && hi > lo) {
-            char* src = mystage + area_b + (size_t)s * cap2_b;
-            if constexpr (std::is_same<Tw, To>::value) {
-              cta_copy((char*)(recv + base + s_lo + lo), src + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
-            } else {
-              To* out = recv + base + s_lo + lo;
-              cta_reduce<Tw, To, RedNone>(&out, 1, &src, lo * sizeof(Tw), 1, hi - lo, RedNone(), 1.0, 1);
-            }
-          }
-        }
-        break;
       }
-      case DevColl::reduce: {
-        if (rank != root) break;
-        const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
-        split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo) {
-          To* out = recv + base + lo;
-          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
-        }
-        break;
-      }
-      case DevColl::reduce_scatter: {
-        const size_t base = c * cap_e, len = clamp_len(T.recv_counts[rank], base, cap_e);
-        split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo) {
-          To* out = recv + base + lo;
-          cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
-        }
-        break;
-      }
-      case DevColl::allgather:
-      case DevColl::gather:
-      case DevColl::alltoall: {
-        if (kind == DevColl::gather && rank != root) break;
-        const size_t base = c * cap_e;
-        for (int r = 0; r < p; ++r) {
-          const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
-          split_range(len, cta, nct, VEC, lo, hi);
-          if (recv && hi > lo) {
-            if constexpr (std::is_same<Tw, To>::value)
-              cta_copy((char*)(recv + T.recv_displs[r] + base + lo), slot[r] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
-          }
-        }
-        break;
-      }
-      case DevColl::bcast: {
-        if (rank == root) break;
-        const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
-        split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo) {
-          if constexpr (std::is_same<Tw, To>::value)
-            cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
-        }
-        break;
-      }
-      case DevColl::scatter: {
-        const size_t base = c * full_e, len = clamp_len(T.recv_counts[rank], base, full_e);
-        split_range(len, cta, nct, VEC, lo, hi);
-        if (recv && hi > lo) {
-          if constexpr (std::is_same<Tw, To>::value)
-            cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
-        }
-        break;
-      }
-      case DevColl::barrier: break;
     }
   }
 
@@ -250,7 +295,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
     // Both halves were used: make sure every peer is done with them before the
     // next launch (which may start on either half) writes into them.
     const uint64_t e = make_epoch(P.seq, 1);
-    arrive_and_post(ws, rank, FlagLayout::off_C, 2, e, false, 0, 0);
+    arrive_and_post(ws, rank, FlagLayout::off_C, 2, nct, e, false, 0, 0);
     (void)wait_all(ws, rank, FlagLayout::off_C, 2, e, P.timeout_ns);
   }
 }

@@ -102,22 +102,22 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* slot, uint64_t epoch, 
 // handshakes
 // ---------------------------------------------------------------------------
 /**
- * Called by every thread of every CTA of `rank` once the CTA's share of the
- * preceding writes is issued.  The last CTA to arrive stores `epoch` into
+ * Called by every thread of every CTA of a group of `group` CTAs of `rank` once
+ * the CTA's share of the preceding writes is issued.  The last CTA to arrive stores `epoch` into
  * slot [rank] of every rank's flag array `off` (optionally after publishing
  * `meta_value` into the meta word of parity `meta_par`).
  */
 __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, size_t off, int counter_idx,
-                                                uint64_t epoch, bool with_meta, int meta_par,
+                                                unsigned group, uint64_t epoch, bool with_meta, int meta_par,
                                                 uint64_t meta_value) {
   __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     int last = 1;
-    if (gridDim.x > 1) {
+    if (group > 1) {
       __threadfence();  // this CTA's writes before the arrival count
       unsigned* ctr = (unsigned*)flag_slot(ws.flags[rank], FlagLayout::off_arrive, counter_idx);
-      last = atomicInc(ctr, gridDim.x - 1) == gridDim.x - 1;
+      last = atomicInc(ctr, group - 1) == group - 1;
       if (last) __threadfence();  // other CTAs' writes before the flag stores
     }
     s_last = last;

@@ -93,11 +93,12 @@ __device__ __forceinline__ size_t clamp_len(size_t count, size_t lo, size_t cap)
 // copies
 // ---------------------------------------------------------------------------
 template <typename V>
-__device__ __forceinline__ void copy_units(char* dst, const char* src, size_t units, bool src_is_staging) {
+__device__ __forceinline__ void copy_units(char* dst, const char* src, size_t units, bool src_is_staging,
+                                           unsigned lane, unsigned nlanes) {
   V* d = (V*)dst;
   const V* s = (const V*)src;
-  const size_t stride = blockDim.x;
-  size_t i = threadIdx.x;
+  const size_t stride = nlanes;
+  size_t i = lane;
   // four independent loads in flight per thread
   for (; i + 3 * stride < units; i += 4 * stride) {
     V a, b, c, e;
@@ -109,34 +110,40 @@ __device__ __forceinline__ void copy_units(char* dst, const char* src, size_t un
 }
 
 /**
- * Copy `nbytes` with all threads of the CTA.  Uses the widest unit both
- * addresses allow (16, 8, 4, 2 or 1 bytes).
+ * Copy `nbytes` with `nlanes` cooperating threads (this thread is `lane`).  Uses
+ * the widest unit both addresses allow (16, 8, 4, 2 or 1 bytes).
  */
-__device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t nbytes, bool src_is_staging) {
+__device__ __forceinline__ void group_copy(char* dst, const char* src, size_t nbytes, bool src_is_staging,
+                                           unsigned lane, unsigned nlanes) {
   if (nbytes == 0) return;
   const uintptr_t mis = (uintptr_t)dst | (uintptr_t)src;
   if ((mis & 15) == 0) {
     const size_t nv = nbytes >> 4;
-    copy_units<uint4>(dst, src, nv, src_is_staging);
+    copy_units<uint4>(dst, src, nv, src_is_staging, lane, nlanes);
     const size_t done = nv << 4;
-    if (threadIdx.x < (nbytes - done)) dst[done + threadIdx.x] = src[done + threadIdx.x];
+    for (size_t k = lane; k < nbytes - done; k += nlanes) dst[done + k] = src[done + k];
   } else if ((mis & 7) == 0) {
     const size_t nv = nbytes >> 3;
-    copy_units<uint2>(dst, src, nv, src_is_staging);
+    copy_units<uint2>(dst, src, nv, src_is_staging, lane, nlanes);
     const size_t done = nv << 3;
-    if (threadIdx.x < (nbytes - done)) dst[done + threadIdx.x] = src[done + threadIdx.x];
+    for (size_t k = lane; k < nbytes - done; k += nlanes) dst[done + k] = src[done + k];
   } else if ((mis & 3) == 0) {
     const size_t nv = nbytes >> 2;
-    copy_units<uint32_t>(dst, src, nv, src_is_staging);
+    copy_units<uint32_t>(dst, src, nv, src_is_staging, lane, nlanes);
     const size_t done = nv << 2;
-    if (threadIdx.x < (nbytes - done)) dst[done + threadIdx.x] = src[done + threadIdx.x];
+    for (size_t k = lane; k < nbytes - done; k += nlanes) dst[done + k] = src[done + k];
   } else if ((mis & 1) == 0) {
     const size_t nv = nbytes >> 1;
-    copy_units<uint16_t>(dst, src, nv, src_is_staging);
-    if ((nbytes & 1) && threadIdx.x == 0) dst[nbytes - 1] = src[nbytes - 1];
+    copy_units<uint16_t>(dst, src, nv, src_is_staging, lane, nlanes);
+    if ((nbytes & 1) && lane == 0) dst[nbytes - 1] = src[nbytes - 1];
   } else {
-    copy_units<uint8_t>(dst, src, nbytes, src_is_staging);
+    copy_units<uint8_t>(dst, src, nbytes, src_is_staging, lane, nlanes);
   }
+}
+
+/** Copy with all threads of the CTA. */
+__device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t nbytes, bool src_is_staging) {
+  group_copy(dst, src, nbytes, src_is_staging, threadIdx.x, blockDim.x);
 }
 
 // ---------------------------------------------------------------------------
@@ -192,6 +199,18 @@ __device__ __forceinline__ void cta_fanout(char* const* dsts, int ndst, size_t d
       for (int d = 0; d < ndst; ++d) dsts[d][dst_off + nbytes - 1] = src[nbytes - 1];
   } else {
     fanout_units<uint8_t>(dsts, ndst, dst_off, src, nbytes);
+  }
+}
+
+/** Single destination, a subset of the CTA's threads: used to serve all peers of a small message at once. */
+template <typename Ti, typename Tw>
+__device__ __forceinline__ void group_publish(char* dst, const Ti* src, size_t n, unsigned lane, unsigned nlanes) {
+  if constexpr (std::is_same<Ti, Tw>::value) {
+    group_copy(dst, (const char*)src, n * sizeof(Ti), false, lane, nlanes);
+  } else {
+    using Ai = typename Elem<Ti>::Acc;
+    using Aw = typename Elem<Tw>::Acc;
+    for (size_t i = lane; i < n; i += nlanes) ((Tw*)dst)[i] = Elem<Tw>::down(acc_cast<Aw, Ai>(Elem<Ti>::up(src[i])));
   }
 }
 

@@ -106,14 +106,14 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
   if (P.mc_in != nullptr) {
     // ---- zero-copy: operate on the user's symmetric buffers --------------------
     const uint64_t e = make_epoch(P.seq, 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, e, true, (int)(P.seq & 1), 1);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, true, (int)(P.seq & 1), 1);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
     const size_t nvec = (P.count * sizeof(T) + 15) >> 4;  // symmetric allocations are padded to 16 bytes
     size_t s_lo, s_hi;
     split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
     reduce_vectors<T, OP>(P.mc_in, P.mc_out, s_lo, s_hi, scale);
     __threadfence_system();
-    arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
+    arrive_and_post(ws, rank, FlagLayout::off_B, 1, gridDim.x, e, false, 0, 0);
     (void)wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns);
     return;
   }
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
     if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
 
     const uint64_t e = make_epoch(P.seq, c + 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, e, c == 0, (int)(P.seq & 1), G);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, c == 0, (int)(P.seq & 1), G);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
 
     const size_t nvec = (len * sizeof(T) + 15) >> 4;  // the tail vector may include stale bytes: harmless
@@ -142,14 +142,14 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
     split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
     reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale);
     __threadfence_system();
-    arrive_and_post(ws, rank, FlagLayout::off_B, 1, e, false, 0, 0);
+    arrive_and_post(ws, rank, FlagLayout::off_B, 1, gridDim.x, e, false, 0, 0);
     if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
 
     if (hi > lo) cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(T), (hi - lo) * sizeof(T), true);
   }
   if (G > 1) {
     const uint64_t e = make_epoch(P.seq, 1);
-    arrive_and_post(ws, rank, FlagLayout::off_C, 2, e, false, 0, 0);
+    arrive_and_post(ws, rank, FlagLayout::off_C, 2, gridDim.x, e, false, 0, 0);
     (void)wait_all(ws, rank, FlagLayout::off_C, 2, e, P.timeout_ns);
   }
 }

@@ -247,6 +247,20 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   }
 
 
+  // Large uniform reduce_scatter / allgather / alltoall run pipelined: smaller chunks, half of the
+  // grid publishing while the other half consumes.
+  size_t slot_e = cap_e;
+  if ((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
+      p > 1 && P.count * esz >= tn.pipeline_min_bytes) {
+    size_t chunk_b = std::max<size_t>(P.count * esz / 8, 512 * 1024);
+    chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
+    if (chunk_b >= 256 && chunk_b < P.count * esz) {
+      slot_e = chunk_b / esz;
+      P.pipelined = 1;
+      P.slot_elems = slot_e;
+    }
+  }
+
   for (int lr = 0; lr < I.nlocal; ++lr) {
     const int r = I.rank0 + lr;
     const RankArgs& a = ranks[(size_t)lr];
@@ -278,10 +292,10 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
         break;
       case DevColl::reduce: need = P.count; chunk_unit = cap_e; work = P.count; break;
       case DevColl::bcast: need = P.count; chunk_unit = full_e; work = P.count; break;
-      case DevColl::reduce_scatter: need = mx(T.recv_counts); chunk_unit = cap_e; work = need * (size_t)p; break;
-      case DevColl::allgather: need = mx(T.recv_counts); chunk_unit = cap_e; work = need * (size_t)p; break;
+      case DevColl::reduce_scatter: need = mx(T.recv_counts); chunk_unit = slot_e; work = need * (size_t)p; break;
+      case DevColl::allgather: need = mx(T.recv_counts); chunk_unit = slot_e; work = need * (size_t)p; break;
       case DevColl::alltoall:
-        need = std::max(mx(T.send_counts), mx(T.recv_counts)); chunk_unit = cap_e; work = need * (size_t)p; break;
+        need = std::max(mx(T.send_counts), mx(T.recv_counts)); chunk_unit = slot_e; work = need * (size_t)p; break;
       case DevColl::gather:
         need = r == d.root ? mx(T.recv_counts) : T.send_counts[r];
         chunk_unit = cap_e; work = r == d.root ? need * (size_t)p : need; break;
@@ -302,6 +316,10 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   if (d.kind == DevColl::allreduce && algo == AllreduceAlgo::nvls) cap = zero_copy ? tn.max_ctas_zero_copy : tn.max_ctas_nvls;
   if (I.nlocal > 1) cap = std::min(cap, std::max(1, I.sm_count / I.nlocal));  // cooperative launch must be co-resident
   ctas = std::max(1, std::min(ctas, cap));
+  if (P.pipelined) {
+    ctas = std::max(2, std::min(cap, 128));   // the whole budget: half publishes, half consumes
+    if (I.nlocal > 1) ctas = std::max(2, std::min(ctas, I.sm_count / I.nlocal));
+  }
   if (max_work_bytes <= 4096) threads = std::min(threads, 256);
 
   I.order_after_previous(stream);

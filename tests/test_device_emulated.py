@@ -285,6 +285,38 @@ def test_multichunk_paths(small_stage_comm):
             assert torch.equal(outs[d], torch.cat([a2a[r][d * 30011:(d + 1) * 30011] for r in range(p)]))
 
 
+def test_pipelined_schedule(al):
+    """Large uniform reduce_scatter / allgather / alltoall: publisher and consumer CTAs, many chunks."""
+    old = al.get_tuning("pipeline_min_bytes")
+    al.set_tuning("pipeline_min_bytes", 16384)
+    try:
+        for p in (2, 8):
+            comm = al.DeviceComm(emulate=p)
+            n = 1_500_007  # per-rank slice, not a multiple of anything
+            for it in range(2):
+                ss = [rand(n, torch.float32, 200 + r + it) for r in range(p)]
+                outs = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+                comm.allgather(ss, outs)
+                xs = [rand(n * p, torch.float32, 210 + r + it) for r in range(p)]
+                rs = [torch.zeros(n, device="cuda") for _ in range(p)]
+                comm.reduce_scatter(xs, rs)
+                a2 = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+                comm.alltoall(xs, a2)
+                small = [torch.full((3,), float(r), device="cuda") for r in range(p)]
+                comm.allreduce(small)
+                torch.cuda.synchronize()
+                full, want = torch.cat(ss), ref_reduce(xs, "sum")
+                for r in range(p):
+                    assert torch.equal(outs[r], full)
+                    torch.testing.assert_close(rs[r], want[r * n:(r + 1) * n])
+                    assert torch.equal(a2[r], torch.cat([xs[q][r * n:(r + 1) * n] for q in range(p)]))
+                    assert torch.all(small[r] == sum(range(p)))
+            assert comm.status()["code"] == 0
+            comm.close()
+    finally:
+        al.set_tuning("pipeline_min_bytes", old)
+
+
 def test_barrier_nonblocking_and_stats(comm):
     p = comm.size
     comm.barrier()

@@ -46,6 +46,7 @@ TOOLS = {
     "bandwidth": ["benchmark/bandwidth.cpp"],
     "benchmark_waits": ["benchmark/benchmark_waits.cpp"],
     "benchmark_events": ["benchmark/benchmark_events.cpp"],
+    "stress_progress": ["benchmark/stress_progress.cpp"],
     "hello_world": ["examples/hello_world.cpp"],
     "allreduce": ["examples/allreduce.cpp"],
     "pingpong": ["examples/pingpong.cpp"],

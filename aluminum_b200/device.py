@@ -280,6 +280,11 @@ class DeviceComm:
             raise AlError("tensor was not created by symm_empty of this communicator")
         check(self._lib.al_dev_symm_free(self._h, C.c_void_p(base)))
 
+    def peer_ptr(self, tensor, peer: int) -> int:
+        """Address, in this process, of rank ``peer``'s copy of a symmetric tensor (usable by kernels of this
+        library; it is not wrapped in a tensor because the memory physically lives on another GPU)."""
+        return int(check_ptr(self._lib.al_dev_symm_peer_ptr(self._h, C.c_void_p(tensor.data_ptr()), int(peer))))
+
     def peer_tensor(self, tensor, peer: int):
         """The view, in this process, of rank ``peer``'s copy of a symmetric tensor."""
         torch = self._torch
@@ -312,10 +317,11 @@ class DeviceComm:
     def halo_exchange(self, tensors, depth: int = 1, periodic: bool = False, ctas: int = 0, stream=None) -> None:
         """Fused halo exchange of fp32 tensors shaped (N, C, D_local + 2*depth, H, W) split along D.
 
-        ``tensors[r]`` must be rank r's tensor as addressable from this process: own tensor plus
-        :meth:`peer_tensor` views of the neighbours (all ranks' tensors in emulation)."""
-        ref = next(t for t in tensors if t is not None)
+        ``tensors[r]`` must be rank r's tensor as addressable from this process: the own tensor plus
+        :meth:`peer_ptr` addresses of the neighbours (all ranks' tensors in emulation)."""
+        ref = next(t for t in tensors if t is not None and not isinstance(t, int))
         n, c, dtot, h, w = ref.shape
-        arr = (C.c_void_p * self.size)(*[(t.data_ptr() if t is not None else None) for t in tensors])
+        arr = (C.c_void_p * self.size)(*[(None if t is None else (t if isinstance(t, int) else t.data_ptr()))
+                                         for t in tensors])
         check(self._lib.al_halo_exchange(self._h, arr, n * c, dtot - 2 * depth, h * w, depth, 1 if periodic else 0,
                                          int(ctas), self._stream(stream)))

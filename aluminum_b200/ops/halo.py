@@ -56,7 +56,7 @@ class HaloExchange:
                 if periodic:
                     nb %= p
                 if 0 <= nb < p and nb != comm.rank:
-                    self.tensors[nb] = comm.peer_tensor(slabs, nb)
+                    self.tensors[nb] = comm.peer_ptr(slabs, nb)
 
     def exchange(self, ctas: int = 0) -> None:
         """Fill the neighbours' halo planes from this rank's boundary planes and wait for theirs."""

@@ -1,0 +1,90 @@
+// stress_progress - many small non-blocking allreduces in flight at once.
+//
+//   alrun -n 8 stress_progress [--ops 64] [--streams 8] [--rounds 20] [--min-bytes 4096] [--max-bytes 262144]
+//
+// Per rank: `streams` CUDA streams, one device communicator per stream (the library's
+// model: a communicator is bound to a stream), `ops` NonblockingAllreduce calls with
+// log-uniform fp32 sizes (seed 1, identical on every rank) spread round-robin over the
+// communicators, each followed by Wait.  With AL_REQ_MEMOPS=1 both the completion record
+// and the Wait are stream memory operations (cuStreamWriteValue32 / cuStreamWaitValue32),
+// so nothing in the loop synchronises with the host.  Reports operations per second
+// (max over ranks of the round time) and the p50 / p99 of the per-operation device time.
+#include <algorithm>
+#include <random>
+
+#include "../cpp_tests/test_common.hpp"
+
+using namespace altest;
+
+int main(int argc, char** argv) {
+  Args a(argc, argv);
+  try {
+    Al::Initialize(argc, argv);
+    const int nops = (int)a.num("ops", 64), nstreams = (int)a.num("streams", 8), rounds = (int)a.num("rounds", 20);
+    const double lo = std::log((double)a.num("min-bytes", 4096)), hi = std::log((double)a.num("max-bytes", 262144));
+    Al::HostCommunicator hc;
+    std::vector<cudaStream_t> streams((size_t)nstreams);
+    std::vector<std::unique_ptr<Al::DeviceCommunicator>> comms;
+    for (auto& s : streams) {
+      AL_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+      comms.emplace_back(new Al::DeviceCommunicator(s));
+    }
+    std::mt19937 rng(1);
+    std::uniform_real_distribution<double> U(lo, hi);
+    std::vector<size_t> counts((size_t)nops);
+    std::vector<float*> bufs((size_t)nops);
+    for (int i = 0; i < nops; ++i) {
+      counts[(size_t)i] = std::max<size_t>(1, (size_t)std::exp(U(rng)) / 4);
+      AL_CHECK_CUDA(cudaMalloc((void**)&bufs[(size_t)i], counts[(size_t)i] * 4));
+      std::vector<float> h(counts[(size_t)i], 1.0f);
+      AL_CHECK_CUDA(cudaMemcpy(bufs[(size_t)i], h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+    }
+    std::vector<cudaEvent_t> e0((size_t)nops), e1((size_t)nops);
+    for (int i = 0; i < nops; ++i) { cudaEventCreate(&e0[(size_t)i]); cudaEventCreate(&e1[(size_t)i]); }
+    std::vector<double> round_us, op_us;
+    for (int r = 0; r < rounds + 3; ++r) {
+      Al::Barrier<Al::HostBackend>(hc);
+      const double t0 = Al::get_time();
+      for (int i = 0; i < nops; ++i) {
+        Al::DeviceCommunicator& c = *comms[(size_t)(i % nstreams)];
+        Al::DeviceBackend::req_type req;
+        AL_CHECK_CUDA(cudaEventRecord(e0[(size_t)i], c.get_stream()));
+        Al::NonblockingAllreduce<Al::DeviceBackend>(bufs[(size_t)i], counts[(size_t)i], Al::ReductionOperator::max, c, req);
+        Al::Wait<Al::DeviceBackend>(req);  // stream-side join, the host continues
+        AL_CHECK_CUDA(cudaEventRecord(e1[(size_t)i], c.get_stream()));
+      }
+      for (auto s : streams) AL_CHECK_CUDA(cudaStreamSynchronize(s));
+      const double dt = (Al::get_time() - t0) * 1e6;
+      if (r >= 3) {
+        round_us.push_back(dt);
+        for (int i = 0; i < nops; ++i) {
+          float ms = 0;
+          cudaEventElapsedTime(&ms, e0[(size_t)i], e1[(size_t)i]);
+          op_us.push_back(ms * 1e3);
+        }
+      }
+    }
+    for (auto& c : comms) c->check_status();
+    // correctness: max of ones is one
+    std::vector<float> h(counts[0]);
+    AL_CHECK_CUDA(cudaMemcpy(h.data(), bufs[0], counts[0] * 4, cudaMemcpyDeviceToHost));
+    if (h[0] != 1.0f || h.back() != 1.0f) throw_al_exception("wrong result");
+    std::vector<double> worst(round_us.size());
+    Al::Allreduce<Al::HostBackend>((const double*)round_us.data(), worst.data(), round_us.size(), Al::ReductionOperator::max, hc);
+    std::sort(worst.begin(), worst.end());
+    std::sort(op_us.begin(), op_us.end());
+    if (hc.rank() == 0) {
+      const double med = worst[worst.size() / 2];
+      printf("stress ranks=%d streams=%d ops=%d memops=%s round_median_us=%.1f ops_per_s=%.0f op_p50_us=%.1f op_p99_us=%.1f\n",
+             hc.size(), nstreams, nops, getenv("AL_REQ_MEMOPS") ? getenv("AL_REQ_MEMOPS") : "0", med, nops / (med * 1e-6),
+             op_us[op_us.size() / 2], op_us[(size_t)(op_us.size() * 0.99)]);
+    }
+    Al::Barrier<Al::HostBackend>(hc);
+    comms.clear();
+    Al::Finalize();
+  } catch (const std::exception& e) {
+    fprintf(stderr, "stress_progress: %s\n", e.what());
+    return 1;
+  }
+  return 0;
+}

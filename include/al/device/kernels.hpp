@@ -39,6 +39,7 @@ struct NvlsParams {
   const char* mc_in;    ///< zero-copy flavour: multicast alias of the symmetric input (nullptr = staged)
   char* mc_out;         ///< zero-copy flavour: multicast alias of the symmetric output
   size_t count;
+  size_t chunk_elems;   ///< non-zero: pipelined staged flavour with chunks of this many elements
   uint64_t chunks;
   uint64_t seq;
   uint64_t timeout_ns;

@@ -42,7 +42,8 @@ struct Tuning {
   int max_ctas = 128;                          ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
   int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
   int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
-  size_t pipeline_min_bytes = size_t{2} << 20;  ///< AL_PIPELINE_MIN: per-rank slice from which reduce_scatter / allgather / alltoall split the grid into publishers and consumers
+  size_t pipeline_min_bytes = size_t{32} << 20;  ///< AL_PIPELINE_MIN: per-rank slice from which reduce_scatter / allgather / alltoall split the grid into publishers and consumers
+  size_t nvls_pipeline_min_bytes = size_t{128} << 20;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is pipelined from this size on
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
   // ---- diagnostics ------------------------------------------------------------
   bool trace = false;                          ///< AL_TRACE: record every API call

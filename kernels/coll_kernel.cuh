@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   // instead of one peer after the other.
   const unsigned grp_lanes = blockDim.x / (unsigned)p;
   const unsigned grp = threadIdx.x / grp_lanes, lane = threadIdx.x % grp_lanes;
-  constexpr size_t kSmallBytes = 8192;
+  constexpr size_t kSmallBytes = 65536;  // per-peer slice up to which the peers are served in parallel
 
   // ------------------------------ publish (remote stores) --------------------
   auto publish = [&](uint64_t c, unsigned part, unsigned nparts) {
@@ -110,12 +110,14 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           const size_t len = clamp_len(cnt, base, unit);
           maxlen = len > maxlen ? len : maxlen;
         }
-        if (nparts == 1 && grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
+        if (grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
           if ((int)grp < p && send) {
             const int d = (int)grp;
             const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
             const size_t len = clamp_len(cnt, base, unit);
-            if (len) group_publish<Ti, Tw>(all_stage[d] + slot_off, send + T.send_displs[d] + base, len, lane, grp_lanes);
+            split_range(len, part, nparts, VEC, lo, hi);
+            if (hi > lo)
+              group_publish<Ti, Tw>(all_stage[d] + slot_off + lo * sizeof(Tw), send + T.send_displs[d] + base + lo, hi - lo, lane, grp_lanes);
           }
           break;
         }
@@ -172,11 +174,13 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
             const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
             maxlen = len > maxlen ? len : maxlen;
           }
-          if (nparts == 1 && grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
+          if (grp_lanes >= 32 && maxlen * sizeof(Tw) <= kSmallBytes) {
             if ((int)grp < p && recv) {
               const int r = (int)grp;
               const size_t len = clamp_len(T.recv_counts[r], base, cap_e);
-              group_copy((char*)(recv + T.recv_displs[r] + base), slot[r], len * sizeof(Tw), true, lane, grp_lanes);
+              split_range(len, part, nparts, VEC, lo, hi);
+              if (hi > lo)
+                group_copy((char*)(recv + T.recv_displs[r] + base + lo), slot[r] + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true, lane, grp_lanes);
             }
             break;
           }

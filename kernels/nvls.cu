@@ -75,10 +75,10 @@ __device__ __forceinline__ uint4 scale_pack(uint4 v, float s) {
  */
 template <typename T, NvOp OP>
 __device__ __forceinline__ void reduce_vectors(const char* mc_in, char* mc_out, size_t v_lo, size_t v_hi,
-                                               float scale) {
+                                               float scale, unsigned part, unsigned nparts) {
   constexpr int U = 4;
-  const size_t stride = (size_t)blockDim.x * gridDim.x;
-  size_t v = v_lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)blockDim.x * nparts;
+  size_t v = v_lo + (size_t)part * blockDim.x + threadIdx.x;
   for (; v + (U - 1) * stride < v_hi; v += U * stride) {
     uint4 a[U];
 #pragma unroll
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
     const size_t nvec = (P.count * sizeof(T) + 15) >> 4;  // symmetric allocations are padded to 16 bytes
     size_t s_lo, s_hi;
     split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
-    reduce_vectors<T, OP>(P.mc_in, P.mc_out, s_lo, s_hi, scale);
+    reduce_vectors<T, OP>(P.mc_in, P.mc_out, s_lo, s_hi, scale, blockIdx.x, gridDim.x);
     __threadfence_system();
     arrive_and_post(ws, rank, FlagLayout::off_B, 1, gridDim.x, e, false, 0, 0);
     (void)wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns);
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
     const size_t nvec = (len * sizeof(T) + 15) >> 4;  // the tail vector may include stale bytes: harmless
     size_t s_lo, s_hi;
     split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
-    reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale);
+    reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale, blockIdx.x, gridDim.x);
     __threadfence_system();
     arrive_and_post(ws, rank, FlagLayout::off_B, 1, gridDim.x, e, false, 0, 0);
     if (!wait_all(ws, rank, FlagLayout::off_B, 1, e, P.timeout_ns)) return;
@@ -154,8 +154,87 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
   }
 }
 
+/**
+ * Staged NVLS allreduce for large private buffers, software-pipelined over chunks by
+ * three groups of CTAs that run concurrently:
+ *   IN   copies chunk c of the user's input into the multicast-bound staging half (HBM),
+ *   RED  switch-reduces this rank's slice of chunk c in place (NVLink),
+ *   OUT  copies the finished chunk to the user's output (HBM),
+ * so that the copies of neighbouring chunks hide behind the NVLink phase.  Flags:
+ * A(c) "my copy-in of chunk c is done" (to everyone), B(c) "my slice of chunk c is
+ * reduced and replicated" (to everyone), C(c) "I copied chunk c out" (to everyone;
+ * IN only looks at its own, the closing wait looks at all).
+ */
+template <typename T, NvOp OP>
+__global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __grid_constant__ NvlsParams P) {
+  const Workspace& ws = P.ws;
+  const int p = ws.p, rank = P.rank;
+  if (poisoned(ws, rank)) return;
+  const float scale = (float)P.scale;
+  const size_t half = ws.half_bytes;
+  const size_t chunk_e = P.chunk_elems;
+  const uint64_t G = P.chunks;
+  const T* send = (const T*)P.send;
+  T* recv = (T*)P.recv;
+  const unsigned n = gridDim.x;
+  unsigned n_red = n / 4 < 4 ? 4 : n / 4;
+  if (n_red > n - 2) n_red = n - 2;
+  const unsigned n_in = (n - n_red) / 2, n_out = n - n_red - n_in;
+  const unsigned b = blockIdx.x;
+
+  if (b < n_in) {
+    for (uint64_t c = 0; c < G; ++c) {
+      if (c >= 2) {  // the half is free once my own OUT group copied chunk c-2 out
+        __shared__ int s_ok;
+        if (threadIdx.x == 0) {
+          uint64_t seen = 0;
+          s_ok = wait_flag(flag_slot(ws.flags[rank], FlagLayout::off_C, rank), make_epoch(P.seq, c - 1), P.timeout_ns, &seen);
+          if (!s_ok) report_timeout(ws, rank, rank, 2, make_epoch(P.seq, c - 1), seen);
+        }
+        __syncthreads();
+        if (!s_ok) return;
+      }
+      char* mystage = ws.stage[rank] + (size_t)((P.seq + c) & 1) * half;
+      const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
+      size_t lo, hi;
+      split_range(len, b, n_in, 16 / sizeof(T), lo, hi);
+      if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
+      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G);
+    }
+  } else if (b < n_in + n_red) {
+    for (uint64_t c = 0; c < G; ++c) {
+      if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      char* mc = ws.mc_stage + (size_t)((P.seq + c) & 1) * half;
+      const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
+      const size_t nvec = (len * sizeof(T) + 15) >> 4;
+      size_t s_lo, s_hi;
+      split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
+      reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale, b - n_in, n_red);
+      __threadfence_system();
+      arrive_and_post(ws, rank, FlagLayout::off_B, 1, n_red, make_epoch(P.seq, c + 1), false, 0, 0);
+    }
+  } else {
+    for (uint64_t c = 0; c < G; ++c) {
+      if (!wait_all(ws, rank, FlagLayout::off_B, 1, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      char* mystage = ws.stage[rank] + (size_t)((P.seq + c) & 1) * half;
+      const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
+      size_t lo, hi;
+      split_range(len, b - n_in - n_red, n_out, 16 / sizeof(T), lo, hi);
+      if (hi > lo) cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(T), (hi - lo) * sizeof(T), true);
+      arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_out, make_epoch(P.seq, c + 1), false, 0, 0);
+    }
+  }
+  // Closing barrier: every rank has copied its last chunk out; both halves are free for the next launch.
+  (void)wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, G), P.timeout_ns);
+}
+
 template <typename T, NvOp OP>
 void launch(const NvlsParams& P, int ctas, int threads, cudaStream_t s) {
+  if (P.chunk_elems && !P.mc_in && ctas >= 8) {
+    nvls_allreduce_pipelined_kernel<T, OP><<<ctas, threads, 0, s>>>(P);
+    AL_CHECK_CUDA(cudaGetLastError());
+    return;
+  }
   nvls_allreduce_kernel<T, OP><<<ctas, threads, 0, s>>>(P);
   AL_CHECK_CUDA(cudaGetLastError());
 }

@@ -239,10 +239,14 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0);
     }
     if (algo == AllreduceAlgo::automatic) {
-      if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
-      else if (bytes <= tn.ar_oneshot_max_bytes || p == 1) algo = AllreduceAlgo::one_shot;
+      // Measured on 4 and 8 B200: the one-shot push wins for small messages (up to 256 KiB on
+      // <= 4 ranks, 16 KiB on 8), NVLS above, the two-shot push where NVLS does not apply.
+      const size_t one_shot_max = p <= 4 ? tn.ar_oneshot_max_bytes : std::min<size_t>(tn.ar_oneshot_max_bytes, 16384);
+      if (bytes <= one_shot_max || p == 1) algo = AllreduceAlgo::one_shot;
+      else if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
       else algo = AllreduceAlgo::two_shot;
     }
+    if (algo != AllreduceAlgo::nvls) zero_copy = false;
     P.two_phase = algo == AllreduceAlgo::two_shot ? 1 : 0;
   }
 
@@ -252,7 +256,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   size_t slot_e = cap_e;
   if ((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
       p > 1 && P.count * esz >= tn.pipeline_min_bytes) {
-    size_t chunk_b = std::max<size_t>(P.count * esz / 8, 512 * 1024);
+    size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {
       slot_e = chunk_b / esz;
@@ -334,6 +338,15 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     N.recv = ranks[0].recv;
     N.count = P.count;
     N.chunks = P.local_chunks[I.rank0];
+    if (!zero_copy && bytes >= tn.nvls_pipeline_min_bytes) {
+      // pipelined flavour: chunks of 1/8 of the message (at least 16 MiB, at most a staging half);
+      // smaller chunks are dominated by the per-chunk handshakes
+      size_t chunk_b = std::max<size_t>(bytes / 8, size_t{16} << 20);
+      chunk_b = std::min(chunk_b / 4096 * 4096, half);
+      N.chunk_elems = chunk_b / esz;
+      N.chunks = ceil_div(P.count, N.chunk_elems);
+      ctas = std::max(8, std::min(tn.max_ctas_nvls, 128));
+    }
     N.seq = P.seq;
     N.timeout_ns = P.timeout_ns;
     N.scale = P.scale;

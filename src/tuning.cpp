@@ -31,6 +31,7 @@ void Tuning::load_from_env() {
   ar_oneshot_max_bytes = (size_t)env_long("AL_AR_ONESHOT_MAX", (long)ar_oneshot_max_bytes);
   ar_nvls_min_bytes = (size_t)env_long("AL_AR_NVLS_MIN", (long)ar_nvls_min_bytes);
   pipeline_min_bytes = (size_t)env_long("AL_PIPELINE_MIN", (long)pipeline_min_bytes);
+  nvls_pipeline_min_bytes = (size_t)env_long("AL_NVLS_PIPELINE_MIN", (long)nvls_pipeline_min_bytes);
   max_ctas = (int)env_long("AL_MAX_CTAS_PER_OP", max_ctas);
   max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
   max_ctas_zero_copy = (int)env_long("AL_MAX_CTAS_ZERO_COPY", max_ctas_zero_copy);
@@ -77,6 +78,7 @@ std::string Tuning::describe() const {
      << "ar_oneshot_max_bytes = " << ar_oneshot_max_bytes << "\n"
      << "ar_nvls_min_bytes = " << ar_nvls_min_bytes << "\n"
      << "pipeline_min_bytes = " << pipeline_min_bytes << "\n"
+     << "nvls_pipeline_min_bytes = " << nvls_pipeline_min_bytes << "\n"
      << "max_ctas = " << max_ctas << "\n"
      << "max_ctas_nvls = " << max_ctas_nvls << "\n"
      << "max_ctas_zero_copy = " << max_ctas_zero_copy << "\n"

@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
             cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         } else {             // rank d gets slice d of every rank's chunk
           const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
-          for (int d = 0; d < p; ++d) {
+          for (int i = 0; i < p; ++i) {
+            const int d = (rank + 1 + i) % p;  // rotated start: at every step the destinations form a permutation
             size_t s_lo, s_hi;
             split_range(len, (unsigned)d, (unsigned)p, VEC, s_lo, s_hi);
             split_range(s_hi - s_lo, part, nparts, VEC, lo, hi);
@@ -121,7 +122,10 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           }
           break;
         }
-        for (int d = 0; d < p; ++d) {
+        // Every rank starts with a different destination (rank+1, rank+2, ...): at any moment the
+        // ranks write to distinct peers instead of all converging on one GPU's ingress link.
+        for (int i = 0; i < p; ++i) {
+          const int d = (rank + 1 + i) % p;
           const size_t cnt = kind == DevColl::reduce_scatter ? T.recv_counts[d] : T.send_counts[d];
           const size_t len = clamp_len(cnt, base, unit);
           split_range(len, part, nparts, VEC, lo, hi);

@@ -171,3 +171,14 @@ def test_host_transfer_backend(al, bin_dir, op):
                         "--backend", "ht", "--op", op, "--max-size", "65536", "--odd-sizes", "--nonblocking"],
                        capture_output=True, text=True, timeout=180, env={**__import__("os").environ, "AL_GPU_ID": "0"})
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_single_gpu_tools(al, bin_dir):
+    """Wait / event micro-benchmarks and the single-rank device examples run on this GPU."""
+    for tool, needle in (("benchmark_waits", "signal-to-pass"), ("benchmark_events", "pinned flag"),
+                         ("test_stream_mem_ops", "stream memory operations")):
+        r = subprocess.run([str(bin_dir / tool)] + (["200"] if tool.startswith("benchmark") else []),
+                           capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and needle in r.stdout, tool + r.stdout + r.stderr
+    r = subprocess.run([str(bin_dir / "hello_world"), "device"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "sum of ranks = 0" in r.stdout, r.stdout + r.stderr

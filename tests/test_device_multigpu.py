@@ -26,3 +26,14 @@ def test_ops_device_backend(bin_dir, op):
                             "--backend", "device", "--op", op, "--max-size", str(1 << 20), "--odd-sizes", "--zero"] + extra,
                            capture_output=True, text=True, timeout=240, env=env)
         assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_rma_ring_exchange_and_bandwidth(bin_dir):
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    for cmd in (["test_rma", "--max-size", "65536"], ["test_exchange", "--backend", "device", "--peers", "1"],
+                ["bandwidth", "--bytes", "8388608", "--iters", "3"], ["pingpong", "device"]):
+        r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n if cmd[0] != "pingpong" else 2), "--timeout", "120",
+                            str(bin_dir / cmd[0])] + cmd[1:], capture_output=True, text=True, timeout=180)
+        assert r.returncode == 0, " ".join(cmd) + r.stdout + r.stderr

@@ -105,3 +105,17 @@ def test_debug_checks_reject_bad_arguments(bin_dir):
             "try:\n    c.bcast(x, root=5)\n    print('no error')\nexcept al.AlError as e:\n    print('rejected')\n") % str(ROOT)
     r = run([sys.executable, "-c", code], env={"AL_DEBUG": "1"})
     assert "rejected" in r.stdout, r.stdout + r.stderr
+
+
+def test_examples_and_exchange_on_cpu_ranks(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "3", bin_dir / "hello_world"])
+    assert r.returncode == 0 and r.stdout.count("sum of ranks = 3") == 3, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "2", bin_dir / "allreduce"])
+    assert r.returncode == 0 and r.stdout.count("value 3 (expected 3)") == 2, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "2", bin_dir / "pingpong"])
+    assert r.returncode == 0 and "per round trip" in r.stdout
+    r = run([bin_dir / "alrun", "-n", "4", bin_dir / "test_exchange", "--peers", "2", "--size", "5000"])
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "2", bin_dir / "benchmark_ops", "--backend", "host", "--op", "allreduce",
+             "--max-bytes", "4096", "--num-iters", "5"])
+    assert r.returncode == 0 and "host float allreduce" in r.stdout

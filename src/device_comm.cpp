@@ -241,8 +241,10 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     if (algo == AllreduceAlgo::automatic) {
       // Measured on 4 and 8 B200: the one-shot push wins for small messages (up to 256 KiB on
       // <= 4 ranks, 16 KiB on 8), NVLS above, the two-shot push where NVLS does not apply.
-      const size_t one_shot_max = p <= 4 ? tn.ar_oneshot_max_bytes : std::min<size_t>(tn.ar_oneshot_max_bytes, 16384);
+      const size_t one_shot_max = p == 2 ? tn.ar_oneshot_max_bytes * 8
+                                  : (p <= 4 ? tn.ar_oneshot_max_bytes : std::min<size_t>(tn.ar_oneshot_max_bytes, 16384));
       if (bytes <= one_shot_max || p == 1) algo = AllreduceAlgo::one_shot;
+      else if (p == 2 && bytes >= (size_t{4} << 20) && !zero_copy) algo = AllreduceAlgo::two_shot;  // two ranks: the switch saves no traffic, measured 470 vs 380 GB/s
       else if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
       else algo = AllreduceAlgo::two_shot;
     }

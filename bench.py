@@ -15,7 +15,7 @@ through the public `Trainer.run` API with a host->device copy of every step's
 inputs from pinned memory and a device->host read of every step's loss.
 
 --impl reference   the unmodified reference cannot be installed here (it is a CMake
-                   project that requires MPI) -> prints "unavailable".
+                   project that requires MPI, which this image lacks) -> prints "unavailable".
 --impl ddp-nccl    PyTorch DistributedDataParallel over NCCL on the same model and
                    data: the "path that only calls NCCL", kept as a local comparison.
 """
@@ -102,7 +102,7 @@ def main():
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "llnl/Aluminum is a CMake C++ library that hard-requires MPI (none installed, no network); "
-                          "pip install of /root/reference fails: neither setup.py nor pyproject.toml"}))
+                          "pip install of the reference tree fails: neither setup.py nor pyproject.toml"}))
         return 0
 
     import torch

@@ -37,3 +37,15 @@ def test_rma_ring_exchange_and_bandwidth(bin_dir):
         r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n if cmd[0] != "pingpong" else 2), "--timeout", "120",
                             str(bin_dir / cmd[0])] + cmd[1:], capture_output=True, text=True, timeout=180)
         assert r.returncode == 0, " ".join(cmd) + r.stdout + r.stderr
+
+
+def test_data_parallel_matches_single_process(bin_dir):
+    import sys
+    from pathlib import Path
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    worker = Path(__file__).resolve().parent / "workers" / "ddp_worker.py"
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "240", sys.executable, str(worker)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("ok") == n, r.stdout + r.stderr

@@ -119,3 +119,19 @@ def test_examples_and_exchange_on_cpu_ranks(bin_dir):
     r = run([bin_dir / "alrun", "-n", "2", bin_dir / "benchmark_ops", "--backend", "host", "--op", "allreduce",
              "--max-bytes", "4096", "--num-iters", "5"])
     assert r.returncode == 0 and "host float allreduce" in r.stdout
+
+
+def test_python_host_api(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "3", "--timeout", "120", sys.executable, W / "host_python_api.py"])
+    assert r.returncode == 0 and r.stdout.count("ok") == 3, r.stdout + r.stderr
+
+
+def test_info_and_tuning_from_python(built_lib):
+    import aluminum_b200 as al
+    assert "Aluminum-B200" in al.info() and "max_ctas" in al.info()
+    old = al.get_tuning("max_ctas")
+    al.set_tuning("max_ctas", 48)
+    assert al.get_tuning("max_ctas") == 48
+    al.set_tuning("max_ctas", old)
+    with pytest.raises(al.AlError):
+        al.set_tuning("no_such_entry", 1)

@@ -137,6 +137,69 @@ def build(tools: bool = True, jobs: int | None = None, verbose: bool = False) ->
     return LIB
 
 
+def _sanitizer_compiler(kind: str) -> str:
+    """First of $CXX, g++, clang++ that can link a program with the sanitizer's runtime."""
+    import tempfile
+    with tempfile.TemporaryDirectory() as td:
+        src = Path(td) / "t.cpp"
+        src.write_text("int main() { return 0; }\n")
+        for cand in (CXX, "/usr/bin/g++", "g++", "clang++"):
+            exe = shutil.which(cand)
+            if exe is None:
+                continue
+            r = subprocess.run([exe, f"-fsanitize={kind}", str(src), "-o", str(Path(td) / "t")],
+                               capture_output=True, text=True)
+            if r.returncode == 0:
+                return exe
+    raise RuntimeError(f"no compiler on this machine links with -fsanitize={kind}")
+
+
+def build_sanitized(kind: str = "thread", tools: tuple[str, ...] = ("test_units", "test_ops"),
+                    jobs: int | None = None) -> dict[str, Path]:
+    """Build some tools with every host source compiled under a sanitizer.
+
+    The host runtime is compiled again with ``-fsanitize=<kind>`` into
+    ``build/obj_<kind>`` and linked statically into each tool together with the
+    ordinary kernel objects (device code is not instrumented).  Returns the
+    paths of the instrumented tools, ``build/<kind>/<tool>``.
+    """
+    build(tools=False, jobs=jobs)
+    cxx = _sanitizer_compiler(kind)
+    odir = ROOT / "build" / f"obj_{kind}"
+    bdir = ROOT / "build" / kind
+    odir.mkdir(parents=True, exist_ok=True)
+    bdir.mkdir(parents=True, exist_ok=True)
+    flags = [f for f in CXXFLAGS if f != "-O2"] + ["-O1", "-g", f"-fsanitize={kind}", f"-I{ROOT / 'cpp_tests'}"]
+    stamp = _headers_digest() + hashlib.sha1(" ".join(flags).encode()).hexdigest()
+    jobs = jobs or max(1, (os.cpu_count() or 4))
+
+    def cc(src: Path) -> Path:
+        obj = odir / (src.relative_to(ROOT).as_posix().replace("/", "__") + ".o")
+        if _needs(obj, src, stamp):
+            _run([cxx] + flags + ["-c", str(src), "-o", str(obj)])
+            _mark(obj, src, stamp)
+        return obj
+
+    host = sorted((ROOT / "src").glob("*.cpp"))
+    tool_srcs = [ROOT / s for t in tools for s in TOOLS[t]]
+    with ThreadPoolExecutor(jobs) as ex:
+        objs = list(ex.map(cc, host + tool_srcs))
+    host_objs, tool_objs = objs[:len(host)], objs[len(host):]
+    kernels = [OBJ / (k.relative_to(ROOT).as_posix().replace("/", "__") + ".o")
+               for k in sorted((ROOT / "kernels").glob("*.cu"))]
+    out: dict[str, Path] = {}
+    i = 0
+    for t in tools:
+        n = len(TOOLS[t])
+        exe = bdir / t
+        _run([cxx, f"-fsanitize={kind}", "-pthread", "-o", str(exe)] + [str(o) for o in tool_objs[i:i + n]] +
+             [str(o) for o in host_objs] + [str(k) for k in kernels] +
+             [f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static", "-ldl", "-lrt"])
+        out[t] = exe
+        i += n
+    return out
+
+
 if __name__ == "__main__":
     p = build(verbose=True)
     print(p)

@@ -15,6 +15,7 @@
 #include <cstring>
 #include <iostream>
 #include <map>
+#include <mutex>
 #include <random>
 #include <string>
 #include <thread>
@@ -184,22 +185,30 @@ class HangWatchdog {
  public:
   explicit HangWatchdog(double seconds) : limit_(seconds), th_([this] { loop(); }) {}
   ~HangWatchdog() { stop_ = true; th_.join(); }
-  void arm(const std::string& what) { what_ = what; t0_ = now(); armed_ = true; }
+  void arm(const std::string& what) {
+    std::lock_guard<std::mutex> g(m_);
+    what_ = what;
+    t0_ = now();
+    armed_ = true;
+  }
   void disarm() { armed_ = false; }
  private:
   static double now() { return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
   void loop() {
     while (!stop_) {
+      std::unique_lock<std::mutex> g(m_);
       if (armed_ && now() - t0_ > limit_) {
         fprintf(stderr, "hang watchdog: '%s' exceeded %.0f s, aborting\n", what_.c_str(), limit_);
         fflush(stderr);
         _exit(86);
       }
+      g.unlock();
       std::this_thread::sleep_for(std::chrono::milliseconds(50));
     }
   }
   double limit_;
   std::atomic<bool> stop_{false}, armed_{false};
+  std::mutex m_;
   std::string what_;
   double t0_ = 0;
   std::thread th_;

@@ -9,6 +9,7 @@
 #include <sstream>
 #include <atomic>
 #include <cstdio>
+#include <mutex>
 #include <thread>
 
 #include "Al.hpp"
@@ -124,8 +125,18 @@ static void test_pool() {
 }
 
 // A state that records when it ran and finishes after a number of steps.
+// Completion log shared between the engine thread (writer) and the test (reader).
+struct ProbeLog {
+  void push(int id) { std::lock_guard<std::mutex> g(m); ids.push_back(id); }
+  size_t size() { std::lock_guard<std::mutex> g(m); return ids.size(); }
+  int at(size_t i) { std::lock_guard<std::mutex> g(m); return ids[i]; }
+  void clear() { std::lock_guard<std::mutex> g(m); ids.clear(); }
+  std::mutex m;
+  std::vector<int> ids;
+};
+
 struct ProbeState : AlState {
-  ProbeState(const void* key, int id, int steps, std::vector<int>* log, std::atomic<int>* running, std::atomic<int>* peak,
+  ProbeState(const void* key, int id, int steps, ProbeLog* log, std::atomic<int>* running, std::atomic<int>* peak,
              RunType rt = RunType::bounded, bool advance = false)
       : key_(key), id_(id), left_(steps), log_(log), running_(running), peak_(peak), rt_(rt), adv_(advance) {}
   void start() override {
@@ -136,7 +147,7 @@ struct ProbeState : AlState {
   PEAction step() override {
     if (adv_ && !advanced_) { advanced_ = true; return PEAction::advance; }
     if (--left_ > 0) return PEAction::cont;
-    log_->push_back(id_);
+    log_->push(id_);
     --*running_;
     return PEAction::complete;
   }
@@ -145,7 +156,7 @@ struct ProbeState : AlState {
   const char* get_name() const override { return "Probe"; }
   const void* key_;
   int id_, left_;
-  std::vector<int>* log_;
+  ProbeLog* log_;
   std::atomic<int>*running_, *peak_;
   RunType rt_;
   bool adv_, advanced_ = false;
@@ -153,14 +164,14 @@ struct ProbeState : AlState {
 
 static void test_progress_engine() {
   ProgressEngine pe;
-  std::vector<int> log;
+  ProbeLog log;
   std::atomic<int> running{0}, peak{0};
   int k1, k2;
   // Same stream: bounded states beyond the limit wait; completion order of equal-length states is FIFO.
   for (int i = 0; i < 12; ++i) pe.enqueue(new ProbeState(&k1, i, 200, &log, &running, &peak));
   while (pe.in_flight() || log.size() < 12) std::this_thread::yield();
   CHECK(peak.load() <= std::max(1, tuning().pe_num_concurrent_ops));
-  for (int i = 0; i < 12; ++i) CHECK(log[(size_t)i] == i);
+  for (int i = 0; i < 12; ++i) CHECK(log.at((size_t)i) == i);
   // Unbounded states are all admitted at once.
   log.clear(); peak = 0;
   for (int i = 0; i < 10; ++i) pe.enqueue(new ProbeState(&k2, i, 2000, &log, &running, &peak, RunType::unbounded));

@@ -137,6 +137,16 @@ class HostComm:
     def split(self, color: int, key: int) -> "HostComm":
         return HostComm(check_ptr(self._lib.al_host_comm_split(self._h, color, key)))
 
+    def stats(self) -> dict:
+        """Counters of this rank: collectives, p2p_ops, bytes contributed or sent, failures."""
+        out = (C.c_uint64 * 4)()
+        check(self._lib.al_host_comm_stats(self._h, out))
+        return dict(zip(["collectives", "p2p_ops", "bytes", "failures"], [int(v) for v in out]))
+
+    def abort(self, why: str = "aborted by the caller") -> None:
+        """Fail the communicator on this rank: operations in flight end with an error, later calls raise."""
+        check(self._lib.al_host_comm_abort(self._h, why.encode()))
+
     def close(self) -> None:
         if self._h:
             self._lib.al_host_comm_destroy(self._h)

@@ -69,6 +69,10 @@ class DeviceComm:
     def set_timeout_ms(self, ms: float) -> None:
         check(self._lib.al_dev_comm_set_timeout_ms(self._h, float(ms)))
 
+    def abort(self, why: str = "aborted by the caller") -> None:
+        """Make every later call on this communicator raise; recovery is a new communicator."""
+        check(self._lib.al_dev_comm_abort(self._h, why.encode()))
+
     def stats(self) -> dict:
         out = (C.c_uint64 * 8)()
         check(self._lib.al_dev_comm_stats(self._h, out))

@@ -43,6 +43,10 @@ void* al_host_comm_split(void* comm, int color, int key);
 void al_host_comm_destroy(void* comm);
 int al_host_comm_rank(void* comm);
 int al_host_comm_size(void* comm);
+/** Fills out[0..3]: collectives, p2p_ops, bytes, failures. */
+int al_host_comm_stats(void* comm, uint64_t* out);
+/** Puts the communicator into the failed state on this rank (why may be NULL). */
+int al_host_comm_abort(void* comm, const char* why);
 /**
  * kind: OpKind.  inplace != 0 selects the in-place form on `recv`.
  * vector != 0 uses the count / displacement arrays (entries per rank; unused ones may be NULL).
@@ -69,6 +73,8 @@ int al_dev_comm_nlocal(void* comm);
 int al_dev_comm_has_multicast(void* comm);
 const char* al_dev_comm_backing(void* comm);
 int al_dev_comm_set_timeout_ms(void* comm, double ms);
+/** Every later call on the communicator fails (why may be NULL). */
+int al_dev_comm_abort(void* comm, const char* why);
 /** Fills out[0..7]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy. */
 int al_dev_comm_stats(void* comm, uint64_t* out);
 /** Status record: out[0]=code, [1]=rank, [2]=peer, [3]=where, [4]=epoch, [5]=seen. Never fails. */

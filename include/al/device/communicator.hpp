@@ -18,6 +18,7 @@
  */
 #pragma once
 #include <memory>
+#include <string>
 #include <vector>
 
 #include "al/bootstrap.hpp"
@@ -120,6 +121,13 @@ class DeviceCommunicator {
 
   /** Throws al_exception if a kernel of this communicator reported a failure. */
   void check_status() const;
+  /**
+   * Mark the communicator unusable on this rank: every later call throws.
+   * Kernels already enqueued still end by themselves (their waits are
+   * bounded).  Recovery is abort() on the surviving ranks followed by a new
+   * communicator; the reference has no equivalent.
+   */
+  void abort(const std::string& why = "aborted by the caller");
   /** Non-throwing form: copy of the status record. */
   internal::device::DeviceStatus status() const;
   internal::device::CommStats stats() const;

@@ -60,6 +60,14 @@ struct P2PItem {
   size_t bytes = 0;
 };
 
+/** Counters of one communicator (this rank's view). */
+struct CommStats {
+  uint64_t collectives = 0;  ///< collective calls accepted
+  uint64_t p2p_ops = 0;      ///< point-to-point calls accepted (a MultiSendRecv counts once)
+  uint64_t bytes = 0;        ///< payload bytes this rank contributed or sent
+  uint64_t failures = 0;     ///< operations that ended in an error (time-outs included)
+};
+
 }  // namespace host
 }  // namespace internal
 
@@ -96,6 +104,17 @@ class HostCommunicator {
   void collective(internal::host::CollArgs&& args, internal::host::Request* req);
   /** Start a set of sends/receives that progress together. */
   void p2p(std::vector<internal::host::P2PItem>&& items, internal::host::Request* req, const char* name);
+
+  /** Counters since creation. */
+  internal::host::CommStats stats() const;
+  /**
+   * Put the communicator into the failed state on this rank: operations in
+   * flight end with an error at their next progress step and later calls
+   * throw.  The reference has no recovery path; the documented one here is
+   * abort() on every surviving rank followed by a new communicator.
+   */
+  void abort(const std::string& why = "aborted by the caller");
+  bool failed() const;
 
   struct Impl;
   Impl* impl() const { return impl_.get(); }

@@ -50,6 +50,13 @@ struct Tuning {
   bool debug_checks = false;                   ///< AL_DEBUG: argument checks on every call
   bool signal_handler = true;                  ///< !AL_DISABLE_SIGNAL_HANDLER
 
+  // ---- host-side fault injection (tests only; nothing here touches a GPU) -------
+  int fault_rank = -1;                         ///< AL_FAULT_RANK: world rank that misbehaves (-1: nobody)
+  long fault_op = 0;                           ///< AL_FAULT_OP: which host collective of a communicator (1 = its first)
+  int fault_kind = 0;                          ///< AL_FAULT_KIND: 0 none, 1 the rank never signals that op, 2 it signals AL_FAULT_DELAY_MS late
+  long fault_delay_ms = 0;                     ///< AL_FAULT_DELAY_MS
+  long fault_jitter_us = 0;                    ///< AL_FAULT_JITTER_US: every rank sleeps a random time below this before each publish
+
   /** Re-read every AL_* environment variable. */
   void load_from_env();
   /** One "name = value" line per entry, for al_info. */

@@ -78,7 +78,7 @@ int al_info(char* buf, size_t buflen) {
   X(pe_num_concurrent_ops) X(pe_hang_seconds) X(host_stage_bytes) X(host_mailbox_bytes) X(host_wait_timeout_s) \
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
   X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
-  X(disable_background_streams)
+  X(disable_background_streams) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us)
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {
@@ -128,6 +128,15 @@ void* al_host_comm_split(void* comm, int color, int key) {
 void al_host_comm_destroy(void* comm) { delete (HostCommunicator*)comm; }
 int al_host_comm_rank(void* comm) { return ((HostCommunicator*)comm)->rank(); }
 int al_host_comm_size(void* comm) { return ((HostCommunicator*)comm)->size(); }
+int al_host_comm_stats(void* comm, uint64_t* out) {
+  return guard([&] {
+    host::CommStats s = ((HostCommunicator*)comm)->stats();
+    out[0] = s.collectives; out[1] = s.p2p_ops; out[2] = s.bytes; out[3] = s.failures;
+  });
+}
+int al_host_comm_abort(void* comm, const char* why) {
+  return guard([&] { ((HostCommunicator*)comm)->abort(why ? why : "aborted by the caller"); });
+}
 
 int al_host_collective(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op, int root,
                        int inplace, int vector, const size_t* sc, const size_t* sd, const size_t* rc, const size_t* rd,
@@ -212,6 +221,9 @@ int al_dev_comm_has_multicast(void* comm) { return ((DeviceCommunicator*)comm)->
 const char* al_dev_comm_backing(void* comm) { return ((DeviceCommunicator*)comm)->memory_backing(); }
 int al_dev_comm_set_timeout_ms(void* comm, double ms) {
   return guard([&] { ((DeviceCommunicator*)comm)->set_wait_timeout_ms(ms); });
+}
+int al_dev_comm_abort(void* comm, const char* why) {
+  return guard([&] { ((DeviceCommunicator*)comm)->abort(why ? why : "aborted by the caller"); });
 }
 int al_dev_comm_stats(void* comm, uint64_t* out) {
   return guard([&] {

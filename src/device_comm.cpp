@@ -3,6 +3,7 @@
 #include "al/device/communicator.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "al/device/kernels.hpp"
@@ -32,6 +33,8 @@ struct DeviceCommunicator::Impl {
   std::vector<uint64_t> p2p_sent, p2p_recvd;  // [nlocal][p]
   std::vector<std::unique_ptr<SymmBlock>> user_blocks;
   CommStats stats;
+  std::atomic<bool> aborted{false};
+  std::string abort_msg;
   std::mutex mu;
 
   size_t off_stage() const { return FlagLayout::bytes; }
@@ -157,7 +160,14 @@ DeviceStatus DeviceCommunicator::status() const {
   return s;
 }
 
+void DeviceCommunicator::abort(const std::string& why) {
+  std::lock_guard<std::mutex> lock(impl_->mu);
+  if (!impl_->aborted.load()) { impl_->abort_msg = why; impl_->aborted.store(true); }
+}
+
 void DeviceCommunicator::check_status() const {
+  if (impl_->aborted.load(std::memory_order_acquire))
+    throw_al_exception("device communicator aborted: ", impl_->abort_msg, "; create a new one");
   const uint32_t code = __atomic_load_n(&impl_->status_host->code, __ATOMIC_ACQUIRE);
   if (code == kStatusOk) return;
   DeviceStatus s = status();

@@ -24,6 +24,8 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <chrono>
+#include <random>
 #include <thread>
 
 #include "al/host/reduce.hpp"
@@ -138,6 +140,7 @@ struct HostCommunicator::Impl {
   std::atomic<uint64_t> done_seq{0};   // last collective that finished locally
   std::vector<std::atomic<uint64_t>> send_next, send_serving, recv_next, recv_serving;
   std::atomic<bool> failed{false};
+  std::atomic<uint64_t> n_coll{0}, n_p2p{0}, n_bytes{0}, n_fail{0};
   std::string fail_msg;
   std::mutex fail_mu;
   // Local shadows of the mailbox counters this rank owns as a writer.
@@ -178,6 +181,10 @@ class HostState : public AlState {
  protected:
   /** Returns true (and records the failure) when the current wait exceeded the limit. */
   bool timed_out(const char* what) {
+    if (ci_->failed.load(std::memory_order_acquire) && !failed_) {
+      fail("communicator failed: " + ci_->fail_msg);
+      return true;
+    }
     const double now = get_time();
     if (wait_since_ == 0) { wait_since_ = now; return false; }
     if (now - wait_since_ > tuning().host_wait_timeout_s) {
@@ -189,6 +196,7 @@ class HostState : public AlState {
   void progress_made() { wait_since_ = 0; }
   void fail(const std::string& msg) {
     ci_->fail(msg);
+    ci_->n_fail.fetch_add(1, std::memory_order_relaxed);
     if (req_) { req_->error = msg; req_->status.store(2, std::memory_order_release); }
     failed_ = true;
   }
@@ -245,6 +253,7 @@ class CollState final : public HostState {
           phase_ = Phase::publish;
           break;
         case Phase::publish: {
+          if (!inject_fault()) return done();
           const int par = (int)((seq_ + c_) & 1);
           publish(c_, par);
           if (c_ == 0) {
@@ -312,6 +321,22 @@ class CollState final : public HostState {
 
  private:
   enum class Phase { gate, publish, wait_a, wait_b, next_chunk, wait_c };
+
+  /** Host-side fault injection (Tuning::fault_*).  Returns false when this rank drops out of the op. */
+  bool inject_fault() {
+    const Tuning& t = tuning();
+    if (t.fault_jitter_us > 0) {
+      static thread_local std::minstd_rand rng((unsigned)(me_ * 7919 + 17));
+      std::this_thread::sleep_for(std::chrono::microseconds((long)(rng() % (unsigned long)t.fault_jitter_us)));
+    }
+    if (t.fault_kind == 0 || c_ != 0 || get_world()->rank() != t.fault_rank || (long)seq_ != t.fault_op) return true;
+    if (t.fault_kind == 2) {
+      std::this_thread::sleep_for(std::chrono::milliseconds(t.fault_delay_ms));
+      return true;
+    }
+    fail(build_string(get_name(), ": injected fault, rank ", me_, " does not signal operation ", seq_));
+    return false;
+  }
 
   PEAction done() {
     // Even a failed op releases the gate so that later ops can observe the failure.
@@ -605,6 +630,15 @@ void HostCommunicator::collective(CollArgs&& args, Request* req) {
       throw_al_exception("reduction ", reduction_name(args.op), " is not defined for ", dtype_name(args.dt));
   }
   const uint64_t seq = ci->next_seq.fetch_add(1);
+  ci->n_coll.fetch_add(1, std::memory_order_relaxed);
+  {
+    size_t elems = args.count;
+    if (args.vector) { elems = 0; for (size_t c : args.send_counts) elems += c; }
+    else if (args.kind == Coll::alltoall || args.kind == Coll::scatter || args.kind == Coll::reduce_scatter)
+      elems *= (size_t)ci->p;
+    if (args.send || args.kind == Coll::allreduce)
+      ci->n_bytes.fetch_add(elems * dtype_size(args.dt), std::memory_order_relaxed);
+  }
   if (req) {
     *req = std::make_shared<ReqState>();
     get_progress_engine()->enqueue(new CollState(ci, std::move(args), *req, seq));
@@ -639,6 +673,9 @@ void HostCommunicator::p2p(std::vector<P2PItem>&& items, Request* req, const cha
   }
   for (auto& it : items)
     if (it.peer < 0 || it.peer >= ci->p) throw_al_exception("point-to-point peer ", it.peer, " out of range");
+  ci->n_p2p.fetch_add(1, std::memory_order_relaxed);
+  for (auto& it : items)
+    if (it.is_send) ci->n_bytes.fetch_add(it.bytes, std::memory_order_relaxed);
   if (req) {
     *req = std::make_shared<ReqState>();
     auto* st = new P2PState(ci, std::move(items), *req, name);
@@ -652,5 +689,18 @@ void HostCommunicator::p2p(std::vector<P2PItem>&& items, Request* req, const cha
     if (r->status.load() == 2) throw_al_exception(r->error);
   }
 }
+
+internal::host::CommStats HostCommunicator::stats() const {
+  internal::host::CommStats s;
+  s.collectives = impl_->n_coll.load();
+  s.p2p_ops = impl_->n_p2p.load();
+  s.bytes = impl_->n_bytes.load();
+  s.failures = impl_->n_fail.load();
+  return s;
+}
+
+void HostCommunicator::abort(const std::string& why) { impl_->fail(why); }
+
+bool HostCommunicator::failed() const { return impl_->failed.load(); }
 
 }  // namespace Al

@@ -39,6 +39,11 @@ void Tuning::load_from_env() {
   trace = env_long("AL_TRACE", trace) != 0;
   debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
   signal_handler = env_long("AL_DISABLE_SIGNAL_HANDLER", 0) == 0;
+  fault_rank = (int)env_long("AL_FAULT_RANK", fault_rank);
+  fault_op = env_long("AL_FAULT_OP", fault_op);
+  fault_kind = (int)env_long("AL_FAULT_KIND", fault_kind);
+  fault_delay_ms = env_long("AL_FAULT_DELAY_MS", fault_delay_ms);
+  fault_jitter_us = env_long("AL_FAULT_JITTER_US", fault_jitter_us);
   if (max_ctas < 1) max_ctas = 1;
   if (max_ctas > AL_MAX_CTAS) max_ctas = AL_MAX_CTAS;
   if (max_ctas_nvls < 1) max_ctas_nvls = 1;
@@ -85,7 +90,12 @@ std::string Tuning::describe() const {
      << "threads_per_cta = " << threads_per_cta << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
-     << "signal_handler = " << signal_handler << "\n";
+     << "signal_handler = " << signal_handler << "\n"
+     << "fault_rank = " << fault_rank << "\n"
+     << "fault_op = " << fault_op << "\n"
+     << "fault_kind = " << fault_kind << "\n"
+     << "fault_delay_ms = " << fault_delay_ms << "\n"
+     << "fault_jitter_us = " << fault_jitter_us << "\n";
   return ss.str();
 }
 

@@ -135,3 +135,26 @@ def test_info_and_tuning_from_python(built_lib):
     al.set_tuning("max_ctas", old)
     with pytest.raises(al.AlError):
         al.set_tuning("no_such_entry", 1)
+
+
+def test_injected_missing_signal_times_out_and_recovers(bin_dir):
+    env = {"AL_HOST_WAIT_TIMEOUT_S": "1", "AL_FAULT_RANK": "1", "AL_FAULT_OP": "2", "AL_FAULT_KIND": "1"}
+    r = run([bin_dir / "alrun", "-n", "3", "--timeout", "120", sys.executable, W / "host_inject.py", "skip"], env=env)
+    assert r.returncode == 0 and r.stdout.count("recovered") == 3, r.stdout + r.stderr
+
+
+def test_injected_delay_is_tolerated(bin_dir):
+    env = {"AL_FAULT_RANK": "1", "AL_FAULT_OP": "2", "AL_FAULT_KIND": "2", "AL_FAULT_DELAY_MS": "300"}
+    r = run([bin_dir / "alrun", "-n", "3", "--timeout", "120", sys.executable, W / "host_inject.py", "delay"], env=env)
+    assert r.returncode == 0 and r.stdout.count("delayed op ok") == 3, r.stdout + r.stderr
+
+
+def test_abort_ends_pending_requests(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "2", "--timeout", "120", sys.executable, W / "host_inject.py", "abort"])
+    assert r.returncode == 0 and r.stdout.count("abort ok") == 2, r.stdout + r.stderr
+
+
+def test_random_delays_between_ranks_do_not_change_results(bin_dir):
+    env = {"AL_FAULT_JITTER_US": "300"}
+    r = run([bin_dir / "alrun", "-n", "4", "--timeout", "200", sys.executable, W / "host_inject.py", "jitter"], env=env)
+    assert r.returncode == 0 and r.stdout.count("jitter ok") == 4, r.stdout + r.stderr

@@ -4,6 +4,7 @@
 //   alrun -n 4 test_ops --backend host|device|ht --op allreduce --datatype float
 //         [--inplace] [--nonblocking] [--reduction-op sum] [--root 0]
 //         [--size N | --min-size A --max-size B] [--odd-sizes] [--zero] [--trials K]
+//         [--threads N] [--permute 2,0,1,...]
 //
 // Parity: test/test_ops.cpp (driver), test/op_runner.hpp (per-op buffer
 // conventions).  The reference's oracle is MPI itself; here every rank can
@@ -302,9 +303,81 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
   throw_al_exception("unknown op ", c.op);
 }
 
+/** A communicator for one test thread: same ranks, its own stream where the backend has streams. */
+template <typename Backend>
+typename Backend::comm_type make_thread_comm(const typename Backend::comm_type& comm) {
+  if constexpr (std::is_same<typename Backend::comm_type, Al::HostCommunicator>::value) {
+    return comm.copy();
+  } else {
+#ifdef AL_HAS_CUDA
+    cudaStream_t s = nullptr;
+    AL_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    return comm.copy(s);
+#else
+    return comm.copy();
+#endif
+  }
+}
+
+template <typename Backend>
+void release_thread_comm(typename Backend::comm_type& comm) {
+  if constexpr (!std::is_same<typename Backend::comm_type, Al::HostCommunicator>::value) {
+#ifdef AL_HAS_CUDA
+    cudaStream_t s = comm.get_stream();
+    AL_CHECK_CUDA(cudaStreamSynchronize(s));
+    { typename Backend::comm_type dying = std::move(comm); }
+    AL_CHECK_CUDA(cudaStreamDestroy(s));
+#endif
+  }
+}
+
+/** Runs every size of the sweep on one communicator; returns the number of failed sizes (stops at the first). */
+template <typename Backend, typename T>
+int sweep(typename Backend::comm_type& comm, Case c, const std::vector<size_t>& sizes, long trials, HangWatchdog& dog) {
+  for (size_t n : sizes) {
+    for (long t = 0; t < trials; ++t) {
+      c.n = n;
+      dog.arm(c.op + " size " + std::to_string(n));
+      bool ok = false;
+      try {
+        ok = run_case<Backend, T>(c, comm);
+      } catch (const std::exception& e) {
+        fprintf(stderr, "[rank %d] %s size %zu threw: %s\n", comm.rank(), c.op.c_str(), n, e.what());
+      }
+      dog.disarm();
+      if (!ok) return 1;
+    }
+  }
+  return 0;
+}
+
+/** "--permute 2,0,1": rank i of the world becomes rank list[i] of the tested communicator. */
+inline std::vector<int> parse_permutation(const std::string& s, int size) {
+  std::vector<int> perm;
+  size_t pos = 0;
+  while (pos <= s.size()) {
+    const size_t comma = s.find(',', pos);
+    const std::string tok = s.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos);
+    if (!tok.empty()) perm.push_back(std::stoi(tok));
+    if (comma == std::string::npos) break;
+    pos = comma + 1;
+  }
+  if ((int)perm.size() != size) throw_al_exception("--permute wants ", size, " entries, got ", perm.size());
+  std::vector<int> seen((size_t)size, 0);
+  for (int v : perm) {
+    if (v < 0 || v >= size || seen[(size_t)v]++) throw_al_exception("--permute is not a permutation of 0..", size - 1);
+  }
+  return perm;
+}
+
 template <typename Backend, typename T>
 int run_all(const Args& a) {
-  typename Backend::comm_type comm;
+  typename Backend::comm_type world;
+  // Tested communicator: the world, or the world with its ranks permuted
+  // (test/test_utils.hpp:308-334 of the reference does the same with MPI_Comm_split).
+  typename Backend::comm_type comm = a.has("permute")
+      ? world.split(1, parse_permutation(a.str("permute", ""), world.size())[(size_t)world.rank()])
+      : world.copy();
   HangWatchdog dog((double)a.num("hang-timeout", 60));
   Case c;
   c.op = a.str("op", "allreduce");
@@ -320,25 +393,29 @@ int run_all(const Args& a) {
     for (long t = 0; t < trials; ++t) { typename Backend::comm_type extra = comm.copy(); (void)extra; }
     return 0;
   }
+  const int nthreads = (int)a.num("threads", 1);
   int failed = 0;
-  for (size_t n : sizes) {
-    for (long t = 0; t < trials; ++t) {
-      c.n = n;
-      dog.arm(c.op + " size " + std::to_string(n));
-      bool ok = false;
-      try {
-        ok = run_case<Backend, T>(c, comm);
-      } catch (const std::exception& e) {
-        fprintf(stderr, "[rank %d] %s size %zu threw: %s\n", comm.rank(), c.op.c_str(), n, e.what());
-      }
-      dog.disarm();
-      if (!ok) { ++failed; break; }
-    }
-    if (failed) break;
+  if (nthreads <= 1) {
+    failed = sweep<Backend, T>(comm, c, sizes, trials, dog);
+  } else {
+    // Thread-multiple: one communicator per thread (created here, in the same
+    // order on every rank), all threads inside the library at once.  Two
+    // threads never share a communicator (test/test_ops.cpp:373-391 of the reference).
+    std::vector<typename Backend::comm_type> comms;
+    for (int t = 0; t < nthreads; ++t) comms.push_back(make_thread_comm<Backend>(comm));
+    std::vector<int> rc((size_t)nthreads, 0);
+    std::vector<std::thread> th;
+    for (int t = 0; t < nthreads; ++t)
+      th.emplace_back([&, t] { rc[(size_t)t] = sweep<Backend, T>(comms[(size_t)t], c, sizes, trials, dog); });
+    for (auto& x : th) x.join();
+    for (int r : rc) failed += r;
+    for (auto& cm : comms) release_thread_comm<Backend>(cm);
   }
   if (comm.rank() == 0 && !a.has("quiet"))
-    printf("%s %s %s%s%s sizes=%zu ranks=%d: %s\n", Backend::Name().c_str(), c.op.c_str(), a.str("datatype", "float").c_str(),
-           c.inplace ? " inplace" : "", c.nonblocking ? " nonblocking" : "", sizes.size(), comm.size(), failed ? "FAIL" : "ok");
+    printf("%s %s %s%s%s%s sizes=%zu ranks=%d%s: %s\n", Backend::Name().c_str(), c.op.c_str(),
+           a.str("datatype", "float").c_str(), c.inplace ? " inplace" : "", c.nonblocking ? " nonblocking" : "",
+           a.has("permute") ? " permuted" : "", sizes.size(), comm.size(),
+           nthreads > 1 ? (" threads=" + std::to_string(nthreads)).c_str() : "", failed ? "FAIL" : "ok");
   return failed;
 }
 

@@ -188,6 +188,28 @@ static void test_progress_engine() {
   CHECK(!pe.is_running());
 }
 
+// Several user threads hand their first state to an engine that is not running yet:
+// exactly one of them may create the thread, the others wait for it.
+static void test_progress_engine_concurrent_start() {
+  for (int round = 0; round < 20; ++round) {
+    ProgressEngine pe;
+    ProbeLog log;
+    std::atomic<int> running{0}, peak{0}, go{0};
+    int keys[4];
+    std::vector<std::thread> th;
+    for (int t = 0; t < 4; ++t)
+      th.emplace_back([&, t] {
+        while (!go.load()) std::this_thread::yield();
+        for (int i = 0; i < 8; ++i) pe.enqueue(new ProbeState(&keys[t], t * 8 + i, 5, &log, &running, &peak));
+      });
+    go = 1;
+    for (auto& x : th) x.join();
+    while (log.size() < 32) std::this_thread::yield();
+    pe.stop();
+    CHECK(log.size() == 32);
+  }
+}
+
 static void test_reduce_and_halves() {
   using namespace Al::internal::host;
   for (float f : {0.f, 1.f, -2.5f, 65504.f, 6.1e-5f, 1e-7f, 0.333f}) {
@@ -260,6 +282,7 @@ int main() {
   test_allocator();
   test_pool();
   test_progress_engine();
+  test_progress_engine_concurrent_start();
   test_reduce_and_halves();
   test_lifecycle_and_trace();
   if (g_fail) { fprintf(stderr, "%d check(s) failed\n", g_fail); return 1; }

@@ -31,6 +31,10 @@ class HostTransferCommunicator {
   HostTransferCommunicator copy(cudaStream_t stream = nullptr) const {
     return HostTransferCommunicator(host_.group(), stream);
   }
+  /** MPI_Comm_split analogue (collective). */
+  HostTransferCommunicator split(int color, int key, cudaStream_t stream = nullptr) const {
+    return HostTransferCommunicator(host_.group().split(color, key), stream);
+  }
   int rank() const { return host_.rank(); }
   int size() const { return host_.size(); }
   int local_rank() const { return host_.local_rank(); }

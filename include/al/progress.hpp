@@ -77,6 +77,7 @@ class ProgressEngine {
   std::atomic<bool> started_{false};
   std::atomic<bool> stop_flag_{false};
   std::mutex start_mu_;
+  bool starting_ = false;  ///< a caller is inside run() creating the thread (guarded by start_mu_)
   std::condition_variable start_cv_;
   bool thread_ready_ = false;
 

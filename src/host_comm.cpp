@@ -194,15 +194,27 @@ class HostState : public AlState {
     return false;
   }
   void progress_made() { wait_since_ = 0; }
+  // The outcome reaches the request only in publish_outcome(), the last thing a
+  // state does: once the request is complete its owner may destroy the
+  // communicator, so nothing of *ci_ may be touched afterwards.
   void fail(const std::string& msg) {
     ci_->fail(msg);
     ci_->n_fail.fetch_add(1, std::memory_order_relaxed);
-    if (req_) { req_->error = msg; req_->status.store(2, std::memory_order_release); }
+    err_ = msg;
     failed_ = true;
   }
-  void finish_ok() {
-    if (req_) req_->status.store(1, std::memory_order_release);
+  void publish_outcome() {
+    if (!req_ || published_) return;
+    published_ = true;
+    if (failed_) {
+      req_->error = err_;
+      req_->status.store(2, std::memory_order_release);
+    } else {
+      req_->status.store(1, std::memory_order_release);
+    }
   }
+  std::string err_;
+  bool published_ = false;
   HostCommunicator::Impl* ci_;
   Request req_;
   double wait_since_ = 0;
@@ -240,7 +252,7 @@ class CollState final : public HostState {
   std::string get_desc() const override { return build_string("seq=", seq_, " count=", a_.count, " chunk=", c_); }
 
   PEAction step() override {
-    if (failed_) return PEAction::complete;
+    if (failed_) { publish_outcome(); return PEAction::complete; }
     for (;;) {
       switch (phase_) {
         case Phase::gate:
@@ -306,14 +318,12 @@ class CollState final : public HostState {
             phase_ = Phase::wait_c;
             break;
           }
-          finish_ok();
           return done();
         case Phase::wait_c:
           if (!all_reached(&Workspace::C, epoch(seq_, 1))) {
             if (timed_out("the closing barrier")) return done();
             return PEAction::cont;
           }
-          finish_ok();
           return done();
       }
     }
@@ -341,6 +351,7 @@ class CollState final : public HostState {
   PEAction done() {
     // Even a failed op releases the gate so that later ops can observe the failure.
     ci_->done_seq.store(seq_, std::memory_order_release);
+    publish_outcome();
     return PEAction::complete;
   }
 
@@ -530,7 +541,7 @@ class P2PState final : public HostState {
   RunType get_run_type() const override { return RunType::unbounded; }
 
   PEAction step() override {
-    if (failed_) return PEAction::complete;
+    if (failed_) { publish_outcome(); return PEAction::complete; }
     bool all_done = true, moved = false;
     const size_t slot = ws_.lay().slot;
     const int me = ci_->me;
@@ -571,7 +582,7 @@ class P2PState final : public HostState {
       }
     }
     if (all_done) {
-      finish_ok();
+      publish_outcome();
       return PEAction::complete;
     }
     if (moved) progress_made();
@@ -582,6 +593,7 @@ class P2PState final : public HostState {
           auto& serving = x.item.is_send ? ci_->send_serving : ci_->recv_serving;
           if (serving[(size_t)x.item.peer].load() == x.ticket) serving[(size_t)x.item.peer].store(x.ticket + 1);
         }
+      publish_outcome();
       return PEAction::complete;
     }
     return PEAction::cont;

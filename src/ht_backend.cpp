@@ -75,6 +75,12 @@ class HTState final : public AlState {
         return PEAction::advance;
       case 1:
         launch_host();  // non-blocking host operation driven by the same engine
+        // A rank that receives nothing (non-root of reduce / gather, root of
+        // scatter with no slice, a pure send) only had to get its data off the
+        // device: its stream is released now instead of after the exchange
+        // (the reference signals such ranks early too, e.g.
+        // include/aluminum/ht/reduce.hpp and ht/gather.hpp).
+        if (early_release_) wait.signal();
         phase_ = 2;
         return PEAction::cont;
       case 2:
@@ -83,7 +89,7 @@ class HTState final : public AlState {
         } catch (const al_exception& e) {
           std::cerr << "[al] host-transfer operation failed: " << e.what() << "\n";
         }
-        wait.signal();  // release the stream: H2D copy and end flag follow
+        if (!early_release_) wait.signal();  // release the stream: H2D copy and end flag follow
         phase_ = 3;
         return PEAction::cont;
       default:
@@ -102,6 +108,7 @@ class HTState final : public AlState {
   HostBackend::req_type host_req;
   std::function<void(HostBackend::req_type*)> launcher;
   bool unbounded_ = false;
+  bool early_release_ = false;  ///< nothing comes back to the device: do not hold the stream during the exchange
 
  private:
   void launch_host() { launcher(&host_req); }
@@ -128,6 +135,7 @@ void run_collective(Resolved&& r, HostTransferCommunicator& comm, cudaStream_t s
   st->wait.wait(stream);
   if (hrecv) AL_CHECK_CUDA(cudaMemcpyAsync(drecv, hrecv, e.recv_elems * esz, cudaMemcpyHostToDevice, stream));
   st->end_flag.record(stream);
+  st->early_release_ = hrecv == nullptr && r.kind != OpKind::barrier;  // a barrier holds the stream by definition
 
   auto shared = std::make_shared<Resolved>(std::move(r));
   shared->send = hsend;
@@ -162,6 +170,7 @@ void run_p2p(std::vector<host::P2PItem>&& items, HostTransferCommunicator& comm,
   for (auto& b : backs)
     if (b.bytes) AL_CHECK_CUDA(cudaMemcpyAsync(b.dev, b.host, b.bytes, cudaMemcpyHostToDevice, stream));
   st->end_flag.record(stream);
+  st->early_release_ = backs.empty();
   auto shared = std::make_shared<std::vector<host::P2PItem>>(std::move(items));
   HostCommunicator* hc = &comm.host();
   st->launcher = [shared, hc, name](HostBackend::req_type* req) {

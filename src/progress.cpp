@@ -36,11 +36,19 @@ ProgressEngine::~ProgressEngine() {
 void ProgressEngine::run() {
   std::unique_lock<std::mutex> lk(start_mu_);
   if (started_.load(std::memory_order_acquire)) return;
+  if (starting_) {
+    // Another caller is bringing the thread up (its wait below released the lock): wait for it.
+    start_cv_.wait(lk, [this] { return started_.load(std::memory_order_acquire); });
+    return;
+  }
+  starting_ = true;
   stop_flag_.store(false);
   thread_ready_ = false;
   thread_ = std::thread(&ProgressEngine::engine, this);
   start_cv_.wait(lk, [this] { return thread_ready_; });
   started_.store(true, std::memory_order_release);
+  starting_ = false;
+  start_cv_.notify_all();
 }
 
 void ProgressEngine::stop() {

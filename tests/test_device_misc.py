@@ -163,7 +163,8 @@ def test_data_parallel_single_gpu_matches_torch(al):
     assert len(losses) == 3 and tr.h2d_bytes > 0 and tr.d2h_bytes == 12
 
 
-@pytest.mark.parametrize("op", ["allreduce", "alltoall", "bcast", "sendrecv", "gatherv"])
+@pytest.mark.parametrize("op", ["allreduce", "alltoall", "bcast", "sendrecv", "gatherv", "reduce", "scatter", "send",
+                                "barrier"])
 def test_host_transfer_backend(al, bin_dir, op):
     """GPU buffers staged through pinned memory, ranks as two processes sharing this GPU
     (no kernel of one rank waits for the other: the stream waits are released by the host)."""
@@ -171,6 +172,16 @@ def test_host_transfer_backend(al, bin_dir, op):
                         "--backend", "ht", "--op", op, "--max-size", "65536", "--odd-sizes", "--nonblocking"],
                        capture_output=True, text=True, timeout=180, env={**__import__("os").environ, "AL_GPU_ID": "0"})
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_host_transfer_backend_threads_and_permuted_ranks(al, bin_dir):
+    """Two user threads per rank, each with its own stream and communicator, on a communicator
+    whose ranks are swapped; the progress thread serves both streams."""
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", "2", "--timeout", "120", str(bin_dir / "test_ops"),
+                        "--backend", "ht", "--op", "allreduce", "--max-size", "16384", "--threads", "2",
+                        "--permute", "1,0", "--nonblocking"],
+                       capture_output=True, text=True, timeout=180, env={**__import__("os").environ, "AL_GPU_ID": "0"})
+    assert r.returncode == 0 and "threads=2: ok" in r.stdout, r.stdout + r.stderr
 
 
 def test_single_gpu_tools(al, bin_dir):

@@ -158,3 +158,22 @@ def test_random_delays_between_ranks_do_not_change_results(bin_dir):
     env = {"AL_FAULT_JITTER_US": "300"}
     r = run([bin_dir / "alrun", "-n", "4", "--timeout", "200", sys.executable, W / "host_inject.py", "jitter"], env=env)
     assert r.returncode == 0 and r.stdout.count("jitter ok") == 4, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("op", ["allreduce", "reduce_scatter", "alltoallv", "bcast", "sendrecv", "multisendrecv"])
+def test_thread_multiple(bin_dir, op):
+    """Three user threads per rank, each on its own communicator, all inside the library at once."""
+    for extra in ([], ["--nonblocking"]):
+        r = run([bin_dir / "alrun", "-n", "4", "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", op,
+                 "--threads", "3", "--max-size", "8192", "--odd-sizes"] + extra)
+        assert r.returncode == 0 and "threads=3: ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("op", ["allreduce", "gather", "scatterv", "send"])
+def test_permuted_ranks(bin_dir, op):
+    r = run([bin_dir / "alrun", "-n", "4", "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", op,
+             "--permute", "2,0,3,1", "--root", "3", "--max-size", "8192"])
+    assert r.returncode == 0 and "permuted" in r.stdout and ": ok" in r.stdout, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "3", "--timeout", "60", bin_dir / "test_ops", "--backend", "host", "--op", op,
+             "--permute", "2,0,0"])
+    assert r.returncode != 0 and "not a permutation" in r.stderr, r.stdout + r.stderr

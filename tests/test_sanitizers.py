@@ -44,6 +44,17 @@ def test_host_backend_is_race_free(tsan_tools, bin_dir, op):
     assert _clean(out), out[-3000:]
 
 
+@pytest.mark.parametrize("op", ["allreduce", "alltoall", "sendrecv"])
+def test_thread_multiple_is_race_free(tsan_tools, bin_dir, op):
+    """Three user threads per rank plus the progress thread, non-blocking, under ThreadSanitizer."""
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", "2", "--timeout", "300", str(tsan_tools["test_ops"]),
+                        "--backend", "host", "--op", op, "--threads", "3", "--nonblocking", "--max-size", "4096"],
+                       capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and ": ok" in out, out[-3000:]
+    assert _clean(out), out[-3000:]
+
+
 @pytest.fixture(scope="module")
 def asan_tools(built_lib):
     from aluminum_b200 import _build

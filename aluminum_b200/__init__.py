@@ -9,7 +9,8 @@ expert / context / pipeline) in :mod:`aluminum_b200.parallel` and the models
 used by the end-to-end benchmark in :mod:`aluminum_b200.models`.
 """
 from ._lib import AlError, lib_path
-from .comm import HostComm, Request, finalize, get_tuning, info, init, set_tuning, world_rank, world_size
+from .comm import (HostComm, Request, finalize, get_tuning, info, init, local_rank, local_size, node_index,
+                   num_nodes, set_tuning, world_rank, world_size)
 
 
 def __getattr__(name):
@@ -20,5 +21,5 @@ def __getattr__(name):
 
 
 __version__ = "0.1.0"
-__all__ = ["AlError", "HostComm", "DeviceComm", "Request", "init", "finalize", "info", "world_rank", "world_size",
+__all__ = ["AlError", "HostComm", "DeviceComm", "Request", "init", "finalize", "info", "world_rank", "world_size", "local_rank", "local_size", "num_nodes", "node_index",
            "set_tuning", "get_tuning", "lib_path"]

@@ -49,6 +49,25 @@ def world_size() -> int:
     return _lib.load().al_world_size()
 
 
+def local_rank() -> int:
+    """Rank among the processes of this node."""
+    return _lib.load().al_world_local_rank()
+
+
+def local_size() -> int:
+    return _lib.load().al_world_local_size()
+
+
+def num_nodes() -> int:
+    """Number of nodes the world spans (1 unless the TCP transport connected several hosts)."""
+    return _lib.load().al_world_num_nodes()
+
+
+def node_index() -> int:
+    """Index of this rank's node; `comm.split(node_index(), rank)` gives the node-local communicator."""
+    return _lib.load().al_world_node_index()
+
+
 def info() -> str:
     buf = C.create_string_buffer(16384)
     check(_lib.load().al_info(buf, len(buf)))

@@ -26,6 +26,11 @@ int al_finalize(void);
 int al_initialized(void);
 int al_world_rank(void);
 int al_world_size(void);
+int al_world_local_rank(void);
+int al_world_local_size(void);
+/** Number of nodes the world spans, and the index of this rank's node (0-based, by lowest rank). */
+int al_world_num_nodes(void);
+int al_world_node_index(void);
 int al_cuda_available(void);
 /** Writes a NUL-terminated description (version, features, tuning, topology) into buf. */
 int al_info(char* buf, size_t buflen);

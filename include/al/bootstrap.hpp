@@ -1,16 +1,29 @@
 /**
  * @file bootstrap.hpp
  * Host control plane: rank discovery from the launcher's environment and a
- * full mesh of Unix-domain sockets between the ranks of one node, used to
- * exchange memory handles (including file descriptors), shared-memory names
- * and communicator ids.
+ * full mesh of stream sockets between the ranks - Unix-domain sockets between
+ * ranks of one node (they can pass file descriptors), TCP between nodes - used
+ * to exchange memory handles, shared-memory names, addresses and communicator
+ * ids.
  *
  * This takes the place of MPI in the reference, where every communicator
  * duplicates an MPI_Comm, derives the node-local communicator with
  * MPI_Comm_split_type and broadcasts the NCCL id over MPI
  * (include/aluminum/mpi_comm_and_stream_wrapper.hpp:46-129,
- * src/nccl_impl.cpp:46-60, src/mpi_impl.cpp:148-205).  Scope: the ranks of one
- * NVLink domain / one host.
+ * src/nccl_impl.cpp:46-60, src/mpi_impl.cpp:148-205).
+ *
+ * Transports (AL_TRANSPORT = auto | unix | tcp, default auto):
+ *   unix  every rank is on this host; ranks find each other through abstract
+ *         socket names derived from the job key.
+ *   tcp   ranks may be on several hosts: rank 0 listens on
+ *         MASTER_ADDR:AL_MASTER_PORT (default MASTER_PORT + 1), collects every
+ *         rank's node name, address and listening port and hands the table to
+ *         everyone; pairs on the same node still connect through Unix sockets.
+ *   auto  tcp when MASTER_ADDR is set and the launcher reports more ranks than
+ *         local ranks (LOCAL_WORLD_SIZE < WORLD_SIZE, SLURM_NNODES > 1,
+ *         AL_NNODES > 1), else unix.
+ * A rank's node is AL_NODE_ID when set (tests use it to model several nodes on
+ * one machine), else its host name.
  *
  * Launcher variables understood (first match wins), mirroring the set the
  * reference's test helpers read (test/test_utils.hpp:463-530):
@@ -46,6 +59,10 @@ class World {
   static std::unique_ptr<World> from_env();
   /** Explicit construction (used by tests that fork ranks themselves). */
   static std::unique_ptr<World> connect(int rank, int size, int local_rank, const std::string& job_key);
+  /** Multi-host construction: rendezvous at master_addr:master_port (see the file comment). */
+  static std::unique_ptr<World> connect_tcp(int rank, int size, int local_rank_hint, const std::string& job_key,
+                                            const std::string& master_addr, int master_port,
+                                            const std::string& node_id);
   ~World();
 
   int rank() const { return rank_; }
@@ -53,6 +70,15 @@ class World {
   int local_rank() const { return local_rank_; }
   int local_size() const { return local_size_; }
   const std::string& job_key() const { return key_; }
+  /** Node name of a rank; ranks with equal names share memory and can pass descriptors. */
+  const std::string& node_of(int rank) const { return nodes_.at((size_t)rank); }
+  bool same_node(int rank) const { return nodes_.at((size_t)rank) == nodes_.at((size_t)rank_); }
+  /** Number of distinct nodes. */
+  int num_nodes() const { return num_nodes_; }
+  /** Position of a rank's node among the distinct nodes, numbered in order of their lowest rank. */
+  int node_index(int rank) const;
+  /** IP address (text) under which `rank` is reachable from other nodes. */
+  const std::string& address_of(int rank) const { return addrs_.at((size_t)rank); }
 
   void send(int peer, const void* buf, size_t bytes);
   void recv(int peer, void* buf, size_t bytes);
@@ -69,9 +95,17 @@ class World {
   int rank_ = 0, size_ = 1, local_rank_ = 0, local_size_ = 1;
   std::string key_;
   std::vector<int> socks_;  // socks_[peer], -1 for self
-  int listen_fd_ = -1;
+  std::vector<std::string> nodes_, addrs_;
+  int num_nodes_ = 1;
+  int listen_fd_ = -1, tcp_listen_fd_ = -1;
+  void mesh(const std::vector<int>& tcp_ports, double tmo);
   std::mutex coll_mu_;
 };
+
+/** A TCP listening socket on an ephemeral port (returned in *port). */
+int bootstrap_tcp_listen(int* port);
+/** Connects to ip:port with TCP_NODELAY set, retrying for timeout_s seconds; -1 when the time is up. */
+int bootstrap_tcp_connect(const std::string& ip, int port, double timeout_s);
 
 /**
  * An ordered subset of the world; the unit on which communicators are built.
@@ -89,6 +123,8 @@ class Group {
   int size() const { return (int)members_.size(); }
   int world_rank_of(int r) const { return members_[(size_t)r]; }
   const std::vector<int>& members() const { return members_; }
+  /** True when every member is on this rank's node (shared memory and descriptor passing work). */
+  bool single_node() const;
 
   void allgather(const void* in, void* out, size_t bytes_per_rank) const;
   void bcast(void* buf, size_t bytes, int root) const;

@@ -55,6 +55,10 @@ int al_finalize(void) { return guard([] { Finalize(); }); }
 int al_initialized(void) { return Initialized() ? 1 : 0; }
 int al_world_rank(void) { int r = -1; guard([&] { r = get_world()->rank(); }); return r; }
 int al_world_size(void) { int r = -1; guard([&] { r = get_world()->size(); }); return r; }
+int al_world_local_rank(void) { int r = -1; guard([&] { r = get_world()->local_rank(); }); return r; }
+int al_world_local_size(void) { int r = -1; guard([&] { r = get_world()->local_size(); }); return r; }
+int al_world_num_nodes(void) { int r = -1; guard([&] { r = get_world()->num_nodes(); }); return r; }
+int al_world_node_index(void) { int r = -1; guard([&] { r = get_world()->node_index(get_world()->rank()); }); return r; }
 int al_cuda_available(void) { return cuda::device_usable() ? 1 : 0; }
 
 int al_info(char* buf, size_t buflen) {

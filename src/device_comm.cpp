@@ -105,6 +105,15 @@ DeviceCommunicator::DeviceCommunicator(cudaStream_t stream)
 DeviceCommunicator::DeviceCommunicator(const Group& group, cudaStream_t stream)
     : group_(group), stream_(stream), impl_(std::make_shared<Impl>()) {
   require_device();
+  if (!group.single_node()) {
+    // Peers' memory is mapped through descriptors passed between processes and reached over NVLink;
+    // neither crosses a node boundary.
+    for (int r = 0; r < group.size(); ++r)
+      if (!group.world()->same_node(group.world_rank_of(r)))
+        throw_al_exception("a device communicator spans one NVLink domain, but rank ", r, " is on node '",
+                           group.world()->node_of(group.world_rank_of(r)),
+                           "': split the communicator by node, or use the host-transfer backend across nodes");
+  }
   const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
   auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot), true);
   impl_->ws.half_bytes = half;

@@ -18,6 +18,9 @@
 //     know each other's counts in vector operations.
 #include "al/host/communicator.hpp"
 
+#include "host_impl.hpp"
+#include "host_net.hpp"
+
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -37,13 +40,6 @@
 #include "al/tuning.hpp"
 #include "al/util/meta.hpp"
 #include "al/util/utils.hpp"
-
-#if defined(__x86_64__)
-#include <immintrin.h>
-#define AL_CPU_RELAX() _mm_pause()
-#else
-#define AL_CPU_RELAX() ((void)0)
-#endif
 
 namespace Al {
 namespace internal {
@@ -133,35 +129,23 @@ class Workspace {
 using namespace internal;
 using namespace internal::host;
 
-struct HostCommunicator::Impl {
-  std::unique_ptr<Workspace> ws;
-  int p = 1, me = 0;
-  std::atomic<uint64_t> next_seq{1};   // collective sequence numbers handed out at call time
-  std::atomic<uint64_t> done_seq{0};   // last collective that finished locally
-  std::vector<std::atomic<uint64_t>> send_next, send_serving, recv_next, recv_serving;
-  std::atomic<bool> failed{false};
-  std::atomic<uint64_t> n_coll{0}, n_p2p{0}, n_bytes{0}, n_fail{0};
-  std::string fail_msg;
-  std::mutex fail_mu;
-  // Local shadows of the mailbox counters this rank owns as a writer.
-  std::vector<uint64_t> sent_count, acked_count;
-
-  Impl(const Group& g)
-      : p(g.size()), me(g.rank()), send_next((size_t)g.size()), send_serving((size_t)g.size()),
-        recv_next((size_t)g.size()), recv_serving((size_t)g.size()), sent_count((size_t)g.size(), 0),
-        acked_count((size_t)g.size(), 0) {
+HostCommunicator::Impl::Impl(const Group& g)
+    : p(g.size()), me(g.rank()), send_next((size_t)g.size()), send_serving((size_t)g.size()),
+      recv_next((size_t)g.size()), recv_serving((size_t)g.size()), sent_count((size_t)g.size(), 0),
+      acked_count((size_t)g.size(), 0) {
+  for (int i = 0; i < p; ++i) {
+    send_next[(size_t)i] = 0; send_serving[(size_t)i] = 0;
+    recv_next[(size_t)i] = 0; recv_serving[(size_t)i] = 0;
+  }
+  if (g.single_node()) {
     const uint64_t id = g.agree_on_id();
     ws.reset(new Workspace(g, id, tuning().host_stage_bytes, tuning().host_mailbox_bytes));
-    for (int i = 0; i < p; ++i) {
-      send_next[(size_t)i] = 0; send_serving[(size_t)i] = 0;
-      recv_next[(size_t)i] = 0; recv_serving[(size_t)i] = 0;
-    }
+  } else {
+    net.reset(new NetMesh(g));
   }
-  void fail(const std::string& msg) {
-    std::lock_guard<std::mutex> g(fail_mu);
-    if (!failed.load()) { fail_msg = msg; failed.store(true); }
-  }
-};
+}
+
+HostCommunicator::Impl::~Impl() = default;
 
 namespace {
 
@@ -171,58 +155,6 @@ inline size_t clamp_len(size_t count, size_t lo, size_t cap) {
   if (count <= lo) return 0;
   return std::min(cap, count - lo);
 }
-
-/** Base of host states: owns the request and the time-out bookkeeping. */
-class HostState : public AlState {
- public:
-  HostState(HostCommunicator::Impl* ci, Request req) : ci_(ci), req_(std::move(req)) {}
-  const void* get_compute_stream() const override { return ci_; }
-
- protected:
-  /** Returns true (and records the failure) when the current wait exceeded the limit. */
-  bool timed_out(const char* what) {
-    if (ci_->failed.load(std::memory_order_acquire) && !failed_) {
-      fail("communicator failed: " + ci_->fail_msg);
-      return true;
-    }
-    const double now = get_time();
-    if (wait_since_ == 0) { wait_since_ = now; return false; }
-    if (now - wait_since_ > tuning().host_wait_timeout_s) {
-      fail(build_string(get_name(), ": timed out after ", tuning().host_wait_timeout_s, " s waiting for ", what));
-      return true;
-    }
-    return false;
-  }
-  void progress_made() { wait_since_ = 0; }
-  // The outcome reaches the request only in publish_outcome(), the last thing a
-  // state does: once the request is complete its owner may destroy the
-  // communicator, so nothing of *ci_ may be touched afterwards.
-  void fail(const std::string& msg) {
-    ci_->fail(msg);
-    ci_->n_fail.fetch_add(1, std::memory_order_relaxed);
-    err_ = msg;
-    failed_ = true;
-  }
-  void publish_outcome() {
-    if (!req_ || published_) return;
-    published_ = true;
-    if (failed_) {
-      req_->error = err_;
-      req_->status.store(2, std::memory_order_release);
-    } else {
-      req_->status.store(1, std::memory_order_release);
-    }
-  }
-  std::string err_;
-  bool published_ = false;
-  HostCommunicator::Impl* ci_;
-  Request req_;
-  double wait_since_ = 0;
-  bool failed_ = false;
-
- public:
-  bool has_failed() const { return failed_; }
-};
 
 class CollState final : public HostState {
  public:
@@ -531,11 +463,6 @@ class P2PState final : public HostState {
       xfers_.push_back(x);
     }
   }
-  ~P2PState() override {
-    for (void* t : temps_) mempool.release_bytes(MemoryType::HOST, t);
-  }
-  /** Keep a temporary buffer alive until the state completes. */
-  void adopt_temp(void* t) { temps_.push_back(t); }
   const char* get_name() const override { return name_; }
   std::string get_desc() const override { return build_string("transfers=", xfers_.size()); }
   RunType get_run_type() const override { return RunType::unbounded; }
@@ -609,19 +536,7 @@ class P2PState final : public HostState {
   Workspace& ws_;
   const char* name_;
   std::vector<Xfer> xfers_;
-  std::vector<void*> temps_;
 };
-
-/** Drive a state on the calling thread until it completes. */
-template <typename State>
-void run_inline(State& st) {
-  st.start();
-  unsigned spins = 0;
-  while (st.step() != PEAction::complete) {
-    if (++spins < 200) AL_CPU_RELAX();
-    else std::this_thread::yield();
-  }
-}
 
 }  // namespace
 
@@ -651,13 +566,14 @@ void HostCommunicator::collective(CollArgs&& args, Request* req) {
     if (args.send || args.kind == Coll::allreduce)
       ci->n_bytes.fetch_add(elems * dtype_size(args.dt), std::memory_order_relaxed);
   }
+  Request r = std::make_shared<ReqState>();
+  std::unique_ptr<HostState> st(ci->net ? make_net_collective(ci, std::move(args), r, seq)
+                                        : new CollState(ci, std::move(args), r, seq));
   if (req) {
-    *req = std::make_shared<ReqState>();
-    get_progress_engine()->enqueue(new CollState(ci, std::move(args), *req, seq));
+    *req = r;
+    get_progress_engine()->enqueue(st.release());
   } else {
-    Request r = std::make_shared<ReqState>();
-    CollState st(ci, std::move(args), r, seq);
-    run_inline(st);
+    run_inline(*st);
     if (r->status.load() == 2) throw_al_exception(r->error);
   }
 }
@@ -688,16 +604,15 @@ void HostCommunicator::p2p(std::vector<P2PItem>&& items, Request* req, const cha
   ci->n_p2p.fetch_add(1, std::memory_order_relaxed);
   for (auto& it : items)
     if (it.is_send) ci->n_bytes.fetch_add(it.bytes, std::memory_order_relaxed);
+  Request r = std::make_shared<ReqState>();
+  std::unique_ptr<HostState> st(ci->net ? make_net_p2p(ci, std::move(items), r, name)
+                                        : new P2PState(ci, std::move(items), r, name));
+  for (void* t : temps) st->adopt_temp(t);
   if (req) {
-    *req = std::make_shared<ReqState>();
-    auto* st = new P2PState(ci, std::move(items), *req, name);
-    for (void* t : temps) st->adopt_temp(t);
-    get_progress_engine()->enqueue(st);
+    *req = r;
+    get_progress_engine()->enqueue(st.release());
   } else {
-    Request r = std::make_shared<ReqState>();
-    P2PState st(ci, std::move(items), r, name);
-    for (void* t : temps) st.adopt_temp(t);
-    run_inline(st);
+    run_inline(*st);
     if (r->status.load() == 2) throw_al_exception(r->error);
   }
 }

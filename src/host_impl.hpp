@@ -1,0 +1,140 @@
+// Private to the host backend's translation units: the communicator's state
+// shared by the shared-memory path (host_comm.cpp) and the socket path
+// (host_net.cpp), and the base class of their progress-engine states.
+#pragma once
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "al/host/communicator.hpp"
+#include "al/mempool.hpp"
+#include "al/state.hpp"
+#include "al/tuning.hpp"
+#include "al/util/utils.hpp"
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define AL_CPU_RELAX() _mm_pause()
+#else
+#define AL_CPU_RELAX() ((void)0)
+#endif
+
+namespace Al {
+namespace internal {
+namespace host {
+class Workspace;  // shared-memory segment of a single-node communicator (host_comm.cpp)
+class NetMesh;    // sockets of a communicator that spans nodes (host_net.cpp)
+}  // namespace host
+}  // namespace internal
+
+struct HostCommunicator::Impl {
+  std::unique_ptr<internal::host::Workspace> ws;   // single node
+  std::unique_ptr<internal::host::NetMesh> net;    // several nodes (exactly one of the two is set)
+  int p = 1, me = 0;
+  std::atomic<uint64_t> next_seq{1};   // collective sequence numbers handed out at call time
+  std::atomic<uint64_t> done_seq{0};   // last collective that finished locally
+  std::vector<std::atomic<uint64_t>> send_next, send_serving, recv_next, recv_serving;
+  std::atomic<bool> failed{false};
+  std::atomic<uint64_t> n_coll{0}, n_p2p{0}, n_bytes{0}, n_fail{0};
+  std::string fail_msg;
+  std::mutex fail_mu;
+  // Local shadows of the mailbox counters this rank owns as a writer.
+  std::vector<uint64_t> sent_count, acked_count;
+
+  explicit Impl(const internal::Group& g);
+  ~Impl();
+  void fail(const std::string& msg) {
+    std::lock_guard<std::mutex> g(fail_mu);
+    if (!failed.load()) { fail_msg = msg; failed.store(true); }
+  }
+};
+
+namespace internal {
+namespace host {
+
+/** Base of host states: owns the request and the time-out bookkeeping. */
+class HostState : public AlState {
+ public:
+  HostState(HostCommunicator::Impl* ci, Request req) : ci_(ci), req_(std::move(req)) {}
+  ~HostState() override {
+    for (void* t : temps_) mempool.release_bytes(MemoryType::HOST, t);
+  }
+  const void* get_compute_stream() const override { return ci_; }
+  /** Keep a host buffer from the memory pool alive until the state is destroyed. */
+  void adopt_temp(void* t) { temps_.push_back(t); }
+  /** A pooled host buffer that lives as long as the state. */
+  void* temp(size_t bytes) {
+    void* t = mempool.allocate_bytes(MemoryType::HOST, bytes ? bytes : 1);
+    temps_.push_back(t);
+    return t;
+  }
+
+ protected:
+  /** Returns true (and records the failure) when the current wait exceeded the limit. */
+  bool timed_out(const char* what) {
+    if (ci_->failed.load(std::memory_order_acquire) && !failed_) {
+      fail("communicator failed: " + ci_->fail_msg);
+      return true;
+    }
+    const double now = get_time();
+    if (wait_since_ == 0) { wait_since_ = now; return false; }
+    if (now - wait_since_ > tuning().host_wait_timeout_s) {
+      fail(build_string(get_name(), ": timed out after ", tuning().host_wait_timeout_s, " s waiting for ", what));
+      return true;
+    }
+    return false;
+  }
+  void progress_made() { wait_since_ = 0; }
+  // The outcome reaches the request only in publish_outcome(), the last thing a
+  // state does: once the request is complete its owner may destroy the
+  // communicator, so nothing of *ci_ may be touched afterwards.
+  void fail(const std::string& msg) {
+    ci_->fail(msg);
+    ci_->n_fail.fetch_add(1, std::memory_order_relaxed);
+    err_ = msg;
+    failed_ = true;
+  }
+  void publish_outcome() {
+    if (!req_ || published_) return;
+    published_ = true;
+    if (failed_) {
+      req_->error = err_;
+      req_->status.store(2, std::memory_order_release);
+    } else {
+      req_->status.store(1, std::memory_order_release);
+    }
+  }
+  std::string err_;
+  bool published_ = false;
+  std::vector<void*> temps_;
+  HostCommunicator::Impl* ci_;
+  Request req_;
+  double wait_since_ = 0;
+  bool failed_ = false;
+
+ public:
+  bool has_failed() const { return failed_; }
+};
+
+
+/** Drive a state on the calling thread until it completes. */
+template <typename State>
+void run_inline(State& st) {
+  st.start();
+  unsigned spins = 0;
+  while (st.step() != PEAction::complete) {
+    if (++spins < 200) AL_CPU_RELAX();
+    else std::this_thread::yield();
+  }
+}
+
+/** States of the socket path (host_net.cpp). */
+HostState* make_net_collective(HostCommunicator::Impl* ci, CollArgs&& args, Request req, uint64_t seq);
+HostState* make_net_p2p(HostCommunicator::Impl* ci, std::vector<P2PItem>&& items, Request req, const char* name);
+
+}  // namespace host
+}  // namespace internal
+}  // namespace Al

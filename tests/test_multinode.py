@@ -1,0 +1,87 @@
+"""Worlds that span several nodes, modelled on one machine: `alrun --nodes K` gives consecutive
+blocks of ranks different node names and selects the TCP transport, so ranks of different blocks
+cannot share memory or pass descriptors and every byte between them crosses a socket."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+W = Path(__file__).resolve().parent / "workers"
+
+ALL_OPS = ["allreduce", "reduce", "reduce_scatter", "reduce_scatterv", "allgather", "allgatherv", "alltoall",
+           "alltoallv", "bcast", "gather", "gatherv", "scatter", "scatterv", "barrier", "send", "sendrecv",
+           "multisendrecv"]
+
+
+def run(cmd, env=None, timeout=300):
+    import os
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=timeout, env=e)
+
+
+@pytest.mark.parametrize("op", ALL_OPS)
+def test_every_operation_across_nodes(bin_dir, op):
+    for extra in ([], ["--inplace", "--nonblocking"]):
+        r = run([bin_dir / "alrun", "-n", "4", "--nodes", "2", "--timeout", "120", bin_dir / "test_ops", "--backend", "host",
+                 "--op", op, "--max-size", "262144", "--odd-sizes", "--zero", "--root", "2"] + extra)
+        assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("ranks,nodes,dtype,rop", [(3, 3, "half", "sum"), (5, 2, "int", "max"), (8, 2, "float", "avg"),
+                                                   (6, 3, "bfloat16", "sum"), (4, 4, "ullong", "bxor"),
+                                                   (5, 5, "double", "prod")])
+def test_reductions_across_nodes(bin_dir, ranks, nodes, dtype, rop):
+    for op in ("allreduce", "reduce", "reduce_scatterv"):
+        r = run([bin_dir / "alrun", "-n", str(ranks), "--nodes", str(nodes), "--timeout", "120", bin_dir / "test_ops",
+                 "--backend", "host", "--op", op, "--datatype", dtype, "--reduction-op", rop, "--max-size", "300000",
+                 "--odd-sizes", "--root", "1"])
+        assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_large_messages_across_nodes(bin_dir):
+    """Sizes beyond the socket buffers: partial writes and reads on every connection."""
+    for op in ("allreduce", "bcast", "alltoall", "sendrecv"):
+        r = run([bin_dir / "alrun", "-n", "4", "--nodes", "2", "--timeout", "200", bin_dir / "test_ops", "--backend", "host",
+                 "--op", op, "--min-size", "4194304", "--max-size", "8388608", "--odd-sizes"])
+        assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_threads_and_permuted_ranks_across_nodes(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "4", "--nodes", "2", "--timeout", "120", bin_dir / "test_ops", "--backend", "host",
+             "--op", "alltoallv", "--threads", "3", "--nonblocking", "--permute", "3,1,0,2", "--max-size", "65536"])
+    assert r.returncode == 0 and "threads=3: ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_node_local_and_cross_node_communicators(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "6", "--nodes", "2", "--timeout", "120", sys.executable, W / "host_multinode.py", "hier"])
+    assert r.returncode == 0 and r.stdout.count("hierarchical ok") == 6, r.stdout + r.stderr
+
+
+def test_dead_rank_is_reported_by_its_connections(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "4", "--nodes", "2", "--timeout", "120", sys.executable, W / "host_multinode.py", "dead"],
+            env={"AL_HOST_WAIT_TIMEOUT_S": "5"})
+    assert r.stdout.count("detected the dead rank") == 3, r.stdout + r.stderr
+
+
+def test_mismatched_sizes_are_reported(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "2", "--nodes", "2", "--timeout", "60", sys.executable, W / "host_multinode.py",
+             "mismatch"], env={"AL_HOST_WAIT_TIMEOUT_S": "3"})
+    assert "mismatch reported" in r.stdout, r.stdout + r.stderr
+
+
+def test_examples_across_nodes(bin_dir):
+    r = run([bin_dir / "alrun", "-n", "3", "--nodes", "3", bin_dir / "hello_world"])
+    assert r.returncode == 0 and r.stdout.count("sum of ranks = 3") == 3, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "2", "--nodes", "2", bin_dir / "pingpong"])
+    assert r.returncode == 0 and "per round trip" in r.stdout, r.stdout + r.stderr
+    r = run([bin_dir / "alrun", "-n", "4", "--nodes", "2", bin_dir / "test_exchange", "--peers", "2", "--size", "5000"])
+    assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_rendezvous_times_out_without_rank_zero(bin_dir):
+    env = {"AL_RANK": "1", "AL_WORLD_SIZE": "2", "AL_TRANSPORT": "tcp", "MASTER_ADDR": "127.0.0.1", "AL_MASTER_PORT": "1",
+           "AL_JOB_KEY": "nobody-home", "AL_BOOTSTRAP_TIMEOUT_S": "1"}
+    r = run([bin_dir / "test_ops", "--backend", "host", "--op", "barrier"], env=env, timeout=60)
+    assert r.returncode != 0 and "could not reach the rendezvous" in r.stderr, r.stdout + r.stderr

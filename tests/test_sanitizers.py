@@ -55,6 +55,17 @@ def test_thread_multiple_is_race_free(tsan_tools, bin_dir, op):
     assert _clean(out), out[-3000:]
 
 
+@pytest.mark.parametrize("op", ["allreduce", "reduce", "alltoallv", "bcast", "multisendrecv"])
+def test_socket_path_is_race_free(tsan_tools, bin_dir, op):
+    """Ranks on different (modelled) nodes: the TCP data plane under ThreadSanitizer, two user threads."""
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", "4", "--nodes", "2", "--timeout", "300", str(tsan_tools["test_ops"]),
+                        "--backend", "host", "--op", op, "--threads", "2", "--nonblocking", "--max-size", "300000"],
+                       capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and ": ok" in out, out[-3000:]
+    assert _clean(out), out[-3000:]
+
+
 @pytest.fixture(scope="module")
 def asan_tools(built_lib):
     from aluminum_b200 import _build
@@ -77,6 +88,11 @@ def test_host_backend_is_memory_clean(asan_tools, bin_dir, op):
     """Out-of-bounds accesses, use after free and leaks at exit all fail the run."""
     r = subprocess.run([str(bin_dir / "alrun"), "-n", "3", "--timeout", "300", str(asan_tools["test_ops"]),
                         "--backend", "host", "--op", op, "--max-size", "16384"],
+                       capture_output=True, text=True, timeout=600)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and ": ok" in out and "Sanitizer" not in out, out[-3000:]
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", "4", "--nodes", "2", "--timeout", "300", str(asan_tools["test_ops"]),
+                        "--backend", "host", "--op", op, "--max-size", "300000", "--odd-sizes", "--inplace"],
                        capture_output=True, text=True, timeout=600)
     out = r.stdout + r.stderr
     assert r.returncode == 0 and ": ok" in out and "Sanitizer" not in out, out[-3000:]

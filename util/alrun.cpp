@@ -1,14 +1,20 @@
 // alrun - minimal single-host launcher: forks N copies of a program with the
 // rank environment the library's bootstrap understands.
 //
-//   alrun -n 4 [--timeout SECONDS] program [args...]
+//   alrun -n 4 [--timeout SECONDS] [--nodes K] program [args...]
 //
 // Each child gets AL_RANK, AL_WORLD_SIZE, AL_LOCAL_RANK and a fresh AL_JOB_KEY.
+// --nodes K models K nodes on this machine: consecutive blocks of N/K ranks get
+// the same AL_NODE_ID, the TCP transport is selected and a free rendezvous port
+// is chosen, so ranks of different blocks talk over loopback TCP and cannot
+// share memory or pass descriptors - what ranks on different hosts see.
 // If a child fails or the time limit passes, the remaining children are
 // terminated (by the process ids this launcher created) and alrun exits
 // non-zero.  It stands in for mpirun / jsrun / srun of the reference's test
 // and benchmark drivers (test/run_tests.py:109-143).
+#include <netinet/in.h>
 #include <signal.h>
+#include <sys/socket.h>
 #include <sys/wait.h>
 #include <unistd.h>
 
@@ -20,19 +26,37 @@
 #include <thread>
 #include <vector>
 
+// A TCP port that was free a moment ago (bind to 0, read it back, close).
+static int pick_free_port() {
+  int fd = socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) return 29500;
+  sockaddr_in a{};
+  a.sin_family = AF_INET;
+  a.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  a.sin_port = 0;
+  socklen_t len = sizeof(a);
+  int port = 29500;
+  if (bind(fd, (sockaddr*)&a, sizeof(a)) == 0 && getsockname(fd, (sockaddr*)&a, &len) == 0) port = ntohs(a.sin_port);
+  close(fd);
+  return port;
+}
+
 int main(int argc, char** argv) {
-  int n = 1;
+  int n = 1, nodes = 0;
   double timeout = 0;
   int i = 1;
   for (; i < argc; ++i) {
     if (!strcmp(argv[i], "-n") && i + 1 < argc) n = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--timeout") && i + 1 < argc) timeout = atof(argv[++i]);
+    else if (!strcmp(argv[i], "--nodes") && i + 1 < argc) nodes = atoi(argv[++i]);
     else break;
   }
-  if (i >= argc || n < 1) {
-    fprintf(stderr, "usage: alrun -n N [--timeout SECONDS] program [args...]\n");
+  if (i >= argc || n < 1 || nodes < 0 || nodes > n) {
+    fprintf(stderr, "usage: alrun -n N [--timeout SECONDS] [--nodes K] program [args...]\n");
     return 2;
   }
+  const int per_node = nodes > 0 ? (n + nodes - 1) / nodes : n;
+  const int port = nodes > 0 ? pick_free_port() : 0;
   const std::string key = "alrun-" + std::to_string(getpid()) + "-" +
                           std::to_string(std::chrono::steady_clock::now().time_since_epoch().count());
   std::vector<pid_t> kids;
@@ -42,8 +66,14 @@ int main(int argc, char** argv) {
     if (pid == 0) {
       setenv("AL_RANK", std::to_string(r).c_str(), 1);
       setenv("AL_WORLD_SIZE", std::to_string(n).c_str(), 1);
-      setenv("AL_LOCAL_RANK", std::to_string(r).c_str(), 1);
+      setenv("AL_LOCAL_RANK", std::to_string(r % per_node).c_str(), 1);
       setenv("AL_JOB_KEY", key.c_str(), 1);
+      if (nodes > 0) {
+        setenv("AL_TRANSPORT", "tcp", 1);
+        setenv("AL_NODE_ID", ("node" + std::to_string(r / per_node)).c_str(), 1);
+        setenv("MASTER_ADDR", "127.0.0.1", 1);
+        setenv("AL_MASTER_PORT", std::to_string(port).c_str(), 1);
+      }
       execvp(argv[i], argv + i);
       perror("execvp");
       _exit(127);

@@ -6,11 +6,14 @@
  * point-to-point on host memory, blocking and non-blocking through the
  * progress engine (include/aluminum/mpi_impl.hpp, include/aluminum/mpi/*.hpp,
  * communicator at include/aluminum/mpi/communicator.hpp:49-97).  There is no
- * MPI underneath: ranks of one host share a POSIX shared-memory workspace per
- * communicator and run the same flag protocol the device kernels use
- * (publish into own staging half -> post epoch flag to every peer -> wait for
- * every peer's flag -> pull / reduce), so the CPU ranks double as a model of
- * the device protocol that can be tested without a GPU.
+ * MPI underneath.  When all members are on one node they share a POSIX
+ * shared-memory workspace per communicator and run the same flag protocol the
+ * device kernels use (publish into own staging half -> post epoch flag to
+ * every peer -> wait for every peer's flag -> pull / reduce), so the CPU ranks
+ * double as a model of the device protocol that can be tested without a GPU.
+ * When the members are on several nodes the communicator owns TCP connections
+ * between all pairs and runs the operations as rounds of non-blocking
+ * messages (src/host_net.cpp).
  */
 #pragma once
 #include <atomic>

@@ -1,7 +1,8 @@
 /**
  * @file host_backend.hpp
- * The CPU backend: collectives and point-to-point on host memory between the
- * ranks of one host, blocking or through the progress engine.
+ * The CPU backend: collectives and point-to-point on host memory, through
+ * shared memory between the ranks of one node and through sockets between
+ * nodes, blocking or through the progress engine.
  *
  * Parity: Al::MPIBackend (include/aluminum/mpi_impl.hpp:112-990): same static
  * member names, `comm_type`, `req_type`, `null_req`, algorithm enums (all

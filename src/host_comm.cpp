@@ -540,6 +540,18 @@ class P2PState final : public HostState {
 
 }  // namespace
 
+namespace {
+/** Block the caller until a request handed to the progress engine completes; rethrow its failure. */
+void wait_for(const Request& r) {
+  unsigned spins = 0;
+  while (r->status.load(std::memory_order_acquire) == 0) {
+    if (++spins < 200) AL_CPU_RELAX();
+    else std::this_thread::yield();
+  }
+  if (r->status.load() == 2) throw_al_exception(r->error);
+}
+}  // namespace
+
 HostCommunicator::HostCommunicator() : HostCommunicator(Group::world_group(get_world())) {}
 
 HostCommunicator::HostCommunicator(const Group& group) : group_(group), impl_(new Impl(group)) {}
@@ -572,6 +584,10 @@ void HostCommunicator::collective(CollArgs&& args, Request* req) {
   if (req) {
     *req = r;
     get_progress_engine()->enqueue(st.release());
+  } else if (tuning().host_serialize) {
+    // Every operation, blocking ones included, runs on the progress thread; the caller only waits.
+    get_progress_engine()->enqueue(st.release());
+    wait_for(r);
   } else {
     run_inline(*st);
     if (r->status.load() == 2) throw_al_exception(r->error);
@@ -611,6 +627,10 @@ void HostCommunicator::p2p(std::vector<P2PItem>&& items, Request* req, const cha
   if (req) {
     *req = r;
     get_progress_engine()->enqueue(st.release());
+  } else if (tuning().host_serialize) {
+    // Every operation, blocking ones included, runs on the progress thread; the caller only waits.
+    get_progress_engine()->enqueue(st.release());
+    wait_for(r);
   } else {
     run_inline(*st);
     if (r->status.load() == 2) throw_al_exception(r->error);

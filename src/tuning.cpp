@@ -24,6 +24,7 @@ void Tuning::load_from_env() {
   host_stage_bytes = (size_t)env_long("AL_HOST_STAGE_BYTES", (long)host_stage_bytes);
   host_mailbox_bytes = (size_t)env_long("AL_HOST_MAILBOX_BYTES", (long)host_mailbox_bytes);
   host_wait_timeout_s = (double)env_long("AL_HOST_WAIT_TIMEOUT_S", (long)host_wait_timeout_s);
+  host_serialize = env_long("AL_HOST_SERIALIZE", host_serialize) != 0;
   dev_stage_bytes = (size_t)env_long("AL_DEV_STAGE_BYTES", (long)dev_stage_bytes);
   dev_mailbox_bytes = (size_t)env_long("AL_DEV_MAILBOX_BYTES", (long)dev_mailbox_bytes);
   dev_wait_timeout_ms = (double)env_long("AL_DEV_WAIT_TIMEOUT_MS", (long)dev_wait_timeout_ms);
@@ -76,6 +77,7 @@ std::string Tuning::describe() const {
      << "host_stage_bytes = " << host_stage_bytes << "\n"
      << "host_mailbox_bytes = " << host_mailbox_bytes << "\n"
      << "host_wait_timeout_s = " << host_wait_timeout_s << "\n"
+     << "host_serialize = " << host_serialize << "\n"
      << "dev_stage_bytes = " << dev_stage_bytes << "\n"
      << "dev_mailbox_bytes = " << dev_mailbox_bytes << "\n"
      << "dev_wait_timeout_ms = " << dev_wait_timeout_ms << "\n"

@@ -177,3 +177,12 @@ def test_permuted_ranks(bin_dir, op):
     r = run([bin_dir / "alrun", "-n", "3", "--timeout", "60", bin_dir / "test_ops", "--backend", "host", "--op", op,
              "--permute", "2,0,0"])
     assert r.returncode != 0 and "not a permutation" in r.stderr, r.stdout + r.stderr
+
+
+def test_serialized_mode_runs_blocking_calls_on_the_progress_thread(bin_dir, tmp_path):
+    env = {"AL_HOST_SERIALIZE": "1", "AL_TRACE": "1", "AL_TRACE_DIR": str(tmp_path)}
+    r = run([bin_dir / "alrun", "-n", "3", "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op", "allreduce",
+             "--max-size", "4096"], env=env)
+    assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+    text = next(iter(tmp_path.glob("*.trace.txt"))).read_text()
+    assert "PE START HostAllreduce" in text  # a blocking call went through the engine

@@ -34,6 +34,14 @@ inline long env_long(const char* name, long dflt) {
   long r = std::strtol(v, &end, 0);
   return end == v ? dflt : r;
 }
+/** Fractions allowed ("0.5"); unparsable text gives the default. */
+inline double env_double(const char* name, double dflt) {
+  const char* v = std::getenv(name);
+  if (!v || !*v) return dflt;
+  char* end = nullptr;
+  double r = std::strtod(v, &end);
+  return end == v ? dflt : r;
+}
 inline std::string env_str(const char* name, const std::string& dflt = "") {
   const char* v = std::getenv(name);
   return (v && *v) ? std::string(v) : dflt;

@@ -71,7 +71,7 @@ socklen_t make_addr(sockaddr_un& a, const std::string& key, int rank) {
 
 double timeout_s(const BootstrapFaults& f) {
   if (f.recv_timeout_s >= 0) return f.recv_timeout_s;
-  return (double)env_long("AL_BOOTSTRAP_TIMEOUT_S", 120);
+  return env_double("AL_BOOTSTRAP_TIMEOUT_S", 120.0);
 }
 
 void write_all(int fd, const void* buf, size_t n) {

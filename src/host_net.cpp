@@ -77,7 +77,7 @@ void make_data_socket(int fd) {
 NetMesh::NetMesh(const Group& g) : p_(g.size()), me_(g.rank()) {
   fds_[0].assign((size_t)p_, -1);
   fds_[1].assign((size_t)p_, -1);
-  const double tmo = (double)env_long("AL_BOOTSTRAP_TIMEOUT_S", 120);
+  const double tmo = env_double("AL_BOOTSTRAP_TIMEOUT_S", 120.0);
   int port = 0;
   const int lfd = bootstrap_tcp_listen(&port);
   try {

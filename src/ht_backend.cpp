@@ -74,7 +74,16 @@ class HTState final : public AlState {
         phase_ = 1;
         return PEAction::advance;
       case 1:
-        launch_host();  // non-blocking host operation driven by the same engine
+        try {
+          launch_host();  // non-blocking host operation driven by the same engine
+        } catch (const std::exception& e) {
+          // The host communicator refused the operation (it failed earlier): release the
+          // stream so that nothing on the device waits forever, and say why.
+          std::cerr << "[al] host-transfer operation could not start: " << e.what() << "\n";
+          wait.signal();
+          phase_ = 3;
+          return PEAction::cont;
+        }
         // A rank that receives nothing (non-root of reduce / gather, root of
         // scatter with no slice, a pure send) only had to get its data off the
         // device: its stream is released now instead of after the exchange

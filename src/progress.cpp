@@ -156,7 +156,7 @@ void ProgressEngine::engine() {
           if (bounded) ++num_bounded_;
           in_flight_.fetch_add(1, std::memory_order_acq_rel);
           st->start_time = get_time();
-          trace::record_pe_start(st->get_name(), st->get_desc());
+          if (trace::enabled()) trace::record_pe_start(st->get_name(), st->get_desc());
           st->start();
           pipelines_[i].stage[0].push_back(st);
         }
@@ -171,7 +171,16 @@ void ProgressEngine::engine() {
           AlState* st = vec[k];
           any = true;
           if (st->paused_for_advance) { ++k; continue; }
-          PEAction a = st->step();
+          PEAction a;
+          try {
+            a = st->step();
+          } catch (const std::exception& e) {
+            // A state must report failures through its request; one that throws is
+            // dropped so that the engine (and every other stream) keeps running.
+            std::cerr << "[al] progress engine: " << st->get_name() << " " << st->get_desc() << " threw: " << e.what()
+                      << "\n";
+            a = PEAction::complete;
+          }
           if (a == PEAction::cont) {
             if (hang_s > 0 && !st->hang_reported && get_time() - st->start_time > hang_s) {
               st->hang_reported = true;
@@ -197,7 +206,7 @@ void ProgressEngine::engine() {
           } else {  // complete
             vec.erase(vec.begin() + (long)k);
             if (st->get_run_type() == RunType::bounded) --num_bounded_;
-            trace::record_pe_done(st->get_name(), st->get_desc());
+            if (trace::enabled()) trace::record_pe_done(st->get_name(), st->get_desc());
             delete st;
             in_flight_.fetch_sub(1, std::memory_order_acq_rel);
           }

@@ -13,21 +13,22 @@ Tuning& tuning() {
 }
 
 void Tuning::load_from_env() {
+  using internal::env_double;
   using internal::env_long;
   pe_num_concurrent_ops = (int)env_long("AL_PE_NUM_CONCURRENT_OPS", pe_num_concurrent_ops);
   pe_start_on_demand = env_long("AL_PE_START_ON_DEMAND", pe_start_on_demand) != 0;
   pe_bind_thread = env_long("AL_PE_BIND", pe_bind_thread) != 0;
-  pe_hang_seconds = (double)env_long("AL_PE_HANG_SECONDS", (long)pe_hang_seconds);
+  pe_hang_seconds = env_double("AL_PE_HANG_SECONDS", pe_hang_seconds);
   sync_mem_prealloc = (int)env_long("AL_SYNC_MEM_PREALLOC", sync_mem_prealloc);
   stream_pool_size = (int)env_long("AL_CUDA_STREAM_POOL_SIZE", stream_pool_size);
   disable_background_streams = env_long("AL_DISABLE_BACKGROUND_STREAMS", disable_background_streams) != 0;
   host_stage_bytes = (size_t)env_long("AL_HOST_STAGE_BYTES", (long)host_stage_bytes);
   host_mailbox_bytes = (size_t)env_long("AL_HOST_MAILBOX_BYTES", (long)host_mailbox_bytes);
-  host_wait_timeout_s = (double)env_long("AL_HOST_WAIT_TIMEOUT_S", (long)host_wait_timeout_s);
+  host_wait_timeout_s = env_double("AL_HOST_WAIT_TIMEOUT_S", host_wait_timeout_s);
   host_serialize = env_long("AL_HOST_SERIALIZE", host_serialize) != 0;
   dev_stage_bytes = (size_t)env_long("AL_DEV_STAGE_BYTES", (long)dev_stage_bytes);
   dev_mailbox_bytes = (size_t)env_long("AL_DEV_MAILBOX_BYTES", (long)dev_mailbox_bytes);
-  dev_wait_timeout_ms = (double)env_long("AL_DEV_WAIT_TIMEOUT_MS", (long)dev_wait_timeout_ms);
+  dev_wait_timeout_ms = env_double("AL_DEV_WAIT_TIMEOUT_MS", dev_wait_timeout_ms);
   dev_enable_nvls = env_long("AL_DEV_NVLS", dev_enable_nvls) != 0;
   ar_oneshot_max_bytes = (size_t)env_long("AL_AR_ONESHOT_MAX", (long)ar_oneshot_max_bytes);
   ar_nvls_min_bytes = (size_t)env_long("AL_AR_NVLS_MIN", (long)ar_nvls_min_bytes);

@@ -1,6 +1,7 @@
-"""Parallelism helpers built on the device communicator.
+"""Parallelism helpers built on the communicators.
 
 ``ddp``      data parallel: bucketed, overlapped gradient allreduce + fused SGD
+``host_ddp`` the same on CPU tensors over the host communicator (shared memory or sockets)
 ``trainer``  end-to-end training loop (host batches in, losses out)
 ``tensor``   tensor parallel linear layers (column / row) on allgather / allreduce
 ``sequence`` Megatron-style sequence parallel: reduce-scatter / allgather along the sequence

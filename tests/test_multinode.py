@@ -85,3 +85,10 @@ def test_rendezvous_times_out_without_rank_zero(bin_dir):
            "AL_JOB_KEY": "nobody-home", "AL_BOOTSTRAP_TIMEOUT_S": "1"}
     r = run([bin_dir / "test_ops", "--backend", "host", "--op", "barrier"], env=env, timeout=60)
     assert r.returncode != 0 and "could not reach the rendezvous" in r.stderr, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("launch", [["-n", "3"], ["-n", "4", "--nodes", "2"]])
+def test_data_parallel_training_on_cpu_ranks(bin_dir, launch):
+    """Bucketed, overlapped gradient averaging on the progress thread reproduces full-batch training."""
+    r = run([bin_dir / "alrun", *launch, "--timeout", "200", sys.executable, W / "host_ddp_worker.py"])
+    assert r.returncode == 0 and r.stdout.count("data parallel on CPU ok") == int(launch[1]), r.stdout + r.stderr

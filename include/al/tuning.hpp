@@ -32,6 +32,8 @@ struct Tuning {
   size_t host_stage_bytes = size_t{4} << 20;   ///< AL_HOST_STAGE_BYTES: one staging half per rank
   size_t host_mailbox_bytes = size_t{128} << 10;  ///< AL_HOST_MAILBOX_BYTES: one p2p slot per ordered pair
   double host_wait_timeout_s = 120.0;          ///< AL_HOST_WAIT_TIMEOUT_S: a peer that never arrives raises
+  bool host_two_level = true;                  ///< AL_HOST_TWO_LEVEL: across nodes, small allreduce / bcast and every barrier go through shared memory inside each node and sockets between the nodes' first ranks
+  size_t host_two_level_max_bytes = size_t{32} << 10;  ///< AL_HOST_TWO_LEVEL_MAX: largest message that takes the two-level path (larger ones use every rank's connections)
   bool host_serialize = false;                 ///< AL_HOST_SERIALIZE: blocking host calls also run on the progress thread (the reference's ALUMINUM_MPI_SERIALIZE)
   // ---- device backend ---------------------------------------------------------
   size_t dev_stage_bytes = size_t{64} << 20;   ///< AL_DEV_STAGE_BYTES: one staging half per rank per communicator

@@ -142,6 +142,28 @@ HostCommunicator::Impl::Impl(const Group& g)
     ws.reset(new Workspace(g, id, tuning().host_stage_bytes, tuning().host_mailbox_bytes));
   } else {
     net.reset(new NetMesh(g));
+    // Node structure of the members; a second level pays off when some node holds several of them.
+    World* w = g.world();
+    std::vector<std::string> names;
+    node_of.resize((size_t)p);
+    local_index.resize((size_t)p);
+    std::vector<int> per_node;
+    for (int r = 0; r < p; ++r) {
+      const std::string& nm = w->node_of(g.world_rank_of(r));
+      size_t k = 0;
+      while (k < names.size() && names[k] != nm) ++k;
+      if (k == names.size()) { names.push_back(nm); per_node.push_back(0); }
+      node_of[(size_t)r] = (int)k;
+      local_index[(size_t)r] = per_node[k]++;
+    }
+    const bool two_level = tuning().host_two_level && *std::max_element(per_node.begin(), per_node.end()) > 1 &&
+                           names.size() > 1;
+    if (two_level) {
+      node_comm.reset(new HostCommunicator(g.split(node_of[(size_t)me], me)));
+      const bool leader = local_index[(size_t)me] == 0;
+      Group lg = g.split(leader ? 0 : 1, me);  // collective over all members; only the leaders build on it
+      if (leader) leader_comm.reset(new HostCommunicator(lg));
+    }
   }
 }
 
@@ -552,6 +574,18 @@ void wait_for(const Request& r) {
 }
 }  // namespace
 
+namespace internal {
+namespace host {
+HostState* make_collective_state(HostCommunicator::Impl* ci, CollArgs&& args, Request req, uint64_t seq) {
+  if (ci->node_comm) {
+    if (HostState* st = make_hier_collective(ci, args, req, seq)) return st;  // leaves args alone when it declines
+  }
+  if (ci->net) return make_net_collective(ci, std::move(args), std::move(req), seq);
+  return new CollState(ci, std::move(args), std::move(req), seq);
+}
+}  // namespace host
+}  // namespace internal
+
 HostCommunicator::HostCommunicator() : HostCommunicator(Group::world_group(get_world())) {}
 
 HostCommunicator::HostCommunicator(const Group& group) : group_(group), impl_(new Impl(group)) {}
@@ -579,8 +613,7 @@ void HostCommunicator::collective(CollArgs&& args, Request* req) {
       ci->n_bytes.fetch_add(elems * dtype_size(args.dt), std::memory_order_relaxed);
   }
   Request r = std::make_shared<ReqState>();
-  std::unique_ptr<HostState> st(ci->net ? make_net_collective(ci, std::move(args), r, seq)
-                                        : new CollState(ci, std::move(args), r, seq));
+  std::unique_ptr<HostState> st(make_collective_state(ci, std::move(args), r, seq));
   if (req) {
     *req = r;
     get_progress_engine()->enqueue(st.release());

@@ -33,6 +33,11 @@ class NetMesh;    // sockets of a communicator that spans nodes (host_net.cpp)
 struct HostCommunicator::Impl {
   std::unique_ptr<internal::host::Workspace> ws;   // single node
   std::unique_ptr<internal::host::NetMesh> net;    // several nodes (exactly one of the two is set)
+  // Two-level layout of a communicator that spans nodes and has a node with several members:
+  // a shared-memory communicator per node and a socket communicator of the nodes' first members.
+  std::unique_ptr<HostCommunicator> node_comm, leader_comm;  // leader_comm only on the first member of a node
+  std::vector<int> node_of;       // member -> index of its node (nodes numbered by their lowest member)
+  std::vector<int> local_index;   // member -> rank inside its node's communicator
   int p = 1, me = 0;
   std::atomic<uint64_t> next_seq{1};   // collective sequence numbers handed out at call time
   std::atomic<uint64_t> done_seq{0};   // last collective that finished locally
@@ -130,6 +135,11 @@ void run_inline(State& st) {
     else std::this_thread::yield();
   }
 }
+
+/** The state that runs `args` on communicator `ci`: two-level, socket or shared-memory path (host_comm.cpp). */
+HostState* make_collective_state(HostCommunicator::Impl* ci, CollArgs&& args, Request req, uint64_t seq);
+/** Allreduce / bcast / barrier composed of node-level and leader-level operations (host_hier.cpp); nullptr if not applicable. */
+HostState* make_hier_collective(HostCommunicator::Impl* ci, CollArgs& args, Request req, uint64_t seq);
 
 /** States of the socket path (host_net.cpp). */
 HostState* make_net_collective(HostCommunicator::Impl* ci, CollArgs&& args, Request req, uint64_t seq);

@@ -25,6 +25,8 @@ void Tuning::load_from_env() {
   host_stage_bytes = (size_t)env_long("AL_HOST_STAGE_BYTES", (long)host_stage_bytes);
   host_mailbox_bytes = (size_t)env_long("AL_HOST_MAILBOX_BYTES", (long)host_mailbox_bytes);
   host_wait_timeout_s = env_double("AL_HOST_WAIT_TIMEOUT_S", host_wait_timeout_s);
+  host_two_level = env_long("AL_HOST_TWO_LEVEL", host_two_level) != 0;
+  host_two_level_max_bytes = (size_t)env_long("AL_HOST_TWO_LEVEL_MAX", (long)host_two_level_max_bytes);
   host_serialize = env_long("AL_HOST_SERIALIZE", host_serialize) != 0;
   dev_stage_bytes = (size_t)env_long("AL_DEV_STAGE_BYTES", (long)dev_stage_bytes);
   dev_mailbox_bytes = (size_t)env_long("AL_DEV_MAILBOX_BYTES", (long)dev_mailbox_bytes);
@@ -78,6 +80,8 @@ std::string Tuning::describe() const {
      << "host_stage_bytes = " << host_stage_bytes << "\n"
      << "host_mailbox_bytes = " << host_mailbox_bytes << "\n"
      << "host_wait_timeout_s = " << host_wait_timeout_s << "\n"
+     << "host_two_level = " << host_two_level << "\n"
+     << "host_two_level_max_bytes = " << host_two_level_max_bytes << "\n"
      << "host_serialize = " << host_serialize << "\n"
      << "dev_stage_bytes = " << dev_stage_bytes << "\n"
      << "dev_mailbox_bytes = " << dev_mailbox_bytes << "\n"

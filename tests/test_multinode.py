@@ -92,3 +92,20 @@ def test_data_parallel_training_on_cpu_ranks(bin_dir, launch):
     """Bucketed, overlapped gradient averaging on the progress thread reproduces full-batch training."""
     r = run([bin_dir / "alrun", *launch, "--timeout", "200", sys.executable, W / "host_ddp_worker.py"])
     assert r.returncode == 0 and r.stdout.count("data parallel on CPU ok") == int(launch[1]), r.stdout + r.stderr
+
+
+def test_two_level_path_is_taken_for_small_messages(bin_dir, tmp_path):
+    """Several ranks per node: small allreduce / bcast and barriers are composed of node-level
+    (shared memory) and leader-level (socket) operations; large ones use the flat socket path."""
+    env = {"AL_TRACE": "1", "AL_TRACE_DIR": str(tmp_path)}
+    for op in ("allreduce", "bcast", "barrier"):
+        for extra in ([], ["--inplace", "--nonblocking"]):
+            r = run([bin_dir / "alrun", "-n", "6", "--nodes", "2", "--timeout", "120", bin_dir / "test_ops", "--backend",
+                     "host", "--op", op, "--max-size", "65536", "--odd-sizes", "--zero", "--root", "4"] + extra, env=env)
+            assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+    text = "".join(f.read_text() for f in tmp_path.glob("*.trace.txt"))
+    for name in ("HierAllreduce", "HierBcast", "HierBarrier", "NetAllreduce", "NetBcast"):
+        assert name in text, name
+    r = run([bin_dir / "alrun", "-n", "6", "--nodes", "3", "--timeout", "120", bin_dir / "test_ops", "--backend", "host",
+             "--op", "allreduce", "--max-size", "4096", "--threads", "2", "--nonblocking"], env={"AL_HOST_TWO_LEVEL": "0"})
+    assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr

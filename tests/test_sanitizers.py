@@ -16,11 +16,13 @@ OPS = ["allreduce", "reduce_scatter", "allgatherv", "alltoallv", "bcast", "sendr
 def tsan_tools(built_lib):
     from aluminum_b200 import _build
     try:
-        return _build.build_sanitized("thread")
+        yield _build.build_sanitized("thread")
     except RuntimeError as e:
         if "no compiler" in str(e):
             pytest.skip(str(e))
         raise
+    finally:
+        _build.clean_sanitized("thread")  # instrumented builds are large; leave nothing behind
 
 
 def _clean(out: str) -> bool:
@@ -70,11 +72,13 @@ def test_socket_path_is_race_free(tsan_tools, bin_dir, op):
 def asan_tools(built_lib):
     from aluminum_b200 import _build
     try:
-        return _build.build_sanitized("address")
+        yield _build.build_sanitized("address")
     except RuntimeError as e:
         if "no compiler" in str(e):
             pytest.skip(str(e))
         raise
+    finally:
+        _build.clean_sanitized("address")
 
 
 def test_units_are_memory_clean(asan_tools):

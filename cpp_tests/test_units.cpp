@@ -210,6 +210,31 @@ static void test_progress_engine_concurrent_start() {
   }
 }
 
+// Ordering domains come and go (communicators are created and destroyed): released slots are reused,
+// so more than AL_PE_NUM_STREAMS domains can be served over the life of the engine.
+static void test_progress_engine_slot_reuse() {
+  ProgressEngine pe;
+  ProbeLog log;
+  std::atomic<int> running{0}, peak{0};
+  std::vector<int> keys(3 * AL_PE_NUM_STREAMS);
+  for (size_t k = 0; k < keys.size(); ++k) {
+    pe.enqueue(new ProbeState(&keys[k], (int)k, 3, &log, &running, &peak));
+    while (log.size() < k + 1) std::this_thread::yield();
+    pe.release_key(&keys[k]);
+  }
+  CHECK(log.size() == keys.size());
+  // Without release the table fills up and says so.
+  bool threw = false;
+  try {
+    for (size_t k = 0; k < keys.size(); ++k) pe.enqueue(new ProbeState(&keys[k], (int)k, 1, &log, &running, &peak));
+  } catch (const Al::al_exception&) {
+    threw = true;
+  }
+  CHECK(threw);
+  while (pe.in_flight()) std::this_thread::yield();
+  pe.stop();
+}
+
 static void test_reduce_and_halves() {
   using namespace Al::internal::host;
   for (float f : {0.f, 1.f, -2.5f, 65504.f, 6.1e-5f, 1e-7f, 0.333f}) {
@@ -283,6 +308,7 @@ int main() {
   test_pool();
   test_progress_engine();
   test_progress_engine_concurrent_start();
+  test_progress_engine_slot_reuse();
   test_reduce_and_halves();
   test_lifecycle_and_trace();
   if (g_fail) { fprintf(stderr, "%d check(s) failed\n", g_fail); return 1; }

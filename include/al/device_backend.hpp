@@ -48,6 +48,10 @@ cudaStream_t begin_nonblocking(DeviceCommunicator& comm);
 /** Record completion on `internal_stream` and build the request. */
 Request end_nonblocking(DeviceCommunicator& comm, cudaStream_t internal_stream);
 cudaStream_t begin_nonblocking_stream(cudaStream_t comm_stream);
+/** The same with a given internal stream instead of one from the pool. */
+cudaStream_t begin_nonblocking_on(cudaStream_t comm_stream, cudaStream_t internal);
+/** A new highest-priority, non-blocking stream (the caller destroys it). */
+cudaStream_t create_internal_stream();
 Request end_nonblocking_stream(cudaStream_t comm_stream, cudaStream_t internal_stream);
 bool test_request(Request& req);
 void wait_request(Request& req);

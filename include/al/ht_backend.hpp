@@ -12,12 +12,17 @@
  *   -> GPUWait.wait (stream stalls) -> H2D copy -> GPUStatusFlag.record.
  * The engine state waits for the first flag in pipeline stage 0, advances,
  * runs the host operation, signals the GPUWait and completes when the second
- * flag fires.  Every operation signals at the end (the reference lets roots /
- * non-roots of rooted operations signal early; that refinement is omitted).
+ * flag fires.  A rank that receives nothing back (non-root of reduce / gather,
+ * a pure send) is signalled as soon as its data has left the device, like the
+ * reference's early-signalling policies (ht/base_state.hpp:86-209); every
+ * other rank when the host exchange is complete.
  */
 #pragma once
+#include <memory>
+
 #include "al/device_backend.hpp"
 #include "al/host_backend.hpp"
+#include "al/progress.hpp"
 
 namespace Al {
 
@@ -41,10 +46,29 @@ class HostTransferCommunicator {
   int local_size() const { return host_.local_size(); }
   cudaStream_t get_stream() const { return stream_; }
   HostCommunicator& host() { return host_; }
+  /**
+   * The stream non-blocking operations of this communicator run on, created
+   * on first use.  Every host-transfer communicator has its own: an operation
+   * holds its stream until the host exchange is complete, so operations of
+   * different communicators must never queue behind one another - two ranks
+   * whose threads reach a shared stream in different orders would wait for
+   * each other forever.  (The reference shares its pooled internal streams.)
+   */
+  cudaStream_t internal_stream() {
+    if (!internal_) {
+      internal_ = std::shared_ptr<CUstream_st>(internal::device::create_internal_stream(),
+                                               [](cudaStream_t s) {
+                                                 internal::release_progress_key(s);
+                                                 (void)cudaStreamDestroy(s);
+                                               });
+    }
+    return internal_.get();
+  }
 
  private:
   HostCommunicator host_;
   cudaStream_t stream_;
+  std::shared_ptr<CUstream_st> internal_;
 };
 
 namespace internal {
@@ -72,7 +96,7 @@ class HostTransferBackend {
   static void run(internal::Resolved&& r, comm_type& comm, req_type* req) {
     using namespace internal::device;
     if (req) {
-      cudaStream_t s = begin_nonblocking_stream(comm.get_stream());
+      cudaStream_t s = begin_nonblocking_on(comm.get_stream(), comm.internal_stream());
       internal::ht::run_collective(std::move(r), comm, s);
       *req = end_nonblocking_stream(comm.get_stream(), s);
     } else {
@@ -88,7 +112,7 @@ class HostTransferBackend {
   static void run_p2p(std::vector<p2p_item>&& items, comm_type& comm, req_type* req, const char* name) {
     using namespace internal::device;
     if (req) {
-      cudaStream_t s = begin_nonblocking_stream(comm.get_stream());
+      cudaStream_t s = begin_nonblocking_on(comm.get_stream(), comm.internal_stream());
       internal::ht::run_p2p(std::move(items), comm, s, name);
       *req = end_nonblocking_stream(comm.get_stream(), s);
     } else {

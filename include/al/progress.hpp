@@ -46,7 +46,7 @@ class ProgressEngine {
   /** Stop and join; outstanding states are abandoned. */
   void stop();
   bool is_running() const { return started_.load(std::memory_order_acquire); }
-  /** Hand a heap-allocated state to the engine, which takes ownership. */
+  /** Hand a heap-allocated state to the engine, which takes ownership - also when it throws (table or queue full). */
   void enqueue(AlState* state);
   /** Human-readable dump of every run queue. Safe to call from a signal handler context on a best-effort basis. */
   std::ostream& dump_state(std::ostream& os);
@@ -54,6 +54,13 @@ class ProgressEngine {
   void set_hang_callback(std::function<void(const AlState&, double seconds)> cb);
   /** Device the engine thread makes current before running (set by the CUDA layer). */
   void set_device(int dev) { device_ = dev; }
+  /**
+   * Tell the engine that an ordering domain is gone (its communicator or
+   * stream was destroyed, nothing of it is in flight): the slot can serve a
+   * new key.  Without this a process that keeps creating communicators would
+   * run out of the AL_PE_NUM_STREAMS slots.
+   */
+  void release_key(const void* key);
   /** Number of states admitted and not yet completed. */
   size_t in_flight() const { return in_flight_.load(std::memory_order_acquire); }
   /** The core the thread was bound to, or -1. */
@@ -62,7 +69,7 @@ class ProgressEngine {
  private:
   struct InputQueue {
     explicit InputQueue(const void* k) : key(k), q(AL_PE_INPUT_QUEUE_SIZE) {}
-    const void* key;
+    std::atomic<const void*> key;  ///< read without a lock by enqueue(), changed under add_mu_
     MPSCQueue<AlState*> q;
   };
   struct StreamPipeline {
@@ -101,6 +108,10 @@ class ProgressEngine {
 
 /** The process-wide engine (created by Initialize). */
 ProgressEngine* get_progress_engine();
+/** The engine, or nullptr when the library is not initialised (destructors that may run after Finalize). */
+ProgressEngine* get_progress_engine_if_any();
+/** ProgressEngine::release_key on the process's engine, if there is one. */
+void release_progress_key(const void* key);
 
 }  // namespace internal
 }  // namespace Al

@@ -20,7 +20,19 @@ cudaStream_t begin_nonblocking(DeviceCommunicator& comm) { return begin_nonblock
 
 cudaStream_t begin_nonblocking_stream(cudaStream_t comm_stream) {
   if (tuning().disable_background_streams) return comm_stream;
-  cudaStream_t internal = cuda::stream_pool.get_high_priority_stream();
+  return begin_nonblocking_on(comm_stream, cuda::stream_pool.get_high_priority_stream());
+}
+
+cudaStream_t create_internal_stream() {
+  int least = 0, greatest = 0;
+  AL_CHECK_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+  cudaStream_t s = nullptr;
+  AL_CHECK_CUDA(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, greatest));
+  return s;
+}
+
+cudaStream_t begin_nonblocking_on(cudaStream_t comm_stream, cudaStream_t internal) {
+  if (tuning().disable_background_streams) return comm_stream;
   cudaEvent_t ev = cuda::event_pool.get();
   AL_CHECK_CUDA(cudaEventRecord(ev, comm_stream));
   AL_CHECK_CUDA(cudaStreamWaitEvent(internal, ev, 0));

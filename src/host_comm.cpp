@@ -167,7 +167,10 @@ HostCommunicator::Impl::Impl(const Group& g)
   }
 }
 
-HostCommunicator::Impl::~Impl() = default;
+HostCommunicator::Impl::~Impl() {
+  // Operations of this communicator were queued under its address; the slot can serve another one now.
+  if (ProgressEngine* pe = get_progress_engine_if_any()) pe->release_key(this);
+}
 
 namespace {
 

@@ -1,6 +1,8 @@
 // The progress engine thread (see al/progress.hpp for the contract).
 #include "al/progress.hpp"
 
+#include <memory>
+
 #include <pthread.h>
 #include <sched.h>
 
@@ -61,15 +63,32 @@ void ProgressEngine::stop() {
   started_.store(false, std::memory_order_release);
 }
 
+namespace {
+// Key of a slot whose ordering domain was released; never a valid stream or communicator address.
+const void* const kFreeKey = &kFreeKey;
+}  // namespace
+
+void ProgressEngine::release_key(const void* key) {
+  std::lock_guard<std::mutex> g(add_mu_);
+  const size_t n = num_queues_.load(std::memory_order_acquire);
+  for (size_t i = 0; i < n; ++i)
+    if (queues_[i]->key.load(std::memory_order_relaxed) == key) queues_[i]->key.store(kFreeKey, std::memory_order_release);
+}
+
 ProgressEngine::InputQueue* ProgressEngine::queue_for(const void* key) {
   // Fast path: lock-free scan of the published slots.
   size_t n = num_queues_.load(std::memory_order_acquire);
   for (size_t i = 0; i < n; ++i)
-    if (queues_[i]->key == key) return queues_[i];
+    if (queues_[i]->key.load(std::memory_order_acquire) == key) return queues_[i];
   std::lock_guard<std::mutex> g(add_mu_);
   n = num_queues_.load(std::memory_order_acquire);
   for (size_t i = 0; i < n; ++i)
-    if (queues_[i]->key == key) return queues_[i];
+    if (queues_[i]->key.load(std::memory_order_relaxed) == key) return queues_[i];
+  for (size_t i = 0; i < n; ++i)
+    if (queues_[i]->key.load(std::memory_order_relaxed) == kFreeKey) {  // reuse a released slot
+      queues_[i]->key.store(key, std::memory_order_release);
+      return queues_[i];
+    }
   if (n >= AL_PE_NUM_STREAMS)
     throw_al_exception("progress engine: more than ", AL_PE_NUM_STREAMS,
                        " distinct streams/communicators have outstanding asynchronous work");
@@ -79,10 +98,13 @@ ProgressEngine::InputQueue* ProgressEngine::queue_for(const void* key) {
 }
 
 void ProgressEngine::enqueue(AlState* state) {
+  // The engine owns the state from here on, also when it cannot take it.
+  std::unique_ptr<AlState> guard(state);
   if (!started_.load(std::memory_order_acquire)) run();
   InputQueue* q = queue_for(state->get_compute_stream());
   if (!q->q.try_push(state))
     throw_al_exception("progress engine input queue overflow (", AL_PE_INPUT_QUEUE_SIZE, " entries)");
+  guard.release();
   pending_inputs_.fetch_add(1, std::memory_order_release);
 }
 
@@ -97,7 +119,7 @@ std::ostream& ProgressEngine::dump_state(std::ostream& os) {
   const size_t n = num_queues_.load(std::memory_order_acquire);
   os << "Progress engine: " << n << " stream(s), " << in_flight_.load() << " state(s) in flight\n";
   for (size_t i = 0; i < n; ++i) {
-    os << " stream " << i << " key=" << queues_[i]->key << "\n";
+    os << " stream " << i << " key=" << queues_[i]->key.load() << "\n";
     for (int s = 0; s < AL_PE_NUM_PIPELINE_STAGES; ++s) {
       os << "  stage " << s << ":";
       for (AlState* st : pipelines_[i].stage[s]) {

@@ -137,6 +137,12 @@ ProgressEngine* get_progress_engine() {
   return g_rt->pe.get();
 }
 
+ProgressEngine* get_progress_engine_if_any() { return g_rt ? g_rt->pe.get() : nullptr; }
+
+void release_progress_key(const void* key) {
+  if (g_rt && g_rt->pe) g_rt->pe->release_key(key);
+}
+
 World* get_world() {
   if (!g_rt) throw_al_exception("the library is not initialised (call Al::Initialize first)");
   return g_rt->world.get();

@@ -179,7 +179,7 @@ def test_host_transfer_backend_threads_and_permuted_ranks(al, bin_dir):
     whose ranks are swapped; the progress thread serves both streams."""
     r = subprocess.run([str(bin_dir / "alrun"), "-n", "2", "--timeout", "120", str(bin_dir / "test_ops"),
                         "--backend", "ht", "--op", "allreduce", "--max-size", "16384", "--threads", "2",
-                        "--permute", "1,0", "--nonblocking"],
+                        "--permute", "1,0", "--nonblocking", "--hang-timeout", "20"],
                        capture_output=True, text=True, timeout=180, env={**__import__("os").environ, "AL_GPU_ID": "0"})
     assert r.returncode == 0 and "threads=2: ok" in r.stdout, r.stdout + r.stderr
 

@@ -186,3 +186,23 @@ def test_serialized_mode_runs_blocking_calls_on_the_progress_thread(bin_dir, tmp
     assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
     text = next(iter(tmp_path.glob("*.trace.txt"))).read_text()
     assert "PE START HostAllreduce" in text  # a blocking call went through the engine
+
+
+def test_many_short_lived_communicators(bin_dir, tmp_path):
+    """More communicators than the progress engine has slots, one after another, each with a
+    non-blocking operation: destroyed communicators give their slot back."""
+    script = tmp_path / "many.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path.insert(0, {str(ROOT)!r})\n"
+        "import aluminum_b200 as al\n"
+        "w = al.HostComm()\n"
+        "for i in range(150):\n"
+        "    c = w.split(0, w.rank)\n"
+        "    x = np.ones(8, dtype=np.float32)\n"
+        "    c.allreduce(x, nonblocking=True).wait()\n"
+        "    assert x[0] == c.size\n"
+        "    c.close()\n"
+        "print('many ok')\n")
+    r = run([bin_dir / "alrun", "-n", "2", "--timeout", "120", sys.executable, script])
+    assert r.returncode == 0 and r.stdout.count("many ok") == 2, r.stdout + r.stderr

@@ -1,6 +1,7 @@
 // stress_progress - many small non-blocking allreduces in flight at once.
 //
 //   alrun -n 8 stress_progress [--ops 64] [--streams 8] [--rounds 20] [--min-bytes 4096] [--max-bytes 262144]
+//                              [--backend device|host]
 //
 // Per rank: `streams` CUDA streams, one device communicator per stream (the library's
 // model: a communicator is bound to a stream), `ops` NonblockingAllreduce calls with
@@ -9,6 +10,9 @@
 // and the Wait are stream memory operations (cuStreamWriteValue32 / cuStreamWaitValue32),
 // so nothing in the loop synchronises with the host.  Reports operations per second
 // (max over ranks of the round time) and the p50 / p99 of the per-operation device time.
+// --backend host runs the same pattern on host memory: `streams` host communicators, all
+// operations started before the first Wait, so the progress thread has `ops` states queued
+// at once (it admits a bounded number per communicator); times are host clock.
 #include <algorithm>
 #include <random>
 
@@ -16,10 +20,58 @@
 
 using namespace altest;
 
+// The host form of the stress: every operation of a round is started before any is waited for.
+static int stress_host(const Args& a) {
+  const int nops = (int)a.num("ops", 64), ncomms = (int)a.num("streams", 8), rounds = (int)a.num("rounds", 20);
+  const double lo = std::log((double)a.num("min-bytes", 4096)), hi = std::log((double)a.num("max-bytes", 262144));
+  Al::HostCommunicator hc;
+  std::vector<Al::HostCommunicator> comms;
+  for (int i = 0; i < ncomms; ++i) comms.push_back(hc.copy());
+  std::mt19937 rng(1);
+  std::uniform_real_distribution<double> U(lo, hi);
+  std::vector<std::vector<float>> bufs((size_t)nops);
+  for (auto& b : bufs) b.assign(std::max<size_t>(1, (size_t)std::exp(U(rng)) / 4), 1.0f);
+  std::vector<double> round_us, op_us;
+  std::vector<Al::HostBackend::req_type> reqs((size_t)nops);
+  std::vector<double> t_start((size_t)nops);
+  for (int r = 0; r < rounds + 3; ++r) {
+    Al::Barrier<Al::HostBackend>(hc);
+    const double t0 = Al::get_time();
+    for (int i = 0; i < nops; ++i) {
+      t_start[(size_t)i] = Al::get_time();
+      Al::NonblockingAllreduce<Al::HostBackend>(bufs[(size_t)i].data(), bufs[(size_t)i].size(), Al::ReductionOperator::max,
+                                                comms[(size_t)(i % ncomms)], reqs[(size_t)i]);
+    }
+    for (int i = 0; i < nops; ++i) {
+      Al::Wait<Al::HostBackend>(reqs[(size_t)i]);
+      if (r >= 3) op_us.push_back((Al::get_time() - t_start[(size_t)i]) * 1e6);
+    }
+    if (r >= 3) round_us.push_back((Al::get_time() - t0) * 1e6);
+  }
+  for (auto& b : bufs)
+    if (b.front() != 1.0f || b.back() != 1.0f) throw_al_exception("wrong result");
+  std::vector<double> worst(round_us.size());
+  Al::Allreduce<Al::HostBackend>((const double*)round_us.data(), worst.data(), round_us.size(), Al::ReductionOperator::max, hc);
+  std::sort(worst.begin(), worst.end());
+  std::sort(op_us.begin(), op_us.end());
+  if (hc.rank() == 0) {
+    const double med = worst[worst.size() / 2];
+    printf("stress backend=host ranks=%d communicators=%d ops=%d round_median_us=%.1f ops_per_s=%.0f op_p50_us=%.1f op_p99_us=%.1f\n",
+           hc.size(), ncomms, nops, med, nops / (med * 1e-6), op_us[op_us.size() / 2], op_us[(size_t)(op_us.size() * 0.99)]);
+  }
+  Al::Barrier<Al::HostBackend>(hc);
+  return 0;
+}
+
 int main(int argc, char** argv) {
   Args a(argc, argv);
   try {
     Al::Initialize(argc, argv);
+    if (a.str("backend", "device") == "host") {
+      const int rc = stress_host(a);
+      Al::Finalize();
+      return rc;
+    }
     const int nops = (int)a.num("ops", 64), nstreams = (int)a.num("streams", 8), rounds = (int)a.num("rounds", 20);
     const double lo = std::log((double)a.num("min-bytes", 4096)), hi = std::log((double)a.num("max-bytes", 262144));
     Al::HostCommunicator hc;

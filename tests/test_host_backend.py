@@ -206,3 +206,10 @@ def test_many_short_lived_communicators(bin_dir, tmp_path):
         "print('many ok')\n")
     r = run([bin_dir / "alrun", "-n", "2", "--timeout", "120", sys.executable, script])
     assert r.returncode == 0 and r.stdout.count("many ok") == 2, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("launch", [["-n", "4"], ["-n", "4", "--nodes", "2"]])
+def test_progress_engine_stress_on_cpu_ranks(bin_dir, launch):
+    """64 non-blocking allreduces of 4-256 KB on 8 communicators started before the first Wait."""
+    r = run([bin_dir / "alrun", *launch, "--timeout", "200", bin_dir / "stress_progress", "--backend", "host", "--rounds", "5"])
+    assert r.returncode == 0 and "ops_per_s=" in r.stdout, r.stdout + r.stderr

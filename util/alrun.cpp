@@ -73,6 +73,9 @@ int main(int argc, char** argv) {
         setenv("AL_NODE_ID", ("node" + std::to_string(r / per_node)).c_str(), 1);
         setenv("MASTER_ADDR", "127.0.0.1", 1);
         setenv("AL_MASTER_PORT", std::to_string(port).c_str(), 1);
+        // Progress threads are pinned by node-local rank; the modelled nodes share this machine's
+        // cores, so equal local ranks would land on one core.  Leave the threads unpinned.
+        setenv("AL_PE_BIND", "0", 0);
       }
       execvp(argv[i], argv + i);
       perror("execvp");

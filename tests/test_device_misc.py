@@ -174,16 +174,6 @@ def test_host_transfer_backend(al, bin_dir, op):
     assert r.returncode == 0, r.stdout + r.stderr
 
 
-def test_host_transfer_backend_threads_and_permuted_ranks(al, bin_dir):
-    """Two user threads per rank, each with its own stream and communicator, on a communicator
-    whose ranks are swapped; the progress thread serves both streams."""
-    r = subprocess.run([str(bin_dir / "alrun"), "-n", "2", "--timeout", "120", str(bin_dir / "test_ops"),
-                        "--backend", "ht", "--op", "allreduce", "--max-size", "16384", "--threads", "2",
-                        "--permute", "1,0", "--nonblocking", "--hang-timeout", "20"],
-                       capture_output=True, text=True, timeout=180, env={**__import__("os").environ, "AL_GPU_ID": "0"})
-    assert r.returncode == 0 and "threads=2: ok" in r.stdout, r.stdout + r.stderr
-
-
 def test_single_gpu_tools(al, bin_dir):
     """Wait / event micro-benchmarks and the single-rank device examples run on this GPU."""
     for tool, needle in (("benchmark_waits", "signal-to-pass"), ("benchmark_events", "pinned flag"),

@@ -55,7 +55,7 @@ TOOLS = {
 
 def _headers_digest() -> str:
     h = hashlib.sha1()
-    for d in (ROOT / "include", ROOT / "kernels", ROOT / "cpp_tests", ROOT / "benchmark", ROOT / "examples"):
+    for d in (ROOT / "include", ROOT / "kernels", ROOT / "src", ROOT / "cpp_tests", ROOT / "benchmark", ROOT / "examples"):
         if not d.exists():
             continue
         for f in sorted(d.rglob("*")):

@@ -163,6 +163,8 @@ HostCommunicator::Impl::Impl(const Group& g)
       const bool leader = local_index[(size_t)me] == 0;
       Group lg = g.split(leader ? 0 : 1, me);  // collective over all members; only the leaders build on it
       if (leader) leader_comm.reset(new HostCommunicator(lg));
+      const bool even = *std::min_element(per_node.begin(), per_node.end()) == *std::max_element(per_node.begin(), per_node.end());
+      if (even) rail_comm.reset(new HostCommunicator(g.split(local_index[(size_t)me], me)));
     }
   }
 }

@@ -1,13 +1,18 @@
 // Two-level collectives of a host communicator that spans nodes: shared memory
 // inside each node, sockets between the nodes' first members.
 //
-// Allreduce = reduce to the node's first member, allreduce among the first
+// Small allreduce = reduce to the node's first member, allreduce among the first
 // members, broadcast inside the node; bcast and barrier are composed the same
-// way.  It is the latency path: messages above Tuning::host_two_level_max_bytes,
-// every other operation, and allreduce with the averaging operator use the
-// flat socket path.  The parts are ordinary operations of the two
+// way (the latency path, up to Tuning::host_two_level_max_bytes).  Large
+// allreduce, when every node holds the same number of members = reduce-scatter
+// inside the node, allreduce of each slice among the members with the same
+// node-local rank (all of a node's members use their connections at once, and
+// only 1/local_size of the vector crosses the network per member), allgather
+// inside the node.  Everything else, and allreduce with the averaging
+// operator, uses the flat socket path.  The parts are ordinary operations of the two
 // sub-communicators, run one after another by one composite state, so the
 // composite inherits their time-outs and failure reports.
+#include <algorithm>
 #include <memory>
 
 #include "host_impl.hpp"
@@ -32,6 +37,37 @@ class HierCollState final : public HostState {
     };
     switch (a.kind) {
       case Coll::allreduce: {
+        if (a.count * dtype_size(a.dt) > tuning().host_two_level_max_bytes) {
+          // Bandwidth path over the rails.
+          const int L = node->p, li = node->me;
+          const size_t esz = dtype_size(a.dt);
+          std::vector<size_t> counts((size_t)L), displs((size_t)L);
+          const size_t per = (a.count + (size_t)L - 1) / (size_t)L;
+          for (int r = 0; r < L; ++r) {
+            displs[(size_t)r] = std::min(a.count, (size_t)r * per);
+            counts[(size_t)r] = std::min(per, a.count - displs[(size_t)r]);
+          }
+          char* slice = (char*)a.recv + displs[(size_t)li] * esz;  // this member's slice, reduced in place in recv
+          CollArgs rs = base(Coll::reduce_scatter);
+          rs.vector = true;
+          rs.send = a.send;
+          rs.recv = slice;
+          rs.recv_counts = counts; rs.send_counts = counts; rs.send_displs = displs;
+          rs.recv_displs.assign((size_t)L, 0);
+          add(node, std::move(rs));
+          CollArgs ar = base(Coll::allreduce);
+          ar.count = counts[(size_t)li];
+          ar.send = slice; ar.recv = slice;
+          add(ci->rail_comm->impl(), std::move(ar));
+          CollArgs ag = base(Coll::allgather);
+          ag.vector = true;
+          ag.send = slice;
+          ag.recv = a.recv;
+          ag.recv_counts = counts; ag.recv_displs = displs; ag.send_counts = counts;
+          ag.send_displs.assign((size_t)L, 0);
+          add(node, std::move(ag));
+          break;
+        }
         CollArgs r = base(Coll::reduce);
         r.send = a.send;
         r.recv = leader ? a.recv : nullptr;
@@ -137,7 +173,8 @@ HostState* make_hier_collective(HostCommunicator::Impl* ci, CollArgs& args, Requ
   if (!fits || !ci->node_comm) return nullptr;
   // Large messages are bandwidth-bound: the flat path moves them over every member's connections at
   // once, the two-level path over one connection per node.  (Every member evaluates the same test.)
-  if (args.kind != Coll::barrier && args.count * dtype_size(args.dt) > tuning().host_two_level_max_bytes) return nullptr;
+  const bool large = args.count * dtype_size(args.dt) > tuning().host_two_level_max_bytes;
+  if (large && !(args.kind == Coll::allreduce && ci->rail_comm)) return nullptr;
   return new HierCollState(ci, args, std::move(req), seq);
 }
 

@@ -36,6 +36,8 @@ struct HostCommunicator::Impl {
   // Two-level layout of a communicator that spans nodes and has a node with several members:
   // a shared-memory communicator per node and a socket communicator of the nodes' first members.
   std::unique_ptr<HostCommunicator> node_comm, leader_comm;  // leader_comm only on the first member of a node
+  // When every node holds the same number of members: the members with equal node-local rank, one per node.
+  std::unique_ptr<HostCommunicator> rail_comm;
   std::vector<int> node_of;       // member -> index of its node (nodes numbered by their lowest member)
   std::vector<int> local_index;   // member -> rank inside its node's communicator
   int p = 1, me = 0;

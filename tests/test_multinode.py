@@ -104,8 +104,14 @@ def test_two_level_path_is_taken_for_small_messages(bin_dir, tmp_path):
                      "host", "--op", op, "--max-size", "65536", "--odd-sizes", "--zero", "--root", "4"] + extra, env=env)
             assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
     text = "".join(f.read_text() for f in tmp_path.glob("*.trace.txt"))
-    for name in ("HierAllreduce", "HierBcast", "HierBarrier", "NetAllreduce", "NetBcast"):
+    # small messages and (over the rails) large allreduce: composites; large bcast: flat sockets
+    for name in ("HierAllreduce", "HierBcast", "HierBarrier", "NetBcast"):
         assert name in text, name
     r = run([bin_dir / "alrun", "-n", "6", "--nodes", "3", "--timeout", "120", bin_dir / "test_ops", "--backend", "host",
              "--op", "allreduce", "--max-size", "4096", "--threads", "2", "--nonblocking"], env={"AL_HOST_TWO_LEVEL": "0"})
     assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr
+    # uneven nodes (3 + 2 members): no rails, large allreduce falls back to the flat path; tiny staging: many chunks
+    for launch, env2 in ((["-n", "5", "--nodes", "2"], {}), (["-n", "6", "--nodes", "2"], {"AL_HOST_STAGE_BYTES": "65536"})):
+        r = run([bin_dir / "alrun", *launch, "--timeout", "120", bin_dir / "test_ops", "--backend", "host", "--op",
+                 "allreduce", "--max-size", "1048576", "--odd-sizes", "--inplace"], env=env2)
+        assert r.returncode == 0 and ": ok" in r.stdout, r.stdout + r.stderr

@@ -66,7 +66,14 @@ int al_info(char* buf, size_t buflen) {
     std::ostringstream ss;
     ss << "Aluminum-B200 " << AL_VERSION << "\nBackends: host device host-transfer rma\n"
        << "nvtx: " << (profiling::nvtx_available() ? "found" : "not found") << "\n--- tuning ---\n"
-       << tuning().describe() << "--- topology ---\n";
+       << tuning().describe();
+    if (Initialized()) {
+      World* w = get_world();
+      ss << "--- world ---\n"
+         << "rank " << w->rank() << " of " << w->size() << ", local rank " << w->local_rank() << " of " << w->local_size()
+         << ", node " << w->node_index(w->rank()) << " of " << w->num_nodes() << " (" << w->node_of(w->rank()) << ")\n";
+    }
+    ss << "--- topology ---\n";
     if (cuda::device_usable()) ss << device::discover_topology().describe();
     else ss << "no CUDA device usable in this process\n";
     const std::string s = ss.str();

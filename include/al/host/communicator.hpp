@@ -4,7 +4,7 @@
  *
  * Role: what the reference's MPI backend provides - collectives and
  * point-to-point on host memory, blocking and non-blocking through the
- * progress engine (include/aluminum/mpi_impl.hpp, include/aluminum/mpi/*.hpp,
+ * progress engine (include/aluminum/mpi_impl.hpp, the headers under include/aluminum/mpi,
  * communicator at include/aluminum/mpi/communicator.hpp:49-97).  There is no
  * MPI underneath.  When all members are on one node they share a POSIX
  * shared-memory workspace per communicator and run the same flag protocol the

@@ -4,6 +4,7 @@ ranks are started by the library's own launcher).
 
     python cpp_tests/run_tests.py --backends host --max-ranks 4
     python cpp_tests/run_tests.py --backends device --max-ranks 8      # one GPU per rank
+    python cpp_tests/run_tests.py --backends host --max-ranks 8 --nodes 1 2 4   # also over modelled nodes (TCP)
 """
 import argparse
 import itertools
@@ -25,14 +26,20 @@ def main():
     ap.add_argument("--max-size", type=int, default=1 << 14)
     ap.add_argument("--timeout", type=int, default=60)
     ap.add_argument("--max-fails", type=int, default=5)
+    ap.add_argument("--nodes", nargs="+", type=int, default=[1],
+                    help="node counts to model on this machine (host / ht backends; 1 = everything on one node)")
     a = ap.parse_args()
     ranks = [n for n in (1, 2, 4, 8) if n <= a.max_ranks]
     fails = total = 0
-    for n, be, op, dt, nb, ip in itertools.product(ranks, a.backends, OPS, a.datatypes, (False, True), (False, True)):
+    for n, nodes, be, op, dt, nb, ip in itertools.product(ranks, a.nodes, a.backends, OPS, a.datatypes, (False, True),
+                                                         (False, True)):
         if op in ("barrier", "send", "bcast") and ip:
             continue
+        if nodes > 1 and (nodes > n or be == "device"):
+            continue  # a device communicator lives inside one node
         for root in ((0, 1) if op in ROOTED and n > 1 else (0,)):
-            cmd = [str(BIN / "alrun"), "-n", str(n), "--timeout", str(a.timeout), str(BIN / "test_ops"), "--backend", be,
+            launch = ["--nodes", str(nodes)] if nodes > 1 else []
+            cmd = [str(BIN / "alrun"), "-n", str(n), *launch, "--timeout", str(a.timeout), str(BIN / "test_ops"), "--backend", be,
                    "--op", op, "--datatype", dt, "--max-size", str(a.max_size), "--odd-sizes", "--zero", "--quiet",
                    "--root", str(root), "--hang-timeout", str(max(5, a.timeout // 2))]
             cmd += ["--nonblocking"] if nb else []
@@ -44,7 +51,7 @@ def main():
                 rc = -1
             if rc != 0:
                 fails += 1
-                print("FAIL:", " ".join(cmd[4:]), file=sys.stderr)
+                print("FAIL:", " ".join(cmd[1:3] + launch + cmd[5 + len(launch):]), file=sys.stderr)
                 if fails >= a.max_fails:
                     print(f"stopping after {fails} failures", file=sys.stderr)
                     return 1

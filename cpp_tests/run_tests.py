@@ -23,13 +23,14 @@ def main():
     ap.add_argument("--backends", nargs="+", default=["host"])
     ap.add_argument("--datatypes", nargs="+", default=["float", "int"])
     ap.add_argument("--max-ranks", type=int, default=4)
+    ap.add_argument("--min-ranks", type=int, default=1)
     ap.add_argument("--max-size", type=int, default=1 << 14)
     ap.add_argument("--timeout", type=int, default=60)
     ap.add_argument("--max-fails", type=int, default=5)
     ap.add_argument("--nodes", nargs="+", type=int, default=[1],
                     help="node counts to model on this machine (host / ht backends; 1 = everything on one node)")
     a = ap.parse_args()
-    ranks = [n for n in (1, 2, 4, 8) if n <= a.max_ranks]
+    ranks = [n for n in (1, 2, 4, 8) if a.min_ranks <= n <= a.max_ranks]
     fails = total = 0
     for n, nodes, be, op, dt, nb, ip in itertools.product(ranks, a.nodes, a.backends, OPS, a.datatypes, (False, True),
                                                          (False, True)):
@@ -45,13 +46,16 @@ def main():
             cmd += ["--nonblocking"] if nb else []
             cmd += ["--inplace"] if ip else []
             total += 1
+            tail = ""
             try:
-                rc = subprocess.run(cmd, capture_output=True, text=True, timeout=2 * a.timeout).returncode
+                r = subprocess.run(cmd, capture_output=True, text=True, timeout=2 * a.timeout)
+                rc, tail = r.returncode, (r.stdout + r.stderr)[-600:]
             except subprocess.TimeoutExpired:
-                rc = -1
+                rc, tail = -1, "timed out"
             if rc != 0:
                 fails += 1
                 print("FAIL:", " ".join(cmd[1:3] + launch + cmd[5 + len(launch):]), file=sys.stderr)
+                print("      " + tail.strip().replace("\n", "\n      "), file=sys.stderr)
                 if fails >= a.max_fails:
                     print(f"stopping after {fails} failures", file=sys.stderr)
                     return 1

@@ -19,6 +19,8 @@
  *         MASTER_ADDR:AL_MASTER_PORT (default MASTER_PORT + 1), collects every
  *         rank's node name, address and listening port and hands the table to
  *         everyone; pairs on the same node still connect through Unix sockets.
+ *         AL_MASTER_FD (set by alrun --nodes) passes rank 0 a socket that is
+ *         already listening on that port.
  *   auto  tcp when MASTER_ADDR is set and the launcher reports more ranks than
  *         local ranks (LOCAL_WORLD_SIZE < WORLD_SIZE, SLURM_NNODES > 1,
  *         AL_NNODES > 1), else unix.

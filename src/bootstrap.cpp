@@ -267,7 +267,10 @@ std::unique_ptr<World> World::connect_tcp(int rank, int size, int local_rank_hin
   memset(table.data(), 0, table.size() * sizeof(TableEntry));
   const std::string master_ip = resolve_ipv4(master_addr);
   if (rank == 0) {
-    int mfd = tcp_listen(master_port, size, nullptr);
+    // A launcher may hand over the rendezvous socket already listening (no window in which
+    // another process could take the port); otherwise listen on the agreed port.
+    const long inherited = env_long("AL_MASTER_FD", -1);
+    int mfd = inherited >= 0 ? (int)inherited : tcp_listen(master_port, size, nullptr);
     std::vector<int> fds;
     auto close_all = [&] { for (int f : fds) ::close(f); ::close(mfd); };
     snprintf(table[0].node, sizeof(table[0].node), "%s", node_id.c_str());

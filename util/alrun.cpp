@@ -26,19 +26,22 @@
 #include <thread>
 #include <vector>
 
-// A TCP port that was free a moment ago (bind to 0, read it back, close).
-static int pick_free_port() {
+// A listening TCP socket on a free port of the loopback interface.  The launcher keeps it open and
+// hands it to rank 0 (AL_MASTER_FD), so no other process can take the port in between.
+static int open_rendezvous(int backlog, int* port) {
   int fd = socket(AF_INET, SOCK_STREAM, 0);
-  if (fd < 0) return 29500;
+  if (fd < 0) return -1;
   sockaddr_in a{};
   a.sin_family = AF_INET;
   a.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
   a.sin_port = 0;
   socklen_t len = sizeof(a);
-  int port = 29500;
-  if (bind(fd, (sockaddr*)&a, sizeof(a)) == 0 && getsockname(fd, (sockaddr*)&a, &len) == 0) port = ntohs(a.sin_port);
-  close(fd);
-  return port;
+  if (bind(fd, (sockaddr*)&a, sizeof(a)) != 0 || listen(fd, backlog) != 0 || getsockname(fd, (sockaddr*)&a, &len) != 0) {
+    close(fd);
+    return -1;
+  }
+  *port = ntohs(a.sin_port);
+  return fd;
 }
 
 int main(int argc, char** argv) {
@@ -56,7 +59,9 @@ int main(int argc, char** argv) {
     return 2;
   }
   const int per_node = nodes > 0 ? (n + nodes - 1) / nodes : n;
-  const int port = nodes > 0 ? pick_free_port() : 0;
+  int port = 0;
+  const int rendezvous_fd = nodes > 0 ? open_rendezvous(n, &port) : -1;
+  if (nodes > 0 && rendezvous_fd < 0) { perror("alrun: rendezvous socket"); return 2; }
   const std::string key = "alrun-" + std::to_string(getpid()) + "-" +
                           std::to_string(std::chrono::steady_clock::now().time_since_epoch().count());
   std::vector<pid_t> kids;
@@ -73,6 +78,8 @@ int main(int argc, char** argv) {
         setenv("AL_NODE_ID", ("node" + std::to_string(r / per_node)).c_str(), 1);
         setenv("MASTER_ADDR", "127.0.0.1", 1);
         setenv("AL_MASTER_PORT", std::to_string(port).c_str(), 1);
+        if (r == 0) setenv("AL_MASTER_FD", std::to_string(rendezvous_fd).c_str(), 1);  // inherited, already listening
+        else close(rendezvous_fd);
         // Progress threads are pinned by node-local rank; the modelled nodes share this machine's
         // cores, so equal local ranks would land on one core.  Leave the threads unpinned.
         setenv("AL_PE_BIND", "0", 0);
@@ -83,6 +90,7 @@ int main(int argc, char** argv) {
     }
     kids.push_back(pid);
   }
+  if (rendezvous_fd >= 0) close(rendezvous_fd);  // rank 0 holds its own copy
   const auto t0 = std::chrono::steady_clock::now();
   int failures = 0;
   size_t left = kids.size();

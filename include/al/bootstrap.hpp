@@ -88,6 +88,13 @@ class World {
   void send_fd(int peer, int fd);
   int recv_fd(int peer);
 
+  /**
+   * False once `peer`'s end of the control connection is closed: the process
+   * has exited (or finalised the library) and will never take part in anything
+   * again.  Non-blocking; safe to call from any thread.
+   */
+  bool peer_alive(int peer) const;
+
   /** Serialises whole collectives issued by different threads. */
   std::mutex& collective_mutex() { return coll_mu_; }
   BootstrapFaults faults;

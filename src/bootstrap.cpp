@@ -442,6 +442,19 @@ void World::recv(int peer, void* buf, size_t bytes) {
   read_all(socks_.at((size_t)peer), buf, bytes, timeout_s(faults), peer);
 }
 
+bool World::peer_alive(int peer) const {
+  if (peer == rank_) return true;
+  const int fd = socks_.at((size_t)peer);
+  if (fd < 0) return true;
+  pollfd pf{fd, POLLIN | POLLRDHUP, 0};
+  if (::poll(&pf, 1, 0) <= 0) return true;
+  if (pf.revents & (POLLRDHUP | POLLHUP | POLLERR | POLLNVAL)) return false;
+  // Readable: either a control message is waiting (alive) or the stream ended (a read of 0 bytes).
+  char c;
+  const ssize_t n = ::recv(fd, &c, 1, MSG_PEEK | MSG_DONTWAIT);
+  return n != 0;
+}
+
 void World::send_fd(int peer, int fd) {
   if (!same_node(peer))
     throw_al_exception("rank ", peer, " is on another node (", node_of(peer), "): descriptors cannot be passed to it");

@@ -133,6 +133,8 @@ HostCommunicator::Impl::Impl(const Group& g)
     : p(g.size()), me(g.rank()), send_next((size_t)g.size()), send_serving((size_t)g.size()),
       recv_next((size_t)g.size()), recv_serving((size_t)g.size()), sent_count((size_t)g.size(), 0),
       acked_count((size_t)g.size(), 0) {
+  world = g.world();
+  world_rank_of = g.members();
   for (int i = 0; i < p; ++i) {
     send_next[(size_t)i] = 0; send_serving[(size_t)i] = 0;
     recv_next[(size_t)i] = 0; recv_serving[(size_t)i] = 0;
@@ -237,7 +239,7 @@ class CollState final : public HostState {
         }
         case Phase::wait_a: {
           if (!all_reached(&Workspace::A, epoch(seq_, c_ + 1))) {
-            if (timed_out("peers to arrive")) return done();
+            if (missing_peer_gone(&Workspace::A, epoch(seq_, c_ + 1)) || timed_out("peers to arrive")) return done();
             return PEAction::cont;
           }
           progress_made();
@@ -259,7 +261,7 @@ class CollState final : public HostState {
         }
         case Phase::wait_b: {
           if (!all_reached(&Workspace::B, epoch(seq_, c_ + 1))) {
-            if (timed_out("peers' reduced slices")) return done();
+            if (missing_peer_gone(&Workspace::B, epoch(seq_, c_ + 1)) || timed_out("peers' reduced slices")) return done();
             return PEAction::cont;
           }
           progress_made();
@@ -280,7 +282,7 @@ class CollState final : public HostState {
           return done();
         case Phase::wait_c:
           if (!all_reached(&Workspace::C, epoch(seq_, 1))) {
-            if (timed_out("the closing barrier")) return done();
+            if (missing_peer_gone(&Workspace::C, epoch(seq_, 1)) || timed_out("the closing barrier")) return done();
             return PEAction::cont;
           }
           return done();
@@ -312,6 +314,18 @@ class CollState final : public HostState {
     ci_->done_seq.store(seq_, std::memory_order_release);
     publish_outcome();
     return PEAction::complete;
+  }
+
+  /** One of the ranks whose flag is still behind has exited: fail now (its flag can never come). */
+  bool missing_peer_gone(flag_t* (Workspace::*which)(int, int) const, uint64_t e) {
+    for (int r = 0; r < p_; ++r) {
+      if (r == me_ || (ws_.*which)(me_, r)->load(std::memory_order_acquire) >= e) continue;
+      if (!peer_gone(r)) return false;  // one check per call keeps the wait loop cheap
+      if ((ws_.*which)(me_, r)->load(std::memory_order_acquire) >= e) return false;  // it signalled before it left
+      fail(build_string(get_name(), ": rank ", r, " has exited (its control connection is closed)"));
+      return true;
+    }
+    return false;
   }
 
   bool all_reached(flag_t* (Workspace::*which)(int, int) const, uint64_t e) {
@@ -540,7 +554,7 @@ class P2PState final : public HostState {
       return PEAction::complete;
     }
     if (moved) progress_made();
-    else if (timed_out("the matching send/receive")) {
+    else if (pending_peer_gone() || timed_out("the matching send/receive")) {
       // Release the tickets so that later transfers fail fast instead of queueing forever.
       for (auto& x : xfers_)
         if (!x.done) {
@@ -554,6 +568,24 @@ class P2PState final : public HostState {
   }
 
  private:
+  /** The peer of a transfer that is at the head of its queue has exited and left nothing to read. */
+  bool pending_peer_gone() {
+    const int me = ci_->me;
+    for (auto& x : xfers_) {
+      if (x.done) continue;
+      const int peer = x.item.peer;
+      auto& serving = x.item.is_send ? ci_->send_serving : ci_->recv_serving;
+      if (peer == me || serving[(size_t)peer].load(std::memory_order_acquire) != x.ticket) continue;
+      if (!peer_gone(peer)) return false;  // one check per call
+      if (!x.item.is_send &&
+          ws_.sent(me, peer)->load(std::memory_order_acquire) != ci_->acked_count[(size_t)peer])
+        return false;  // it left, but its message is in the mailbox
+      fail(build_string(name_, ": rank ", peer, " has exited (its control connection is closed)"));
+      return true;
+    }
+    return false;
+  }
+
   struct Xfer {
     P2PItem item;
     uint64_t ticket = 0;

@@ -41,6 +41,8 @@ struct HostCommunicator::Impl {
   std::vector<int> node_of;       // member -> index of its node (nodes numbered by their lowest member)
   std::vector<int> local_index;   // member -> rank inside its node's communicator
   int p = 1, me = 0;
+  internal::World* world = nullptr;
+  std::vector<int> world_rank_of;      // member -> world rank (for liveness checks and messages)
   std::atomic<uint64_t> next_seq{1};   // collective sequence numbers handed out at call time
   std::atomic<uint64_t> done_seq{0};   // last collective that finished locally
   std::vector<std::atomic<uint64_t>> send_next, send_serving, recv_next, recv_serving;
@@ -95,6 +97,20 @@ class HostState : public AlState {
     return false;
   }
   void progress_made() { wait_since_ = 0; }
+  /**
+   * While waiting for member `r`: has its process gone?  Looks at the control
+   * connection at most every 50 ms.  A rank that exited can never arrive, so
+   * the caller fails at once instead of sitting out the time-out.
+   */
+  bool peer_gone(int r) {
+    const double now = get_time();
+    if (now - last_alive_check_ < 0.05 && r == last_alive_rank_) return false;
+    last_alive_check_ = now;
+    last_alive_rank_ = r;
+    return ci_->world && !ci_->world->peer_alive(ci_->world_rank_of[(size_t)r]);
+  }
+  double last_alive_check_ = 0;
+  int last_alive_rank_ = -1;
   // The outcome reaches the request only in publish_outcome(), the last thing a
   // state does: once the request is complete its owner may destroy the
   // communicator, so nothing of *ci_ may be touched afterwards.

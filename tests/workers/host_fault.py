@@ -1,6 +1,7 @@
 """Failure detection on CPU ranks: rank 1 never joins the second collective (it exits between
-steps, with nothing in flight); rank 0 must get an exception within the configured wait limit
-instead of hanging, and the communicator must then refuse further work."""
+steps, with nothing in flight); rank 0 must get an exception promptly instead of hanging - the
+closed control connection tells it long before the wait limit (60 s here) - and the communicator
+must then refuse further work."""
 import sys
 import time
 from pathlib import Path
@@ -24,8 +25,8 @@ try:
     sys.exit(2)
 except al.AlError as e:
     dt = time.time() - t0
-    assert "timed out" in str(e), str(e)
-    assert dt < 10, dt
+    assert "has exited" in str(e), str(e)
+    assert dt < 5, dt
 try:
     comm.allreduce(x)
     sys.exit(3)

@@ -83,6 +83,8 @@ elif mode == "abort":
             assert "failed" in str(e), str(e)
         s = comm.stats()
         assert s["failures"] >= 1 and s["collectives"] == 1 and s["p2p_ops"] == 1, s
+    else:
+        time.sleep(1.0)   # stay alive: a rank that exits is noticed by its peers, which is not what is tested here
     print(f"rank {me}: abort ok")
 elif mode == "jitter":
     rng = np.random.default_rng(1234)

@@ -58,7 +58,8 @@ elif mode == "dead":
         sys.exit(2)
     except al.AlError as e:
         assert time.time() - t0 < 15, time.time() - t0
-        assert "closed the connection" in str(e) or "failed" in str(e) or "timed out" in str(e), str(e)
+        # the dead rank itself, or a peer that noticed first and has already left in turn
+        assert any(w in str(e) for w in ("closed the connection", "failed", "timed out", "has exited")), str(e)
     print(f"rank {me}: detected the dead rank")
 elif mode == "mismatch":
     x = np.zeros(100 if me == 0 else 50, dtype=np.float32)

@@ -31,6 +31,17 @@ void launch_collective(const CollParams& P, DType in, DType wire, DType out, int
 /** True when (in, wire, out, op) has a compiled kernel. */
 bool collective_supported(DType in, DType wire, DType out, ReductionOperator op);
 
+// ---- bulk-copy pipeline (kernels/bulk_pipeline.cu) ------------------------------
+/**
+ * Large uniform allgather / alltoall (dt = u8, counts in bytes) and sum
+ * reduce_scatter (f32 / f16 / bf16) with the copy engine (cp.async.bulk) moving
+ * the data; protocol-compatible with the pipelined schedule of the generic
+ * kernel.  Requirements checked by the caller: P.pipelined, every send / recv
+ * pointer 16-byte aligned, the per-rank slice a multiple of 16 bytes.
+ */
+bool bulk_pipeline_supported(DevColl kind, DType dt, ReductionOperator op);
+void launch_bulk_pipeline(const CollParams& P, DType dt, int ctas, int threads, int local_ranks, cudaStream_t stream);
+
 // ---- NVLS allreduce (kernels/nvls.cu) ------------------------------------------
 struct NvlsParams {
   Workspace ws;

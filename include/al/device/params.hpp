@@ -66,7 +66,7 @@ struct DeviceStatus {
   uint32_t code;    ///< StatusCode
   uint32_t rank;    ///< rank that gave up
   uint32_t peer;    ///< rank it was waiting for
-  uint32_t where;   ///< 0: A flags, 1: B flags, 2: C flags, 3: p2p credit, 4: p2p data, 5: rma
+  uint32_t where;   ///< 0: A flags, 1: B flags, 2: C flags, 3: p2p credit, 4: p2p data, 5: rma, 6: a bulk copy that did not complete
   uint64_t epoch;   ///< epoch it was waiting for
   uint64_t seen;    ///< value it last saw
 };
@@ -121,6 +121,7 @@ struct CollParams {
   int two_phase;                 ///< allreduce: 1 = reduce-scatter + allgather, 0 = every rank reduces everything
   int pipelined;                 ///< 1: half of the CTAs publish while the other half consumes (large uniform ops)
   size_t slot_elems;             ///< elements moved per slot and chunk (0 = the slot's capacity)
+  int n_pub;                     ///< bulk-copy pipeline: number of publishing CTAs (0 = half of the grid)
 };
 
 /** Arguments of one point-to-point launch (any mix of sends and receives). */

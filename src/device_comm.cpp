@@ -181,10 +181,10 @@ void DeviceCommunicator::check_status() const {
   if (code == kStatusOk) return;
   DeviceStatus s = status();
   static const char* where[] = {"data-ready flags", "reduced-slice flags", "closing barrier", "send credit",
-                                "incoming data", "RMA / halo signal"};
+                                "incoming data", "RMA / halo signal", "bulk copy completion"};
   impl_->stats.timeouts++;
   throw_al_exception("device communicator failed: rank ", s.rank, " timed out waiting for rank ", s.peer, " (",
-                     where[s.where < 6 ? s.where : 0], ", epoch ", s.epoch, ", last seen ", s.seen,
+                     where[s.where < 7 ? s.where : 0], ", epoch ", s.epoch, ", last seen ", s.seen,
                      "); the communicator is unusable, create a new one");
 }
 
@@ -384,6 +384,27 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   if (d.kind == DevColl::allreduce) {
     if (algo == AllreduceAlgo::one_shot) I.stats.ar_one_shot++;
     else I.stats.ar_two_shot++;
+  }
+  // Opt-in: the pipelined schedule with the copy engine moving the data.  A rank whose buffers do
+  // not qualify runs the generic kernel; the two speak the same protocol.
+  if (P.pipelined && tn.bulk_pipeline && in == wire && wire == out && bulk_pipeline_supported(d.kind, wire, d.op) &&
+      (P.count * esz) % 16 == 0 && (P.slot_elems * esz) % 16 == 0) {
+    bool aligned = true;
+    for (const RankArgs& a : ranks)
+      aligned = aligned && a.send && a.recv && (uintptr_t)a.send % 16 == 0 && (uintptr_t)a.recv % 16 == 0;
+    if (aligned) {
+      int n_pub = tn.bulk_pub_ctas;
+      int n_con = d.kind == DevColl::reduce_scatter ? std::max(1, cap / 2) : tn.bulk_con_ctas;
+      if (I.nlocal > 1) {  // cooperative launch: one CTA per SM with this kernel's shared memory
+        const int per_rank = std::max(2, I.sm_count / I.nlocal);
+        n_pub = std::max(1, std::min(n_pub, per_rank / 2));
+        n_con = std::max(1, std::min(n_con, per_rank - n_pub));
+      }
+      P.n_pub = n_pub;
+      I.stats.bulk_pipeline++;
+      launch_bulk_pipeline(P, wire, n_pub + n_con, threads, I.nlocal, stream);
+      return;
+    }
   }
   launch_collective(P, in, wire, out, ctas, threads, I.nlocal, stream);
 }

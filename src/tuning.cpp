@@ -1,6 +1,7 @@
 // Run-time tuning table (see al/tuning.hpp).
 #include "al/tuning.hpp"
 
+#include <algorithm>
 #include <sstream>
 
 #include "al/util/utils.hpp"
@@ -40,6 +41,9 @@ void Tuning::load_from_env() {
   max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
   max_ctas_zero_copy = (int)env_long("AL_MAX_CTAS_ZERO_COPY", max_ctas_zero_copy);
   threads_per_cta = (int)env_long("AL_THREADS_PER_CTA", threads_per_cta);
+  bulk_pipeline = env_long("AL_DEV_BULK_PIPELINE", bulk_pipeline) != 0;
+  bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
+  bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
   trace = env_long("AL_TRACE", trace) != 0;
   debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
   signal_handler = env_long("AL_DISABLE_SIGNAL_HANDLER", 0) == 0;
@@ -54,6 +58,8 @@ void Tuning::load_from_env() {
   if (max_ctas_nvls > AL_MAX_CTAS) max_ctas_nvls = AL_MAX_CTAS;
   if (max_ctas_zero_copy < 1) max_ctas_zero_copy = 1;
   if (max_ctas_zero_copy > AL_MAX_CTAS) max_ctas_zero_copy = AL_MAX_CTAS;
+  bulk_pub_ctas = std::max(1, std::min(bulk_pub_ctas, AL_MAX_CTAS / 2));
+  bulk_con_ctas = std::max(1, std::min(bulk_con_ctas, AL_MAX_CTAS / 2));
   if (threads_per_cta < 64) threads_per_cta = 64;
   if (threads_per_cta > 1024) threads_per_cta = 1024;
   threads_per_cta = threads_per_cta / 32 * 32;
@@ -95,6 +101,9 @@ std::string Tuning::describe() const {
      << "max_ctas_nvls = " << max_ctas_nvls << "\n"
      << "max_ctas_zero_copy = " << max_ctas_zero_copy << "\n"
      << "threads_per_cta = " << threads_per_cta << "\n"
+     << "bulk_pipeline = " << bulk_pipeline << "\n"
+     << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
+     << "bulk_con_ctas = " << bulk_con_ctas << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
      << "signal_handler = " << signal_handler << "\n"

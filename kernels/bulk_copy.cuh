@@ -3,7 +3,7 @@
 // tiles: global -> shared (completion on an mbarrier), shared -> global
 // (completion through bulk groups).  The source is always this GPU's own
 // memory; the destinations may be peer-mapped memory of other GPUs, which the
-// engine reaches with plain (non-multicast) stores over NVLink.
+// engine reaches with ordinary one-destination stores over NVLink.
 //
 // Every wait in here is bounded.  A wait on an mbarrier that runs out returns
 // false to the caller after the copies already in flight have drained, so the

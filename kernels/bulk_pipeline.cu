@@ -14,7 +14,7 @@
 // The SMs only issue descriptors, so a handful of CTAs saturates the links and
 // the rest of the GPU stays free for the application's kernels.
 //
-// No load in this file reads another GPU's memory and none is a multicast load.
+// Every load in this file reads this GPU's own memory and has exactly one destination CTA.
 #include "al/cuda/cuda.hpp"
 #include "al/device/kernels.hpp"
 #include "bulk_copy.cuh"

@@ -67,6 +67,7 @@ struct CommStats {
   uint64_t ops = 0, bytes = 0, kernels = 0, timeouts = 0;
   uint64_t ar_one_shot = 0, ar_two_shot = 0, ar_nvls = 0, ar_nvls_zero_copy = 0;
   uint64_t bulk_pipeline = 0;   ///< operations run by the bulk-copy pipeline kernel
+  uint64_t direct = 0;          ///< allgather / alltoall stored straight into symmetric receive buffers
 };
 
 }  // namespace device

@@ -42,6 +42,16 @@ bool collective_supported(DType in, DType wire, DType out, ReductionOperator op)
 bool bulk_pipeline_supported(DevColl kind, DType dt, ReductionOperator op);
 void launch_bulk_pipeline(const CollParams& P, DType dt, int ctas, int threads, int local_ranks, cudaStream_t stream);
 
+// ---- direct allgather / alltoall (kernels/direct.cu) ----------------------------------
+/**
+ * Uniform allgather / alltoall (counts in bytes) whose receive buffers are symmetric
+ * memory: P.recv[r] must hold, for EVERY rank r of the communicator, the address in this
+ * process of rank r's receive buffer (16-byte aligned); nothing is staged.
+ * bulk_engine additionally needs 16-byte aligned send pointers and slices that are a
+ * multiple of 16 bytes.
+ */
+void launch_direct(const CollParams& P, bool bulk_engine, int ctas, int threads, int local_ranks, cudaStream_t stream);
+
 // ---- NVLS allreduce (kernels/nvls.cu) ------------------------------------------
 struct NvlsParams {
   Workspace ws;

@@ -51,6 +51,8 @@ struct Tuning {
   bool bulk_pipeline = false;                  ///< AL_DEV_BULK_PIPELINE: pipelined reduce_scatter / allgather / alltoall move their data with the bulk copy engine (cp.async.bulk) when every buffer is 16-byte aligned
   int bulk_pub_ctas = 16;                      ///< AL_DEV_BULK_PUB_CTAS: publishing CTAs of that kernel (one issuing thread each)
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
+  bool direct_symmetric = false;               ///< AL_DEV_DIRECT: uniform allgather / alltoall whose receive buffer comes from symm_alloc() (same block and offset on every rank) are stored straight into the peers' buffers, without staging
+  bool direct_bulk = false;                    ///< AL_DEV_DIRECT_BULK: ... with the bulk copy engine instead of SM store loops
   // ---- diagnostics ------------------------------------------------------------
   bool trace = false;                          ///< AL_TRACE: record every API call
   bool debug_checks = false;                   ///< AL_DEBUG: argument checks on every call

@@ -90,7 +90,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
   X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas)
+  X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(direct_symmetric) X(direct_bulk)
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {
@@ -242,7 +242,7 @@ int al_dev_comm_stats(void* comm, uint64_t* out) {
     device::CommStats s = ((DeviceCommunicator*)comm)->stats();
     out[0] = s.ops; out[1] = s.bytes; out[2] = s.kernels; out[3] = s.timeouts;
     out[4] = s.ar_one_shot; out[5] = s.ar_two_shot; out[6] = s.ar_nvls; out[7] = s.ar_nvls_zero_copy;
-    out[8] = s.bulk_pipeline;
+    out[8] = s.bulk_pipeline; out[9] = s.direct;
   });
 }
 int al_dev_comm_status(void* comm, uint64_t* out) {

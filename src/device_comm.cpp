@@ -272,11 +272,36 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   }
 
 
+  // Opt-in: a uniform allgather / alltoall whose receive buffers are symmetric memory (the same
+  // offset of the same symm_alloc() block on every rank - as for the zero-copy NVLS allreduce, every
+  // rank must pass the corresponding buffer) stores straight into the peers' buffers.
+  const SymmBlock* direct_block = nullptr;
+  size_t direct_off = 0;
+  if (tn.direct_symmetric && (d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector && p > 1 &&
+      in == DType::u8 && P.count > 0 && P.count % 16 == 0) {
+    const size_t total = P.count * (size_t)p;
+    const int me0 = I.emulated ? 0 : I.rank0;
+    const SymmBlock* b = find_symm(ranks[0].recv, total, &direct_off);
+    bool ok = b != nullptr && direct_off % 16 == 0;
+    for (int lr = 0; ok && lr < I.nlocal; ++lr) {
+      const RankArgs& a = ranks[(size_t)lr];
+      const char* rb = (const char*)b->peer(me0 + lr) + direct_off;
+      const char* sb = (const char*)a.send;
+      ok = a.recv == (const void*)rb && sb != nullptr;
+      if (!ok) break;
+      const size_t sbytes = d.kind == DevColl::allgather ? P.count : total;
+      const bool overlaps = sb < rb + total && rb < sb + sbytes;
+      const bool in_place_ag = d.kind == DevColl::allgather && sb == rb + (size_t)(me0 + lr) * P.count;
+      if (overlaps && !in_place_ag) ok = false;  // an in-place alltoall needs the staged path
+    }
+    if (ok) direct_block = b;
+  }
+
   // Large uniform reduce_scatter / allgather / alltoall run pipelined: smaller chunks, half of the
   // grid publishing while the other half consumes.
   size_t slot_e = cap_e;
   if ((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
-      p > 1 && P.count * esz >= tn.pipeline_min_bytes) {
+      p > 1 && !direct_block && P.count * esz >= tn.pipeline_min_bytes) {
     size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {
@@ -384,6 +409,18 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   if (d.kind == DevColl::allreduce) {
     if (algo == AllreduceAlgo::one_shot) I.stats.ar_one_shot++;
     else I.stats.ar_two_shot++;
+  }
+  if (direct_block) {
+    bool bulk = tn.direct_bulk;
+    for (const RankArgs& a : ranks) bulk = bulk && (uintptr_t)a.send % 16 == 0;
+    for (int r = 0; r < p; ++r) {
+      P.recv[r] = (char*)direct_block->peer(r) + direct_off;
+      P.local_chunks[r] = 1;
+    }
+    const int dctas = bulk ? std::max(1, std::min(cap, 2 * tn.bulk_pub_ctas)) : ctas;
+    I.stats.direct++;
+    launch_direct(P, bulk, dctas, threads, I.nlocal, stream);
+    return;
   }
   // Opt-in: the pipelined schedule with the copy engine moving the data.  A rank whose buffers do
   // not qualify runs the generic kernel; the two speak the same protocol.

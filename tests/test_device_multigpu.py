@@ -32,7 +32,7 @@ def test_rma_ring_exchange_and_bandwidth(bin_dir):
     n = min(_ngpu(), 4)
     if n < 2:
         pytest.skip("needs >= 2 GPUs")
-    for cmd in (["test_rma", "--max-size", "65536"], ["test_exchange", "--backend", "device", "--peers", "1"],
+    for cmd in (["test_rma", "--max-size", "65536"], ["test_rma", "--mode", "halo", "--max-size", "65536"], ["test_exchange", "--backend", "device", "--peers", "1"],
                 ["bandwidth", "--bytes", "8388608", "--iters", "3"], ["pingpong", "device"]):
         r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n if cmd[0] != "pingpong" else 2), "--timeout", "120",
                             str(bin_dir / cmd[0])] + cmd[1:], capture_output=True, text=True, timeout=180)

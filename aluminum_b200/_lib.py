@@ -50,6 +50,7 @@ def _declare(lib) -> None:
         "al_trace_enable": (None, [i]), "al_trace_snapshot": (i, [C.c_char_p, sz]), "al_trace_clear": (None, []),
         "al_host_comm_create": (vp, []), "al_host_comm_split": (vp, [vp, i, i]), "al_host_comm_destroy": (None, [vp]),
         "al_host_comm_rank": (i, [vp]), "al_host_comm_size": (i, [vp]),
+        "al_host_comm_local_rank": (i, [vp]), "al_host_comm_local_size": (i, [vp]), "al_host_comm_local": (vp, [vp]),
         "al_host_comm_stats": (i, [vp, u64p]), "al_host_comm_abort": (i, [vp, C.c_char_p]),
         "al_dev_comm_abort": (i, [vp, C.c_char_p]),
         "al_host_collective": (i, [vp, i, vp, vp, sz, i, i, i, i, i, szp, szp, szp, szp, vpp]),

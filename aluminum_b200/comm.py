@@ -143,7 +143,7 @@ class Request:
 
 # ---------------------------------------------------------------------------------------
 class HostComm:
-    """CPU communicator (shared-memory ranks of one host)."""
+    """CPU communicator: shared memory inside a node, sockets between nodes."""
 
     def __init__(self, _handle=None):
         init()
@@ -152,6 +152,12 @@ class HostComm:
         self._h = C.c_void_p(_handle if _handle else check_ptr(lib.al_host_comm_create()))
         self.rank = lib.al_host_comm_rank(self._h)
         self.size = lib.al_host_comm_size(self._h)
+        self.local_rank = lib.al_host_comm_local_rank(self._h)   # among the members on this rank's node
+        self.local_size = lib.al_host_comm_local_size(self._h)
+
+    def local(self) -> "HostComm":
+        """Collective: the communicator of the members that run on this rank's node."""
+        return HostComm(check_ptr(self._lib.al_host_comm_local(self._h)))
 
     def split(self, color: int, key: int) -> "HostComm":
         return HostComm(check_ptr(self._lib.al_host_comm_split(self._h, color, key)))

@@ -48,6 +48,11 @@ void* al_host_comm_split(void* comm, int color, int key);
 void al_host_comm_destroy(void* comm);
 int al_host_comm_rank(void* comm);
 int al_host_comm_size(void* comm);
+/** Rank among / number of the communicator's members on this rank's node. */
+int al_host_comm_local_rank(void* comm);
+int al_host_comm_local_size(void* comm);
+/** Collective: communicator of the members on this rank's node (NULL + al_last_error() on failure). */
+void* al_host_comm_local(void* comm);
 /** Fills out[0..3]: collectives, p2p_ops, bytes, failures. */
 int al_host_comm_stats(void* comm, uint64_t* out);
 /** Puts the communicator into the failed state on this rank (why may be NULL). */

@@ -98,8 +98,11 @@ class HostCommunicator {
 
   int rank() const { return group_.rank(); }
   int size() const { return group_.size(); }
-  int local_rank() const { return group_.rank(); }
-  int local_size() const { return group_.size(); }
+  /** Rank among, and number of, the members that run on this rank's node (the reference's node-local communicator, mpi_comm_and_stream_wrapper.hpp:46-129). */
+  int local_rank() const;
+  int local_size() const;
+  /** Collective: the communicator of the members on this rank's node, ordered as here (role of get_local_comm()). */
+  HostCommunicator local() const;
   int get_stream() const { return 0; }
   const internal::Group& group() const { return group_; }
 

@@ -140,6 +140,13 @@ void* al_host_comm_split(void* comm, int color, int key) {
 void al_host_comm_destroy(void* comm) { delete (HostCommunicator*)comm; }
 int al_host_comm_rank(void* comm) { return ((HostCommunicator*)comm)->rank(); }
 int al_host_comm_size(void* comm) { return ((HostCommunicator*)comm)->size(); }
+int al_host_comm_local_rank(void* comm) { return ((HostCommunicator*)comm)->local_rank(); }
+int al_host_comm_local_size(void* comm) { return ((HostCommunicator*)comm)->local_size(); }
+void* al_host_comm_local(void* comm) {
+  void* r = nullptr;
+  guard([&] { r = new HostCommunicator(((HostCommunicator*)comm)->local()); });
+  return r;
+}
 int al_host_comm_stats(void* comm, uint64_t* out) {
   return guard([&] {
     host::CommStats s = ((HostCommunicator*)comm)->stats();

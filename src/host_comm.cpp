@@ -171,6 +171,34 @@ HostCommunicator::Impl::Impl(const Group& g)
   }
 }
 
+namespace {
+/** (index of my node among the nodes of the group, my rank inside it, its population). */
+void node_position(const Group& g, int* node, int* lrank, int* lsize) {
+  *node = 0; *lrank = g.rank(); *lsize = g.size();
+  World* w = g.world();
+  if (!w || g.size() <= 1) return;
+  const std::string& mine = w->node_of(g.world_rank_of(g.rank()));
+  std::vector<std::string> seen;
+  int before = 0, total = 0;
+  for (int r = 0; r < g.size(); ++r) {
+    const std::string& nm = w->node_of(g.world_rank_of(r));
+    if (std::find(seen.begin(), seen.end(), nm) == seen.end()) seen.push_back(nm);
+    if (nm == mine) { ++total; if (r < g.rank()) ++before; }
+  }
+  *node = (int)(std::find(seen.begin(), seen.end(), mine) - seen.begin());
+  *lrank = before;
+  *lsize = total;
+}
+}  // namespace
+
+int HostCommunicator::local_rank() const { int n, r, s; node_position(group_, &n, &r, &s); return r; }
+int HostCommunicator::local_size() const { int n, r, s; node_position(group_, &n, &r, &s); return s; }
+HostCommunicator HostCommunicator::local() const {
+  int n, r, s;
+  node_position(group_, &n, &r, &s);
+  return HostCommunicator(group_.split(n, group_.rank()));
+}
+
 HostCommunicator::Impl::~Impl() {
   // Operations of this communicator were queued under its address; the slot can serve another one now.
   if (ProgressEngine* pe = get_progress_engine_if_any()) pe->release_key(this);

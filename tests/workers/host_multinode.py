@@ -26,6 +26,18 @@ if mode == "hier":
     assert al.local_size() == p // 2 and al.local_rank() == me % (p // 2)
     node = world.split(al.node_index(), me)                 # shared memory inside
     leaders = world.split(0 if al.local_rank() == 0 else 1, me)  # sockets across (colour 1: the rest)
+    # the communicator's own view of the node structure
+    assert world.local_size == p // 2 and world.local_rank == me % (p // 2), (world.local_rank, world.local_size)
+    assert node.local_size == node.size and node.local_rank == node.rank
+    mine = world.local()
+    assert mine.size == p // 2 and mine.rank == world.local_rank
+    z = np.full(3, float(me), dtype=np.float32)
+    mine.allreduce(z)
+    first = (me // (p // 2)) * (p // 2)
+    assert z[0] == sum(range(first, first + p // 2)), z
+    odd = world.split(me % 2, me)   # a subset that still spans both nodes
+    assert odd.local_size == sum(1 for r in range(first, first + p // 2) if r % 2 == me % 2)
+    mine.close(); odd.close()
     assert node.size == p // 2
     rng = np.random.default_rng(me)
     for n in (1, 7, 1000, 300001):

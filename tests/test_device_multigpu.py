@@ -32,11 +32,22 @@ def test_rma_ring_exchange_and_bandwidth(bin_dir):
     n = min(_ngpu(), 4)
     if n < 2:
         pytest.skip("needs >= 2 GPUs")
-    for cmd in (["test_rma", "--max-size", "65536"], ["test_rma", "--mode", "halo", "--max-size", "65536"], ["test_exchange", "--backend", "device", "--peers", "1"],
+    for cmd in (["test_rma", "--max-size", "65536"], ["test_exchange", "--backend", "device", "--peers", "1"],
                 ["bandwidth", "--bytes", "8388608", "--iters", "3"], ["pingpong", "device"]):
         r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n if cmd[0] != "pingpong" else 2), "--timeout", "120",
                             str(bin_dir / cmd[0])] + cmd[1:], capture_output=True, text=True, timeout=180)
         assert r.returncode == 0, " ".join(cmd) + r.stdout + r.stderr
+
+
+@pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
+                    reason="written after the last GPU run; set AL_TEST_UNVERIFIED=1 to run it")
+def test_rma_halo_exchange_on_a_2d_grid(bin_dir):
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "120", str(bin_dir / "test_rma"),
+                        "--mode", "halo", "--max-size", "65536"], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and "rma halo" in r.stdout and "FAIL" not in r.stdout, r.stdout + r.stderr
 
 
 def test_data_parallel_matches_single_process(bin_dir):

@@ -3,7 +3,7 @@
 allgather / alltoall into symmetric receive buffers (kernels/direct.cu; ``direct_symmetric`` /
 ``AL_DEV_DIRECT=1``, with ``direct_bulk`` / ``AL_DEV_DIRECT_BULK=1`` for its copy-engine flavour).
 
-They are off by default and so is this file: it runs only with ``AL_TEST_OPTIN_KERNELS=1`` in the
+They are off by default and so is this file: it runs only with ``AL_TEST_UNVERIFIED=1`` in the
 environment.  Results are compared with plain PyTorch references, exactly as for the generic kernel
 in test_device_emulated.py.
 """
@@ -14,8 +14,8 @@ import torch
 
 pytestmark = [
     pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("AL_TEST_OPTIN_KERNELS") != "1",
-                       reason="opt-in kernel: set AL_TEST_OPTIN_KERNELS=1 to test them"),
+    pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
+                       reason="opt-in kernel: set AL_TEST_UNVERIFIED=1 to test them"),
 ]
 
 

@@ -29,6 +29,8 @@ void detach(void* remote_buf, int peer, DeviceCommunicator& comm);
 void notify(int peer, DeviceCommunicator& comm);
 void wait(int peer, DeviceCommunicator& comm);
 void put(const void* src, int dest, void* dest_remote, size_t bytes, DeviceCommunicator& comm);
+/** Drop the bookkeeping (signal counters, imported mappings) kept for a communicator that is going away. */
+void forget(const void* comm_impl) noexcept;
 }  // namespace rma
 }  // namespace internal
 

@@ -7,6 +7,7 @@
 #include <mutex>
 
 #include "al/device/kernels.hpp"
+#include "al/rma.hpp"
 #include "al/runtime.hpp"
 #include "al/trace.hpp"
 #include "al/tuning.hpp"
@@ -67,6 +68,7 @@ struct DeviceCommunicator::Impl {
   }
 
   ~Impl() {
+    internal::rma::forget(this);
     if (chain_event) AL_WARN_CUDA(cudaEventDestroy(chain_event));
     if (status_host) AL_WARN_CUDA(cudaFreeHost(status_host));
   }

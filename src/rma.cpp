@@ -28,8 +28,9 @@ struct State {
   std::map<void*, std::pair<int, std::string>> by_ptr;    // returned pointer -> key
 };
 
-std::mutex g_mu;
-std::map<const void*, State> g_states;
+// Never destroyed: communicators may outlive the static objects of this file at process exit.
+std::mutex& g_mu = *new std::mutex;
+std::map<const void*, State>& g_states = *new std::map<const void*, State>;
 
 State& state_of(DeviceCommunicator& comm) {
   State& s = g_states[comm.impl()];
@@ -107,6 +108,19 @@ void detach(void* remote_buf, int peer, DeviceCommunicator& comm) {
     AL_CHECK_CUDA(cudaStreamSynchronize(comm.get_stream()));
     AL_WARN_CUDA(cudaIpcCloseMemHandle(oit->second.base));
     st.opened.erase(oit);
+  }
+}
+
+void forget(const void* comm_impl) noexcept {
+  // A later communicator may be allocated at the same address: it must start from zeroed counters,
+  // like its flag area.
+  try {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_states.find(comm_impl);
+    if (it == g_states.end()) return;
+    for (auto& o : it->second.opened) AL_WARN_CUDA(cudaIpcCloseMemHandle(o.second.base));
+    g_states.erase(it);
+  } catch (...) {
   }
 }
 

@@ -57,6 +57,8 @@ def _declare(lib) -> None:
         "al_host_p2p": (i, [vp, i, ip, ip, vpp, szp, vpp]),
         "al_host_test": (i, [vpp, ip]), "al_host_wait": (i, [vpp]),
         "al_dev_comm_create": (vp, [vp]), "al_dev_comm_create_emulated": (vp, [i, vp]),
+        "al_dev_comm_create_group": (vp, [C.POINTER(C.c_int), i, vp]),
+        "al_host_comm_create_group": (vp, [C.POINTER(C.c_int), i]),
         "al_dev_comm_split": (vp, [vp, i, i, vp]), "al_dev_comm_destroy": (None, [vp]),
         "al_dev_comm_rank": (i, [vp]), "al_dev_comm_size": (i, [vp]), "al_dev_comm_nlocal": (i, [vp]),
         "al_dev_comm_has_multicast": (i, [vp]), "al_dev_comm_backing": (C.c_char_p, [vp]),

@@ -155,6 +155,14 @@ class HostComm:
         self.local_rank = lib.al_host_comm_local_rank(self._h)   # among the members on this rank's node
         self.local_size = lib.al_host_comm_local_size(self._h)
 
+    @classmethod
+    def from_ranks(cls, world_ranks: Sequence[int]) -> "HostComm":
+        """Communicator over the listed world ranks, in that order.  Collective over those ranks only:
+        every one of them passes the same list, nobody else takes part."""
+        init()
+        arr = (C.c_int * len(world_ranks))(*[int(r) for r in world_ranks])
+        return cls(check_ptr(_lib.load().al_host_comm_create_group(arr, len(world_ranks))))
+
     def local(self) -> "HostComm":
         """Collective: the communicator of the members that run on this rank's node."""
         return HostComm(check_ptr(self._lib.al_host_comm_local(self._h)))

@@ -57,6 +57,15 @@ class DeviceComm:
         self.emulated = self.nlocal > 1 or bool(emulate)
         self._symm = {}
 
+    @classmethod
+    def from_ranks(cls, world_ranks, stream=None) -> "DeviceComm":
+        """Communicator over the listed world ranks, in that order.  Collective over those ranks only."""
+        init()
+        lib = _lib.load()
+        arr = (C.c_int * len(world_ranks))(*[int(r) for r in world_ranks])
+        s = C.c_void_p(stream.cuda_stream if stream is not None else 0)
+        return cls(stream=stream, _handle=check_ptr(lib.al_dev_comm_create_group(arr, len(world_ranks), s)))
+
     # ---- properties / diagnostics -----------------------------------------------------
     @property
     def has_multicast(self) -> bool:

@@ -44,6 +44,11 @@ void al_trace_clear(void);
 
 /* ---- host backend ---- */
 void* al_host_comm_create(void);
+/**
+ * Communicator over the listed world ranks, in that order.  Collective over those ranks only
+ * (every one of them passes the same list); the calling rank must be in it.
+ */
+void* al_host_comm_create_group(const int* world_ranks, int n);
 void* al_host_comm_split(void* comm, int color, int key);
 void al_host_comm_destroy(void* comm);
 int al_host_comm_rank(void* comm);
@@ -75,6 +80,8 @@ int al_host_wait(void** req);
 /* ---- device backend ---- */
 void* al_dev_comm_create(void* stream);
 void* al_dev_comm_create_emulated(int p, void* stream);
+/** As al_host_comm_create_group, for a device communicator on `stream`. */
+void* al_dev_comm_create_group(const int* world_ranks, int n, void* stream);
 void* al_dev_comm_split(void* comm, int color, int key, void* stream);
 void al_dev_comm_destroy(void* comm);
 int al_dev_comm_rank(void* comm);

@@ -132,6 +132,14 @@ void* al_host_comm_create(void) {
   guard([&] { r = new HostCommunicator(); });
   return r;
 }
+void* al_host_comm_create_group(const int* world_ranks, int n) {
+  void* r = nullptr;
+  guard([&] {
+    if (!world_ranks || n < 1) throw_al_exception("a group needs at least one world rank");
+    r = new HostCommunicator(Group(get_world(), std::vector<int>(world_ranks, world_ranks + n)));
+  });
+  return r;
+}
 void* al_host_comm_split(void* comm, int color, int key) {
   void* r = nullptr;
   guard([&] { r = new HostCommunicator(((HostCommunicator*)comm)->split(color, key)); });
@@ -217,6 +225,14 @@ int al_host_wait(void** req) {
 void* al_dev_comm_create(void* stream) {
   void* r = nullptr;
   guard([&] { r = new DeviceCommunicator((cudaStream_t)stream); });
+  return r;
+}
+void* al_dev_comm_create_group(const int* world_ranks, int n, void* stream) {
+  void* r = nullptr;
+  guard([&] {
+    if (!world_ranks || n < 1) throw_al_exception("a group needs at least one world rank");
+    r = new DeviceCommunicator(Group(get_world(), std::vector<int>(world_ranks, world_ranks + n)), (cudaStream_t)stream);
+  });
   return r;
 }
 void* al_dev_comm_create_emulated(int p, void* stream) {

@@ -50,6 +50,20 @@ def test_rma_halo_exchange_on_a_2d_grid(bin_dir):
     assert r.returncode == 0 and "rma halo" in r.stdout and "FAIL" not in r.stdout, r.stdout + r.stderr
 
 
+@pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
+                    reason="written after the last GPU run; set AL_TEST_UNVERIFIED=1 to run it")
+def test_torch_distributed_backend_on_gpus(bin_dir):
+    import sys
+    from pathlib import Path
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    worker = Path(__file__).resolve().parent / "workers" / "torch_backend_worker.py"
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "240", sys.executable, str(worker), "cuda"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("torch backend ok") == n, r.stdout + r.stderr
+
+
 def test_data_parallel_matches_single_process(bin_dir):
     import sys
     from pathlib import Path

@@ -213,3 +213,12 @@ def test_progress_engine_stress_on_cpu_ranks(bin_dir, launch):
     """64 non-blocking allreduces of 4-256 KB on 8 communicators started before the first Wait."""
     r = run([bin_dir / "alrun", *launch, "--timeout", "200", bin_dir / "stress_progress", "--backend", "host", "--rounds", "5"])
     assert r.returncode == 0 and "ops_per_s=" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("launch", [["-n", "2"], ["-n", "3"], ["-n", "4", "--nodes", "2"]])
+def test_torch_distributed_backend_on_cpu_ranks(bin_dir, launch):
+    """torch.distributed collectives, a sub-group and DistributedDataParallel on the "aluminum" backend."""
+    n = int(launch[1])
+    r = run([bin_dir / "alrun"] + launch + ["--timeout", "120", sys.executable, W / "torch_backend_worker.py"], timeout=240)
+    assert r.returncode == 0 and r.stdout.count("torch backend ok") == n, r.stdout + r.stderr
+

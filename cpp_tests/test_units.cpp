@@ -19,6 +19,9 @@
 #include "al/util/mpsc_queue.hpp"
 #include "al/util/resource_pool.hpp"
 #include "al/util/spsc_queue.hpp"
+#include "../kernels/bulk_tiles.cuh"
+#include <cstring>
+#include <random>
 
 using namespace Al;
 using namespace Al::internal;
@@ -300,6 +303,130 @@ static void test_lifecycle_and_trace() {
   CHECK(threw);
 }
 
+// The tile plans of the bulk-copy kernels, executed on host memory: every byte must arrive exactly
+// once at the place the collective defines, every transfer must satisfy the copy engine's 16-byte
+// rules and stay inside its staging slot.
+static void test_bulk_tile_plans() {
+  using namespace Al::internal::device::plan;
+  using Bytes = std::vector<unsigned char>;
+  std::minstd_rand rng(7);
+  const size_t tile = 64;  // the plans are parametric in the tile size; a small one gives many tiles
+  auto fill = [&](Bytes& b, int r) { for (size_t i = 0; i < b.size(); ++i) b[i] = (unsigned char)((i * 131 + (size_t)r * 29 + (i >> 8)) & 0xff); };
+  auto ok16 = [&](const Move& m) { return m.bytes > 0 && m.bytes % 16 == 0 && m.src % 16 == 0 && m.dst % 16 == 0 && m.bytes <= tile; };
+  for (int p : {2, 3, 4, 8}) {
+    for (int trial = 0; trial < 8; ++trial) {
+      const size_t slice = 16 * (1 + rng() % 300);
+      const size_t cap = 256 * (1 + rng() % 4);
+      const size_t slot = 16 * (1 + rng() % (cap / 16));
+      const unsigned n_pub = 1 + rng() % 5, n_con = 1 + rng() % 5;
+      const uint64_t G = (slice + slot - 1) / slot;
+      // ---- staged allgather: send = one slice, receive = p slices ----------------------------------
+      {
+        std::vector<Bytes> send((size_t)p, Bytes(slice)), recv((size_t)p, Bytes(slice * (size_t)p, 0));
+        std::vector<std::vector<int>> hits((size_t)p, std::vector<int>(slice * (size_t)p, 0));
+        std::vector<Bytes> stage((size_t)p, Bytes(2 * cap * (size_t)p, 0xEE));
+        for (int r = 0; r < p; ++r) fill(send[(size_t)r], r);
+        for (uint64_t c = 0; c < G; ++c) {
+          const size_t half = (c & 1) * cap * (size_t)p;
+          for (int r = 0; r < p; ++r)
+            for (unsigned part = 0; part < n_pub; ++part) {
+              const Share sh = share_of(slice, slot, c, part, n_pub, tile);
+              for (size_t k = 0; k < sh.tiles; ++k) {
+                const Move m = ag_publish(sh, k, r, cap, tile);
+                CHECK(ok16(m) && m.peer == -1 && m.src + m.bytes <= slice);
+                CHECK(m.dst >= (size_t)r * cap && m.dst + m.bytes <= (size_t)(r + 1) * cap);
+                for (int d = 0; d < p; ++d) memcpy(&stage[(size_t)d][half + m.dst], &send[(size_t)r][m.src], m.bytes);
+              }
+            }
+          for (int r = 0; r < p; ++r)
+            for (unsigned part = 0; part < n_con; ++part) {
+              const Share sh = share_of(slice, slot, c, part, n_con, tile);
+              for (size_t t = 0; t < fan_tiles(sh, p); ++t) {
+                const Move m = gather_consume(sh, t, p, slice, cap, tile);
+                CHECK(ok16(m) && m.dst + m.bytes <= slice * (size_t)p);
+                memcpy(&recv[(size_t)r][m.dst], &stage[(size_t)r][half + m.src], m.bytes);
+                for (size_t i = 0; i < m.bytes; ++i) hits[(size_t)r][m.dst + i]++;
+              }
+            }
+        }
+        for (int r = 0; r < p; ++r) {
+          bool same = true, once = true;
+          for (int q = 0; q < p; ++q) same = same && memcmp(&recv[(size_t)r][(size_t)q * slice], send[(size_t)q].data(), slice) == 0;
+          for (int h : hits[(size_t)r]) once = once && h == 1;
+          CHECK(same && once);
+        }
+      }
+      // ---- staged alltoall (and the publish half of reduce_scatter): send = p slices ------------------
+      {
+        std::vector<Bytes> send((size_t)p, Bytes(slice * (size_t)p)), recv((size_t)p, Bytes(slice * (size_t)p, 0));
+        std::vector<Bytes> stage((size_t)p, Bytes(2 * cap * (size_t)p, 0xEE));
+        for (int r = 0; r < p; ++r) fill(send[(size_t)r], r + 40);
+        for (uint64_t c = 0; c < G; ++c) {
+          const size_t half = (c & 1) * cap * (size_t)p;
+          for (int r = 0; r < p; ++r)
+            for (unsigned part = 0; part < n_pub; ++part) {
+              const Share sh = share_of(slice, slot, c, part, n_pub, tile);
+              for (size_t t = 0; t < fan_tiles(sh, p); ++t) {
+                const Move m = scatter_publish(sh, t, r, p, slice, cap, tile);
+                CHECK(ok16(m) && m.peer >= 0 && m.peer < p && m.src + m.bytes <= slice * (size_t)p);
+                CHECK(m.dst >= (size_t)r * cap && m.dst + m.bytes <= (size_t)(r + 1) * cap);
+                memcpy(&stage[(size_t)m.peer][half + m.dst], &send[(size_t)r][m.src], m.bytes);
+              }
+            }
+          // what a reduce_scatter consumer folds: slot [r] of rank d holds chunk c of slice d of rank r
+          const size_t base = c * slot, len = clamp(slice, base, slot);
+          for (int d = 0; d < p; ++d)
+            for (int r = 0; r < p; ++r)
+              CHECK(memcmp(&stage[(size_t)d][half + (size_t)r * cap], &send[(size_t)r][(size_t)d * slice + base], len) == 0);
+          for (int r = 0; r < p; ++r)
+            for (unsigned part = 0; part < n_con; ++part) {
+              const Share sh = share_of(slice, slot, c, part, n_con, tile);
+              for (size_t t = 0; t < fan_tiles(sh, p); ++t) {
+                const Move m = gather_consume(sh, t, p, slice, cap, tile);
+                memcpy(&recv[(size_t)r][m.dst], &stage[(size_t)r][half + m.src], m.bytes);
+              }
+            }
+        }
+        for (int r = 0; r < p; ++r)
+          for (int q = 0; q < p; ++q)
+            CHECK(memcmp(&recv[(size_t)r][(size_t)q * slice], &send[(size_t)q][(size_t)r * slice], slice) == 0);
+      }
+      // ---- direct allgather / alltoall: straight into the receive buffers ----------------------------------
+      {
+        const unsigned nct = 1 + rng() % 7;
+        std::vector<Bytes> s1((size_t)p, Bytes(slice)), sp((size_t)p, Bytes(slice * (size_t)p));
+        std::vector<Bytes> r1((size_t)p, Bytes(slice * (size_t)p, 0)), r2((size_t)p, Bytes(slice * (size_t)p, 0));
+        std::vector<std::vector<int>> hits((size_t)p, std::vector<int>(slice * (size_t)p, 0));
+        for (int r = 0; r < p; ++r) { fill(s1[(size_t)r], r + 80); fill(sp[(size_t)r], r + 120); }
+        for (int r = 0; r < p; ++r)
+          for (unsigned cta = 0; cta < nct; ++cta) {
+            const Share sh = share_of(slice, slice, 0, cta, nct, tile);
+            for (size_t k = 0; k < sh.tiles; ++k) {
+              const Move m = ag_direct(sh, k, r, slice, tile);
+              CHECK(ok16(m) && m.src + m.bytes <= slice && m.dst + m.bytes <= slice * (size_t)p);
+              for (int d = 0; d < p; ++d) memcpy(&r1[(size_t)d][m.dst], &s1[(size_t)r][m.src], m.bytes);
+            }
+            for (size_t t = 0; t < fan_tiles(sh, p); ++t) {
+              const Move m = a2a_direct(sh, t, r, p, slice, tile);
+              CHECK(ok16(m) && m.peer >= 0 && m.peer < p);
+              memcpy(&r2[(size_t)m.peer][m.dst], &sp[(size_t)r][m.src], m.bytes);
+              for (size_t i = 0; i < m.bytes; ++i) hits[(size_t)m.peer][m.dst + i]++;
+            }
+          }
+        for (int r = 0; r < p; ++r) {
+          bool once = true;
+          for (int h : hits[(size_t)r]) once = once && h == 1;
+          CHECK(once);
+          for (int q = 0; q < p; ++q) {
+            CHECK(memcmp(&r1[(size_t)r][(size_t)q * slice], s1[(size_t)q].data(), slice) == 0);
+            CHECK(memcmp(&r2[(size_t)r][(size_t)q * slice], &sp[(size_t)q][(size_t)r * slice], slice) == 0);
+          }
+        }
+      }
+    }
+  }
+}
+
 int main() {
   test_meta();
   test_spsc();
@@ -311,6 +438,7 @@ int main() {
   test_progress_engine_slot_reuse();
   test_reduce_and_halves();
   test_lifecycle_and_trace();
+  test_bulk_tile_plans();
   if (g_fail) { fprintf(stderr, "%d check(s) failed\n", g_fail); return 1; }
   printf("all unit tests passed\n");
   return 0;

@@ -18,6 +18,7 @@
 #include "al/cuda/cuda.hpp"
 #include "al/device/kernels.hpp"
 #include "bulk_copy.cuh"
+#include "bulk_tiles.cuh"
 #include "datamove.cuh"
 
 namespace Al {
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(512) bulk_pipeline_kernel(const __grid_constan
   const char* send = (const char*)P.send[rank];
   char* recv = (char*)P.recv[rank];
   const size_t count = Tb.send_counts[0];               // uniform: elements per rank slice
+  const size_t slice_b = count * sizeof(T), slot_b = slot_e * sizeof(T);
   const uint64_t G = P.local_chunks[rank];
   const unsigned n_pub = P.n_pub > 0 ? (unsigned)P.n_pub : gridDim.x / 2;
   const unsigned n_con = gridDim.x - n_pub;
@@ -75,31 +77,25 @@ __global__ void __launch_bounds__(512) bulk_pipeline_kernel(const __grid_constan
     for (uint64_t c = 0; c < G; ++c) {
       if (c >= 2 && !wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, c - 1), P.timeout_ns)) return;
       const int par = (int)((P.seq + c) & 1);
-      const size_t base = c * slot_e, len = clamp_len(count, base, slot_e);
-      size_t lo, hi;
-      split_range(len, blockIdx.x, n_pub, VEC, lo, hi);
+      const plan::Share sh = plan::share_of(slice_b, slot_b, c, blockIdx.x, n_pub, kBulkTile);
       bool ok = true;
-      if (threadIdx.x == 0 && send && hi > lo) {
-        const size_t seg = (hi - lo) * sizeof(T);
-        const size_t nt = (seg + kBulkTile - 1) / kBulkTile;
-        const size_t dst_off = (size_t)par * half + (size_t)rank * cap_b + lo * sizeof(T);
+      if (threadIdx.x == 0 && send && sh.seg) {
+        const size_t half_off = (size_t)par * half;
         if (kind == DevColl::allgather) {
-          const char* src = send + (base + lo) * sizeof(T);
-          ok = bulk::stream_tiles(ring, nt, [&](size_t t, bulk::Tile& tl) {
-            const size_t off = t * (size_t)kBulkTile;
-            tl.src = src + off;
-            tl.bytes = (uint32_t)(seg - off < (size_t)kBulkTile ? seg - off : (size_t)kBulkTile);
+          ok = bulk::stream_tiles(ring, sh.tiles, [&](size_t t, bulk::Tile& tl) {
+            const plan::Move m = plan::ag_publish(sh, t, rank, cap_b, kBulkTile);
+            tl.src = send + m.src;
+            tl.bytes = m.bytes;
             tl.ndst = p;
-            for (int i = 0; i < p; ++i) tl.dst[i] = ws.stage[(rank + 1 + i) % p] + dst_off + off;
+            for (int i = 0; i < p; ++i) tl.dst[i] = ws.stage[(rank + 1 + i) % p] + half_off + m.dst;
           }, P.timeout_ns);
         } else {  // reduce_scatter / alltoall: slice d goes to rank d; tiles rotate over the destinations
-          ok = bulk::stream_tiles(ring, nt * (size_t)p, [&](size_t t, bulk::Tile& tl) {
-            const int d = (rank + 1 + (int)(t % (size_t)p)) % p;
-            const size_t off = (t / (size_t)p) * (size_t)kBulkTile;
-            tl.src = send + (Tb.send_displs[d] + base + lo) * sizeof(T) + off;
-            tl.bytes = (uint32_t)(seg - off < (size_t)kBulkTile ? seg - off : (size_t)kBulkTile);
+          ok = bulk::stream_tiles(ring, plan::fan_tiles(sh, p), [&](size_t t, bulk::Tile& tl) {
+            const plan::Move m = plan::scatter_publish(sh, t, rank, p, slice_b, cap_b, kBulkTile);
+            tl.src = send + m.src;
+            tl.bytes = m.bytes;
             tl.ndst = 1;
-            tl.dst[0] = ws.stage[d] + dst_off + off;
+            tl.dst[0] = ws.stage[m.peer] + half_off + m.dst;
           }, P.timeout_ns);
         }
         __threadfence_system();
@@ -126,17 +122,17 @@ __global__ void __launch_bounds__(512) bulk_pipeline_kernel(const __grid_constan
           T* out = (T*)recv + base + lo;
           cta_reduce<T, T, Red>(&out, 1, slot, lo * sizeof(T), p, hi - lo, red, P.scale, P.int_div);
         }
-      } else if (threadIdx.x == 0 && recv && hi > lo) {
-        const size_t seg = (hi - lo) * sizeof(T);
-        const size_t nt = (seg + kBulkTile - 1) / kBulkTile;
-        ok = bulk::stream_tiles(ring, nt * (size_t)p, [&](size_t t, bulk::Tile& tl) {
-          const int r = (int)(t % (size_t)p);
-          const size_t off = (t / (size_t)p) * (size_t)kBulkTile;
-          tl.src = mystage + (size_t)r * cap_b + lo * sizeof(T) + off;
-          tl.bytes = (uint32_t)(seg - off < (size_t)kBulkTile ? seg - off : (size_t)kBulkTile);
-          tl.ndst = 1;
-          tl.dst[0] = recv + (Tb.recv_displs[r] + base + lo) * sizeof(T) + off;
-        }, P.timeout_ns);
+      } else {
+        const plan::Share sh = plan::share_of(slice_b, slot_b, c, part, n_con, kBulkTile);
+        if (threadIdx.x == 0 && recv && sh.seg) {
+          ok = bulk::stream_tiles(ring, plan::fan_tiles(sh, p), [&](size_t t, bulk::Tile& tl) {
+            const plan::Move m = plan::gather_consume(sh, t, p, slice_b, cap_b, kBulkTile);
+            tl.src = mystage + m.src;
+            tl.bytes = m.bytes;
+            tl.ndst = 1;
+            tl.dst[0] = recv + m.dst;
+          }, P.timeout_ns);
+        }
       }
       if (stage_failed(ok, 6, c)) return;
       arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_con, make_epoch(P.seq, c + 1), false, 0, 0);

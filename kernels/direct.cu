@@ -19,6 +19,7 @@
 #include "al/cuda/cuda.hpp"
 #include "al/device/kernels.hpp"
 #include "bulk_copy.cuh"
+#include "bulk_tiles.cuh"
 #include "datamove.cuh"
 
 namespace Al {
@@ -54,12 +55,9 @@ __global__ void __launch_bounds__(512) direct_kernel(const __grid_constant__ Col
   arrive_and_post(ws, rank, FlagLayout::off_A, 0, nct, e, false, 0, 0);
   if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
 
-  size_t lo, hi;
-  split_range(count, cta, nct, 16, lo, hi);
-  const size_t dst_off = (size_t)rank * count + lo;
+  const plan::Share sh = plan::share_of(count, count, 0, cta, nct, kTile);  // one "chunk": the whole slice
   bool ok = true;
-  if (send && hi > lo) {
-    const size_t seg = hi - lo;
+  if (send && sh.seg) {
     if (kind == DevColl::allgather) {
       // destinations rotated so that the ranks never converge on one ingress link; the own
       // buffer comes last and is skipped when the contribution already sits in place
@@ -77,38 +75,36 @@ __global__ void __launch_bounds__(512) direct_kernel(const __grid_constant__ Col
       }
       if constexpr (Bulk) {
         if (threadIdx.x == 0) {
-          const size_t nt = (seg + kTile - 1) / kTile;
-          ok = bulk::stream_tiles(ring, nt, [&](size_t t, bulk::Tile& tl) {
-            const size_t off = t * (size_t)kTile;
-            tl.src = send + lo + off;
-            tl.bytes = (uint32_t)(seg - off < (size_t)kTile ? seg - off : (size_t)kTile);
+          ok = bulk::stream_tiles(ring, sh.tiles, [&](size_t t, bulk::Tile& tl) {
+            const plan::Move m = plan::ag_direct(sh, t, rank, count, kTile);
+            tl.src = send + m.src;
+            tl.bytes = m.bytes;
             tl.ndst = n;
-            for (int i = 0; i < n; ++i) tl.dst[i] = dsts[i] + dst_off + off;
+            for (int i = 0; i < n; ++i) tl.dst[i] = dsts[i] + m.dst;
           }, P.timeout_ns);
           __threadfence_system();
         }
       } else {
-        cta_fanout(dsts, n, dst_off, send + lo, seg);
+        const plan::Move m = plan::ag_direct(sh, 0, rank, count, kTile);  // offsets of the share's first byte
+        cta_fanout(dsts, n, m.dst, send + m.src, sh.seg);
       }
     } else {  // alltoall: slice d of the send buffer goes to rank d
       if constexpr (Bulk) {
         if (threadIdx.x == 0) {
-          const size_t nt = (seg + kTile - 1) / kTile;
-          ok = bulk::stream_tiles(ring, nt * (size_t)p, [&](size_t t, bulk::Tile& tl) {
-            const int d = (rank + 1 + (int)(t % (size_t)p)) % p;
-            const size_t off = (t / (size_t)p) * (size_t)kTile;
-            tl.src = send + (size_t)d * count + lo + off;
-            tl.bytes = (uint32_t)(seg - off < (size_t)kTile ? seg - off : (size_t)kTile);
+          ok = bulk::stream_tiles(ring, plan::fan_tiles(sh, p), [&](size_t t, bulk::Tile& tl) {
+            const plan::Move m = plan::a2a_direct(sh, t, rank, p, count, kTile);
+            tl.src = send + m.src;
+            tl.bytes = m.bytes;
             tl.ndst = 1;
-            tl.dst[0] = (char*)P.recv[d] + dst_off + off;
+            tl.dst[0] = (char*)P.recv[m.peer] + m.dst;
           }, P.timeout_ns);
           __threadfence_system();
         }
       } else {
         for (int i = 0; i < p; ++i) {
-          const int d = (rank + 1 + i) % p;
-          char* dst = (char*)P.recv[d];
-          cta_fanout(&dst, 1, dst_off, send + (size_t)d * count + lo, seg);
+          const plan::Move m = plan::a2a_direct(sh, (size_t)i, rank, p, count, kTile);  // tile 0 towards destination i
+          char* dst = (char*)P.recv[m.peer];
+          cta_fanout(&dst, 1, m.dst, send + m.src, sh.seg);
         }
       }
     }

@@ -222,3 +222,14 @@ def test_torch_distributed_backend_on_cpu_ranks(bin_dir, launch):
     r = run([bin_dir / "alrun"] + launch + ["--timeout", "120", sys.executable, W / "torch_backend_worker.py"], timeout=240)
     assert r.returncode == 0 and r.stdout.count("torch backend ok") == n, r.stdout + r.stderr
 
+
+def test_compare_settings_tool(bin_dir, tmp_path):
+    """The tuning comparison drives benchmark_ops under two settings and tabulates both."""
+    out = tmp_path / "cmp.md"
+    r = run([sys.executable, ROOT / "benchmark" / "compare_settings.py", "--ranks", "2", "--backend", "host", "--ops", "allreduce",
+             "--min-bytes", "1024", "--max-bytes", "4096", "--num-iters", "3", "--num-warmup", "1",
+             "--setting", "default", "--setting", "small-stage:AL_HOST_STAGE_BYTES=4096", "--out", out], timeout=240)
+    assert r.returncode == 0, r.stdout + r.stderr
+    text = out.read_text()
+    assert "| bytes | default | small-stage | fastest |" in text and "| 4 KiB |" in text, text
+

@@ -9,8 +9,8 @@ expert / context / pipeline) in :mod:`aluminum_b200.parallel` and the models
 used by the end-to-end benchmark in :mod:`aluminum_b200.models`.
 """
 from ._lib import AlError, lib_path
-from .comm import (HostComm, Request, finalize, get_tuning, info, init, local_rank, local_size, node_index,
-                   num_nodes, set_tuning, world_rank, world_size)
+from .comm import (HostComm, Request, alive_ranks, finalize, get_tuning, info, init, local_rank, local_size,
+                   node_index, num_nodes, peer_alive, set_tuning, world_rank, world_size)
 
 
 def __getattr__(name):
@@ -22,4 +22,4 @@ def __getattr__(name):
 
 __version__ = "0.1.0"
 __all__ = ["AlError", "HostComm", "DeviceComm", "Request", "init", "finalize", "info", "world_rank", "world_size", "local_rank", "local_size", "num_nodes", "node_index",
-           "set_tuning", "get_tuning", "lib_path"]
+           "set_tuning", "get_tuning", "lib_path", "peer_alive", "alive_ranks"]

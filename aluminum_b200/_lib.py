@@ -44,7 +44,7 @@ def _declare(lib) -> None:
         "al_last_error": (C.c_char_p, []),
         "al_init": (i, []), "al_finalize": (i, []), "al_initialized": (i, []),
         "al_world_rank": (i, []), "al_world_size": (i, []), "al_world_local_rank": (i, []),
-        "al_world_local_size": (i, []), "al_world_num_nodes": (i, []), "al_world_node_index": (i, []), "al_cuda_available": (i, []),
+        "al_world_local_size": (i, []), "al_world_num_nodes": (i, []), "al_world_peer_alive": (i, [i]), "al_world_node_index": (i, []), "al_cuda_available": (i, []),
         "al_info": (i, [C.c_char_p, sz]),
         "al_set_tuning": (i, [C.c_char_p, d]), "al_get_tuning": (d, [C.c_char_p]),
         "al_trace_enable": (None, [i]), "al_trace_snapshot": (i, [C.c_char_p, sz]), "al_trace_clear": (None, []),

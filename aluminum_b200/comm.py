@@ -68,6 +68,20 @@ def node_index() -> int:
     return _lib.load().al_world_node_index()
 
 
+def peer_alive(world_rank: int) -> bool:
+    """False once the process of that world rank has exited (or finalised the library)."""
+    v = _lib.load().al_world_peer_alive(int(world_rank))
+    if v < 0:
+        raise AlError(f"no such world rank: {world_rank}")
+    return bool(v)
+
+
+def alive_ranks() -> list:
+    """World ranks whose processes are still there, this one included: after a failure the survivors
+    build a new communicator from this list (``HostComm.from_ranks``) and carry on."""
+    return [r for r in range(world_size()) if peer_alive(r)]
+
+
 def info() -> str:
     buf = C.create_string_buffer(16384)
     check(_lib.load().al_info(buf, len(buf)))

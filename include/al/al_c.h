@@ -28,6 +28,8 @@ int al_world_rank(void);
 int al_world_size(void);
 int al_world_local_rank(void);
 int al_world_local_size(void);
+/** 1 while the process of `world_rank` still holds its control connection, 0 once it has exited or finalised, -1 on error. */
+int al_world_peer_alive(int world_rank);
 /** Number of nodes the world spans, and the index of this rank's node (0-based, by lowest rank). */
 int al_world_num_nodes(void);
 int al_world_node_index(void);

@@ -57,6 +57,15 @@ int al_world_rank(void) { int r = -1; guard([&] { r = get_world()->rank(); }); r
 int al_world_size(void) { int r = -1; guard([&] { r = get_world()->size(); }); return r; }
 int al_world_local_rank(void) { int r = -1; guard([&] { r = get_world()->local_rank(); }); return r; }
 int al_world_local_size(void) { int r = -1; guard([&] { r = get_world()->local_size(); }); return r; }
+int al_world_peer_alive(int world_rank) {
+  int r = -1;
+  guard([&] {
+    World* w = get_world();
+    if (world_rank < 0 || world_rank >= w->size()) throw_al_exception("world rank ", world_rank, " out of range");
+    r = w->peer_alive(world_rank) ? 1 : 0;
+  });
+  return r;
+}
 int al_world_num_nodes(void) { int r = -1; guard([&] { r = get_world()->num_nodes(); }); return r; }
 int al_world_node_index(void) { int r = -1; guard([&] { r = get_world()->node_index(get_world()->rank()); }); return r; }
 int al_cuda_available(void) { return cuda::device_usable() ? 1 : 0; }

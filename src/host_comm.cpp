@@ -54,7 +54,7 @@ constexpr size_t kLine = 64;
 struct Layout {
   int p = 1;
   size_t half = 0, slot = 0;
-  size_t off_A = 0, off_B = 0, off_C = 0, off_meta = 0, off_mctl = 0, off_stage = 0, off_mbox = 0, region = 0;
+  size_t off_A = 0, off_B = 0, off_C = 0, off_meta = 0, off_mctl = 0, off_poison = 0, off_stage = 0, off_mbox = 0, region = 0;
   Layout() = default;
   Layout(int p_, size_t half_, size_t slot_) : p(p_), half(half_), slot(round_up(slot_, kLine)) {
     size_t o = 0;
@@ -63,6 +63,7 @@ struct Layout {
     off_C = o; o += (size_t)p * kLine;
     off_meta = o; o += 2 * (size_t)p * kLine;
     off_mctl = o; o += 2 * (size_t)p * kLine;  // sent, acked per source
+    off_poison = o; o += kLine;                // only the word in region 0 is used
     o = round_up(o, 4096);
     off_stage = o; o += 2 * half;
     off_mbox = o; o += (size_t)p * 2 * slot;
@@ -111,6 +112,8 @@ class Workspace {
   flag_t* acked(int owner, int src) const {
     return (flag_t*)(region(owner) + lay_.off_mctl + (size_t)(2 * src + 1) * kLine);
   }
+  /** Member rank + 1 of the first member whose operation failed; 0 while all is well. */
+  flag_t* poison() const { return (flag_t*)(region(0) + lay_.off_poison); }
   char* stage(int r, int par) const { return region(r) + lay_.off_stage + (size_t)par * lay_.half; }
   char* mbox(int owner, int src, int slot) const {
     return region(owner) + lay_.off_mbox + ((size_t)src * 2 + (size_t)slot) * lay_.slot;
@@ -197,6 +200,27 @@ HostCommunicator HostCommunicator::local() const {
   int n, r, s;
   node_position(group_, &n, &r, &s);
   return HostCommunicator(group_.split(n, group_.rank()));
+}
+
+void HostCommunicator::Impl::fail(const std::string& msg) {
+  {
+    std::lock_guard<std::mutex> g(fail_mu);
+    if (failed.load()) return;
+    fail_msg = msg;
+    failed.store(true);
+  }
+  // First failure on this rank: let the peers know instead of leaving them to their time-outs.
+  if (ws) {
+    uint64_t none = 0;
+    ws->poison()->compare_exchange_strong(none, (uint64_t)me + 1, std::memory_order_acq_rel);
+  }
+  if (net) net->shutdown_all();
+  for (auto* sub : {node_comm.get(), leader_comm.get(), rail_comm.get()})
+    if (sub) sub->abort("the communicator it serves failed: " + msg);
+}
+
+uint64_t HostCommunicator::Impl::poisoned_by() const {
+  return ws ? ws->poison()->load(std::memory_order_acquire) : 0;
 }
 
 HostCommunicator::Impl::~Impl() {

@@ -55,10 +55,14 @@ struct HostCommunicator::Impl {
 
   explicit Impl(const internal::Group& g);
   ~Impl();
-  void fail(const std::string& msg) {
-    std::lock_guard<std::mutex> g(fail_mu);
-    if (!failed.load()) { fail_msg = msg; failed.store(true); }
-  }
+  /**
+   * Record the first failure and tell the peers: a word in the shared workspace (single node) or a
+   * shutdown of this communicator's connections (several nodes) ends their waits at once, and the
+   * node / leader / rail communicators of a two-level layout are failed along with their parent.
+   */
+  void fail(const std::string& msg);
+  /** Member rank + 1 of a peer that failed this (single-node) communicator, 0 if none has. */
+  uint64_t poisoned_by() const;
 };
 
 namespace internal {
@@ -86,6 +90,10 @@ class HostState : public AlState {
   bool timed_out(const char* what) {
     if (ci_->failed.load(std::memory_order_acquire) && !failed_) {
       fail("communicator failed: " + ci_->fail_msg);
+      return true;
+    }
+    if (const uint64_t by = ci_->poisoned_by()) {
+      fail(build_string(get_name(), ": rank ", by - 1, " reported a failure on this communicator"));
       return true;
     }
     const double now = get_time();

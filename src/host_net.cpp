@@ -134,6 +134,12 @@ NetMesh::NetMesh(const Group& g) : p_(g.size()), me_(g.rank()) {
       if (fd >= 0) make_data_socket(fd);
 }
 
+void NetMesh::shutdown_all() const {
+  for (const auto& ch : fds_)
+    for (int fd : ch)
+      if (fd >= 0) ::shutdown(fd, SHUT_RDWR);
+}
+
 NetMesh::~NetMesh() {
   for (auto& v : fds_)
     for (int fd : v)

@@ -39,6 +39,8 @@ class NetMesh {
   int fd(int channel, int peer) const { return fds_[channel][(size_t)peer]; }
   int size() const { return p_; }
   int rank() const { return me_; }
+  /** Shut every connection down (both directions): the peers' pending reads end with "connection closed". */
+  void shutdown_all() const;
 
  private:
   int p_ = 1, me_ = 0;

@@ -233,3 +233,14 @@ def test_compare_settings_tool(bin_dir, tmp_path):
     text = out.read_text()
     assert "| bytes | default | small-stage | fastest |" in text and "| 4 KiB |" in text, text
 
+
+@pytest.mark.parametrize("launch", [["-n", "3"], ["-n", "4", "--nodes", "2"], ["-n", "6", "--nodes", "2"]])
+def test_survivors_rebuild_a_communicator_and_continue(bin_dir, launch):
+    """A rank leaves; the others fail fast (also those waiting in another level of a two-level operation,
+    which hear of it through the shared workspace / closed connections), agree on who is left, build a
+    communicator of the survivors and keep training with equal replicas."""
+    n = int(launch[1])
+    r = run([bin_dir / "alrun"] + launch + ["--timeout", "90", sys.executable, W / "host_recover.py"],
+            env={"AL_HOST_WAIT_TIMEOUT_S": "30"}, timeout=180)
+    assert r.stdout.count("recovered with") == n - 1, r.stdout + r.stderr
+

@@ -70,8 +70,8 @@ elif mode == "dead":
         sys.exit(2)
     except al.AlError as e:
         assert time.time() - t0 < 15, time.time() - t0
-        # the dead rank itself, or a peer that noticed first and has already left in turn
-        assert any(w in str(e) for w in ("closed the connection", "failed", "timed out", "has exited")), str(e)
+        # the dead rank itself, a peer that noticed first and said so, or one that has already left in turn
+        assert any(w in str(e) for w in ("closed the connection", "failed", "timed out", "has exited", "reported a failure")), str(e)
     print(f"rank {me}: detected the dead rank")
 elif mode == "mismatch":
     x = np.zeros(100 if me == 0 else 50, dtype=np.float32)

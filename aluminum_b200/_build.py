@@ -50,6 +50,7 @@ TOOLS = {
     "hello_world": ["examples/hello_world.cpp"],
     "allreduce": ["examples/allreduce.cpp"],
     "pingpong": ["examples/pingpong.cpp"],
+    "recover": ["examples/recover.cpp"],
 }
 
 

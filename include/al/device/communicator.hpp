@@ -79,6 +79,8 @@ class DeviceCommunicator {
   DeviceCommunicator();
   explicit DeviceCommunicator(cudaStream_t stream);
   DeviceCommunicator(const internal::Group& group, cudaStream_t stream);
+  /** Communicator over the listed world ranks, in that order; collective over those ranks only. */
+  static DeviceCommunicator from_ranks(const std::vector<int>& world_ranks, cudaStream_t stream = nullptr);
   /** All `p` ranks in this process on the current device (kernel tests on one GPU). */
   static DeviceCommunicator emulated(int p, cudaStream_t stream);
   ~DeviceCommunicator();

@@ -93,6 +93,8 @@ class HostCommunicator {
   HostCommunicator& operator=(const HostCommunicator&) = delete;
 
   HostCommunicator copy(int /*stream*/ = 0) const { return HostCommunicator(group_); }
+  /** Communicator over the listed world ranks, in that order; collective over those ranks only. */
+  static HostCommunicator from_ranks(const std::vector<int>& world_ranks);
   /** MPI_Comm_split analogue. */
   HostCommunicator split(int color, int key) const { return HostCommunicator(group_.split(color, key)); }
 

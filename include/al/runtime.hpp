@@ -12,6 +12,8 @@
  * writes the trace file when tracing is on.
  */
 #pragma once
+#include <vector>
+
 #include "al/bootstrap.hpp"
 #include "al/progress.hpp"
 
@@ -21,6 +23,14 @@ void Initialize(int& argc, char**& argv);
 void Initialize();
 void Finalize();
 bool Initialized();
+/**
+ * World ranks whose processes still hold their control connection, this one
+ * included.  After a rank was lost the survivors build a communicator over
+ * exactly these (HostCommunicator::from_ranks, DeviceCommunicator::from_ranks)
+ * and carry on; the reference has no counterpart (its communicators are fixed
+ * at creation and a lost rank ends the job).
+ */
+std::vector<int> AliveRanks();
 
 namespace internal {
 /** The control-plane world; throws unless the library is initialised. */

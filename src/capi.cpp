@@ -145,7 +145,7 @@ void* al_host_comm_create_group(const int* world_ranks, int n) {
   void* r = nullptr;
   guard([&] {
     if (!world_ranks || n < 1) throw_al_exception("a group needs at least one world rank");
-    r = new HostCommunicator(Group(get_world(), std::vector<int>(world_ranks, world_ranks + n)));
+    r = new HostCommunicator(HostCommunicator::from_ranks(std::vector<int>(world_ranks, world_ranks + n)));
   });
   return r;
 }
@@ -240,7 +240,7 @@ void* al_dev_comm_create_group(const int* world_ranks, int n, void* stream) {
   void* r = nullptr;
   guard([&] {
     if (!world_ranks || n < 1) throw_al_exception("a group needs at least one world rank");
-    r = new DeviceCommunicator(Group(get_world(), std::vector<int>(world_ranks, world_ranks + n)), (cudaStream_t)stream);
+    r = new DeviceCommunicator(DeviceCommunicator::from_ranks(std::vector<int>(world_ranks, world_ranks + n), (cudaStream_t)stream));
   });
   return r;
 }

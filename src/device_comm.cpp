@@ -138,6 +138,10 @@ DeviceCommunicator DeviceCommunicator::emulated(int p, cudaStream_t stream) {
   return DeviceCommunicator(std::move(impl), Group(), stream);
 }
 
+DeviceCommunicator DeviceCommunicator::from_ranks(const std::vector<int>& world_ranks, cudaStream_t stream) {
+  return DeviceCommunicator(Group(get_world(), world_ranks), stream);
+}
+
 DeviceCommunicator::~DeviceCommunicator() = default;
 DeviceCommunicator::DeviceCommunicator(DeviceCommunicator&&) noexcept = default;
 DeviceCommunicator& DeviceCommunicator::operator=(DeviceCommunicator&&) noexcept = default;

@@ -770,6 +770,10 @@ internal::host::CommStats HostCommunicator::stats() const {
 
 void HostCommunicator::abort(const std::string& why) { impl_->fail(why); }
 
+HostCommunicator HostCommunicator::from_ranks(const std::vector<int>& world_ranks) {
+  return HostCommunicator(Group(get_world(), world_ranks));
+}
+
 bool HostCommunicator::failed() const { return impl_->failed.load(); }
 
 }  // namespace Al

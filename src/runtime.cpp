@@ -130,6 +130,14 @@ bool Initialized() {
   return g_rt != nullptr;
 }
 
+std::vector<int> AliveRanks() {
+  internal::World* w = internal::get_world();
+  std::vector<int> alive;
+  for (int r = 0; r < w->size(); ++r)
+    if (w->peer_alive(r)) alive.push_back(r);
+  return alive;
+}
+
 namespace internal {
 
 ProgressEngine* get_progress_engine() {

@@ -244,3 +244,10 @@ def test_survivors_rebuild_a_communicator_and_continue(bin_dir, launch):
             env={"AL_HOST_WAIT_TIMEOUT_S": "30"}, timeout=180)
     assert r.stdout.count("recovered with") == n - 1, r.stdout + r.stderr
 
+
+def test_cpp_recover_example(bin_dir):
+    """examples/recover.cpp: Al::AliveRanks + HostCommunicator::from_ranks after a rank left."""
+    for launch, n in ((["-n", "4"], 4), (["-n", "6", "--nodes", "2"], 6)):
+        r = run([bin_dir / "alrun"] + launch + ["--timeout", "60", bin_dir / "recover"], env={"AL_HOST_WAIT_TIMEOUT_S": "30"}, timeout=120)
+        assert r.stdout.count("carried on with %d of %d" % (n - 1, n)) == n - 1, r.stdout + r.stderr
+

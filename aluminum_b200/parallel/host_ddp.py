@@ -14,6 +14,7 @@ from __future__ import annotations
 
 from typing import List
 
+import numpy as np
 import torch
 from torch import nn
 
@@ -113,6 +114,28 @@ class HostDataParallel:
         self.flat_param.add_(self.flat_mom, alpha=-self.lr)
         self.flat_grad.zero_()
         self.steps += 1
+
+    def rebuild(self, comm, root: int = 0) -> None:
+        """Continue on another communicator, typically the survivors' after a rank was lost
+        (``HostComm.from_ranks(al.alive_ranks())``).  Collective over the new communicator.  Whatever the
+        failed step left behind is dropped: unfinished requests, partly averaged gradients.  Parameters,
+        buffers and momentum are taken from `root` of the new communicator, so the replicas are equal again
+        whichever of them had got how far."""
+        for b in self.buckets:
+            b.req = None
+            b.pending = b.total
+        self.flat_grad.zero_()
+        had_hooks = self.world > 1
+        self.comm, self.world = comm, comm.size
+        if self.world > 1:
+            if not had_hooks:
+                for p in self._bucket_of:
+                    p.register_post_accumulate_grad_hook(self._on_grad)
+            self.broadcast_parameters(root)
+            self.comm.bcast(self.flat_mom.numpy(), root=root)
+            steps = np.array([self.steps], dtype=np.int64)
+            self.comm.bcast(steps, root=root)
+            self.steps = int(steps[0])
 
     def state_dict(self) -> dict:
         return {"model": self.module.state_dict(), "momentum": self.flat_mom.clone(), "steps": self.steps}

@@ -251,3 +251,12 @@ def test_cpp_recover_example(bin_dir):
         r = run([bin_dir / "alrun"] + launch + ["--timeout", "60", bin_dir / "recover"], env={"AL_HOST_WAIT_TIMEOUT_S": "30"}, timeout=120)
         assert r.stdout.count("carried on with %d of %d" % (n - 1, n)) == n - 1, r.stdout + r.stderr
 
+
+@pytest.mark.parametrize("launch", [["-n", "3"], ["-n", "4", "--nodes", "2"]])
+def test_data_parallel_training_outlives_a_rank(bin_dir, launch):
+    """HostDataParallel.rebuild on the survivors' communicator: training goes on, replicas stay equal."""
+    n = int(launch[1])
+    r = run([bin_dir / "alrun"] + launch + ["--timeout", "90", sys.executable, W / "host_ddp_recover.py"],
+            env={"AL_HOST_WAIT_TIMEOUT_S": "30"}, timeout=180)
+    assert r.stdout.count(f"trained on with {n - 1} ranks, steps 6") == n - 1, r.stdout + r.stderr
+

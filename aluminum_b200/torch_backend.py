@@ -212,8 +212,8 @@ class AluminumProcessGroup(dist.ProcessGroup):
             c.alltoall(inp.view(-1), res.view(-1))
         else:
             p = self.size()
-            row_in = inp[0].numel() if inp.dim() > 1 else 1
-            row_out = res[0].numel() if res.dim() > 1 else 1
+            row_in = inp.numel() // inp.shape[0] if inp.dim() > 1 and inp.shape[0] else 1
+            row_out = res.numel() // res.shape[0] if res.dim() > 1 and res.shape[0] else 1
             ins = list(input_split_sizes) if input_split_sizes else [inp.shape[0] // p] * p
             outs = list(output_split_sizes) if output_split_sizes else [res.shape[0] // p] * p
             sc = [n * row_in for n in ins]

@@ -172,6 +172,11 @@ class AluminumProcessGroup(dist.ProcessGroup):
             output.copy_(flat.view_as(output))
         return _Work(output)
 
+    def allgather_coalesced(self, output_lists, input_tensors, opts=None):
+        for outs, inp in zip(output_lists, input_tensors):
+            self.allgather([outs], [inp], opts)
+        return _Work(output_lists)
+
     def allgather_into_tensor_coalesced(self, outputs, inputs, opts=None):
         for o, i in zip(outputs, inputs):
             self._allgather_base(o, i, opts)

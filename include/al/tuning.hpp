@@ -48,6 +48,7 @@ struct Tuning {
   size_t pipeline_min_bytes = size_t{32} << 20;  ///< AL_PIPELINE_MIN: per-rank slice from which reduce_scatter / allgather / alltoall split the grid into publishers and consumers
   size_t nvls_pipeline_min_bytes = size_t{128} << 20;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is pipelined from this size on
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
+  int p2p_max_ctas = 16;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)
   bool bulk_pipeline = false;                  ///< AL_DEV_BULK_PIPELINE: pipelined reduce_scatter / allgather / alltoall move their data with the bulk copy engine (cp.async.bulk) when every buffer is 16-byte aligned
   int bulk_pub_ctas = 16;                      ///< AL_DEV_BULK_PUB_CTAS: publishing CTAs of that kernel (one issuing thread each)
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)

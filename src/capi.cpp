@@ -99,7 +99,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
   X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(direct_symmetric) X(direct_bulk)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(direct_symmetric) X(direct_bulk)
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {

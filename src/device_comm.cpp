@@ -519,8 +519,9 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
       --remaining;
       I.stats.bytes += it.bytes;
     }
-    int per = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(std::min(biggest, slot), (size_t)65536), 16));
+    int per = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(std::min(biggest, slot), (size_t)65536), (size_t)tuning().p2p_max_ctas));
     if (I.nlocal > 1) per = std::max(1, std::min(per, I.sm_count / P.nitems));
+    else per = std::max(1, std::min(per, 2 * I.sm_count / P.nitems));  // waiting CTAs must all be resident
     P.ctas_per_item = per;
     I.stats.ops++;
     I.stats.kernels++;

@@ -41,6 +41,7 @@ void Tuning::load_from_env() {
   max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
   max_ctas_zero_copy = (int)env_long("AL_MAX_CTAS_ZERO_COPY", max_ctas_zero_copy);
   threads_per_cta = (int)env_long("AL_THREADS_PER_CTA", threads_per_cta);
+  p2p_max_ctas = (int)env_long("AL_DEV_P2P_CTAS", p2p_max_ctas);
   bulk_pipeline = env_long("AL_DEV_BULK_PIPELINE", bulk_pipeline) != 0;
   bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
   bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
@@ -60,6 +61,7 @@ void Tuning::load_from_env() {
   if (max_ctas_nvls > AL_MAX_CTAS) max_ctas_nvls = AL_MAX_CTAS;
   if (max_ctas_zero_copy < 1) max_ctas_zero_copy = 1;
   if (max_ctas_zero_copy > AL_MAX_CTAS) max_ctas_zero_copy = AL_MAX_CTAS;
+  p2p_max_ctas = std::max(1, std::min(p2p_max_ctas, AL_MAX_CTAS / 2));
   bulk_pub_ctas = std::max(1, std::min(bulk_pub_ctas, AL_MAX_CTAS / 2));
   bulk_con_ctas = std::max(1, std::min(bulk_con_ctas, AL_MAX_CTAS / 2));
   if (threads_per_cta < 64) threads_per_cta = 64;
@@ -103,6 +105,7 @@ std::string Tuning::describe() const {
      << "max_ctas_nvls = " << max_ctas_nvls << "\n"
      << "max_ctas_zero_copy = " << max_ctas_zero_copy << "\n"
      << "threads_per_cta = " << threads_per_cta << "\n"
+     << "p2p_max_ctas = " << p2p_max_ctas << "\n"
      << "bulk_pipeline = " << bulk_pipeline << "\n"
      << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
      << "bulk_con_ctas = " << bulk_con_ctas << "\n"

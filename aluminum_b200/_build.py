@@ -42,6 +42,7 @@ TOOLS = {
     "test_rma": ["cpp_tests/test_rma.cpp"],
     "test_exchange": ["cpp_tests/test_exchange.cpp"],
     "test_stream_mem_ops": ["cpp_tests/test_stream_mem_ops.cpp"],
+    "test_ht_failure": ["cpp_tests/test_ht_failure.cpp"],
     "benchmark_ops": ["benchmark/benchmark_ops.cpp"],
     "bandwidth": ["benchmark/bandwidth.cpp"],
     "benchmark_waits": ["benchmark/benchmark_waits.cpp"],

@@ -65,6 +65,7 @@ def _declare(lib) -> None:
         "al_dev_comm_set_timeout_ms": (i, [vp, d]), "al_dev_comm_stats": (i, [vp, u64p]),
         "al_dev_comm_status": (i, [vp, u64p]),
         "al_dev_collective": (i, [vp, i, i, vpp, vpp, sz, i, i, i, i, i, i, i, szp, szp, szp, szp, d, i, i, vp, vpp]),
+        "al_dev_time_collective": (i, [vp, i, vp, vp, sz, i, i, i, i, vp, C.POINTER(C.c_float)]),
         "al_dev_p2p": (i, [vp, i, ip, ip, ip, vpp, szp, vp, vpp]),
         "al_dev_test": (i, [vpp, ip]), "al_dev_wait": (i, [vpp]),
         "al_dev_symm_alloc": (vp, [vp, sz]), "al_dev_symm_free": (i, [vp, vp]),

@@ -219,6 +219,18 @@ class DeviceComm:
     def barrier(self, **kw):
         return self._coll("barrier", None, None, 0, **kw)
 
+    def time_collective(self, kind: str, send, recv, count: int, warmup: int = 20, iters: int = 100, op: str = "sum",
+                        stream=None):
+        """Benchmark helper: device times (ms) of ``iters`` out-of-place calls of one collective, each preceded
+        by a host barrier of the ranks and bracketed by a CUDA event pair (native loop, no Python in between).
+        ``count`` is the element count the operation takes (per-rank slice for reduce_scatter / allgather /
+        alltoall)."""
+        out = (C.c_float * iters)()
+        check(self._lib.al_dev_time_collective(self._h, KINDS[kind], C.c_void_p(send.data_ptr()),
+                                               C.c_void_p(recv.data_ptr()), int(count), _code(recv), OPS[op],
+                                               int(warmup), int(iters), self._stream(stream), out))
+        return [float(v) for v in out]
+
     # vector forms: counts / displacements in elements, one row per local rank in emulation
     def reduce_scatterv(self, send, recv, counts, op="sum", **kw):
         return self._coll("reduce_scatter", send, recv, 0, op, tables={"recv_counts": counts}, **kw)

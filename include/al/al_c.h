@@ -107,6 +107,14 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
                       int dt_in, int dt_wire, int dt_out, int op, int root, int inplace, int vector,
                       const size_t* send_counts, const size_t* send_displs, const size_t* recv_counts,
                       const size_t* recv_displs, double scale, int algo, int ctas, void* stream, void** req_out);
+/**
+ * Benchmark helper: `warmup` untimed then `iters` timed out-of-place calls of one collective, each
+ * preceded by a host barrier of the communicator's ranks and bracketed by a CUDA event pair on
+ * `stream` (the reference's own timing protocol, benchmark/benchmark_ops.cpp:184-191).
+ * out_ms receives the `iters` device times in milliseconds.
+ */
+int al_dev_time_collective(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op,
+                           int warmup, int iters, void* stream, float* out_ms);
 /** owner[i] is the issuing rank (emulation) or ignored. */
 int al_dev_p2p(void* comm, int n, const int* is_send, const int* peer, const int* owner, void* const* buf,
                const size_t* bytes, void* stream, void** req_out);

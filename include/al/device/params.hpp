@@ -47,10 +47,10 @@ struct FlagLayout {
   static constexpr size_t off_rma = off_p2p_acked + kMaxRanks * stride;       // [kMaxRanks] notify counters
   static constexpr size_t off_halo = off_rma + kMaxRanks * stride;         // [4] ready-from-lo, ready-from-hi, data-from-lo, data-from-hi
   // Words below are only touched by the owning GPU.
-  static constexpr size_t off_arrive = off_halo + 4 * stride;              // [4] CTA arrival counters (A, B, C, spare)
-  static constexpr size_t off_status = off_arrive + 4 * stride;            // device-local copy of the status code
-  static constexpr size_t off_p2p_arrive = off_status + stride;            // [16] per-item CTA arrival counters
-  static constexpr size_t words = off_p2p_arrive + 16 * stride;
+  static constexpr size_t off_arrive = off_halo + 4 * stride;              // [2][4] CTA arrival counters (A, B, C, spare) per round parity
+  static constexpr size_t off_status = off_arrive + 8 * stride;            // device-local copy of the status code
+  static constexpr size_t off_p2p_arrive = off_status + stride;            // [2][16] per-item CTA arrival counters per piece parity
+  static constexpr size_t words = off_p2p_arrive + 32 * stride;
   static constexpr size_t bytes = (words * 8 + 4095) / 4096 * 4096;
 };
 

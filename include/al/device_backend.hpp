@@ -17,6 +17,10 @@
  * plain host load and Wait involves no event.
  */
 #pragma once
+#include <atomic>
+#include <mutex>
+#include <string>
+
 #include "al/cuda/events.hpp"
 #include "al/cuda/streams.hpp"
 #include "al/cuda/sync_memory.hpp"
@@ -29,6 +33,23 @@ namespace Al {
 namespace internal {
 namespace device {
 
+/** First failure of a communicator's background operations, shared with the requests they returned. */
+struct AsyncFailure {
+  std::atomic<bool> failed{false};
+  std::mutex mu;
+  std::string message;
+  void set(const std::string& what) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!failed.load()) { message = what; failed.store(true, std::memory_order_release); }
+  }
+  /** Throws al_exception if a failure was recorded. */
+  void check(const char* context) {
+    if (!failed.load(std::memory_order_acquire)) return;
+    std::lock_guard<std::mutex> lock(mu);
+    throw_al_exception(context, ": ", message);
+  }
+};
+
 struct RequestState {
   cudaEvent_t event = nullptr;      // event mode
   int32_t* flag = nullptr;          // memops mode: the internal stream's pinned counter word (not owned)
@@ -37,6 +58,7 @@ struct RequestState {
   cudaStream_t orig_stream = nullptr;
   cudaStream_t internal_stream = nullptr;
   std::shared_ptr<DeviceCommunicator::Impl> comm;
+  std::shared_ptr<AsyncFailure> failure;  // host-transfer operations: where the progress engine reports errors
   ~RequestState() {
     if (event) cuda::event_pool.release(event);
   }

@@ -29,8 +29,10 @@ namespace Al {
 class HostTransferCommunicator {
  public:
   HostTransferCommunicator() : HostTransferCommunicator((cudaStream_t) nullptr) {}
-  explicit HostTransferCommunicator(cudaStream_t stream) : host_(), stream_(stream) {}
-  HostTransferCommunicator(const internal::Group& g, cudaStream_t stream) : host_(g), stream_(stream) {}
+  explicit HostTransferCommunicator(cudaStream_t stream)
+      : host_(), stream_(stream), failure_(std::make_shared<internal::device::AsyncFailure>()) {}
+  HostTransferCommunicator(const internal::Group& g, cudaStream_t stream)
+      : host_(g), stream_(stream), failure_(std::make_shared<internal::device::AsyncFailure>()) {}
   HostTransferCommunicator(HostTransferCommunicator&&) noexcept = default;
   HostTransferCommunicator& operator=(HostTransferCommunicator&&) noexcept = default;
   HostTransferCommunicator copy(cudaStream_t stream = nullptr) const {
@@ -46,6 +48,13 @@ class HostTransferCommunicator {
   int local_size() const { return host_.local_size(); }
   cudaStream_t get_stream() const { return stream_; }
   HostCommunicator& host() { return host_; }
+  /**
+   * Where the progress engine records a failed host exchange (a peer that exited, a time-out,
+   * abort).  Once set, every later call on this communicator and Test / Wait on its requests
+   * throw; the device buffers of the failed operation hold no valid result.
+   */
+  const std::shared_ptr<internal::device::AsyncFailure>& failure() const { return failure_; }
+  bool failed() const { return failure_->failed.load(std::memory_order_acquire); }
   /**
    * The stream non-blocking operations of this communicator run on, created
    * on first use.  Every host-transfer communicator has its own: an operation
@@ -68,6 +77,7 @@ class HostTransferCommunicator {
  private:
   HostCommunicator host_;
   cudaStream_t stream_;
+  std::shared_ptr<internal::device::AsyncFailure> failure_;
   std::shared_ptr<CUstream_st> internal_;
 };
 
@@ -99,6 +109,7 @@ class HostTransferBackend {
       cudaStream_t s = begin_nonblocking_on(comm.get_stream(), comm.internal_stream());
       internal::ht::run_collective(std::move(r), comm, s);
       *req = end_nonblocking_stream(comm.get_stream(), s);
+      (*req)->failure = comm.failure();
     } else {
       internal::ht::run_collective(std::move(r), comm, comm.get_stream());
     }
@@ -115,6 +126,7 @@ class HostTransferBackend {
       cudaStream_t s = begin_nonblocking_on(comm.get_stream(), comm.internal_stream());
       internal::ht::run_p2p(std::move(items), comm, s, name);
       *req = end_nonblocking_stream(comm.get_stream(), s);
+      (*req)->failure = comm.failure();
     } else {
       internal::ht::run_p2p(std::move(items), comm, comm.get_stream(), name);
     }

@@ -106,6 +106,13 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* slot, uint64_t epoch, 
  * the CTA's share of the preceding writes is issued.  The last CTA to arrive stores `epoch` into
  * slot [rank] of every rank's flag array `off` (optionally after publishing
  * `meta_value` into the meta word of parity `meta_par`).
+ *
+ * Consecutive rounds of one kernel carry consecutive epochs and count their arrivals in
+ * two counters chosen by the epoch's low bit.  In every schedule of this library a CTA can
+ * only be two rounds ahead of the slowest CTA of its group once the round in between has been
+ * posted (the gate of round k+2 depends, through the peers, on the post of round k), so the
+ * arrivals of at most two neighbouring rounds are ever in flight and a fast CTA's arrival
+ * for round k+1 can never complete the count of round k.
  */
 __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, size_t off, int counter_idx,
                                                 unsigned group, uint64_t epoch, bool with_meta, int meta_par,
@@ -116,7 +123,7 @@ __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, s
     int last = 1;
     if (group > 1) {
       __threadfence();  // this CTA's writes before the arrival count
-      unsigned* ctr = (unsigned*)flag_slot(ws.flags[rank], FlagLayout::off_arrive, counter_idx);
+      unsigned* ctr = (unsigned*)flag_slot(ws.flags[rank], FlagLayout::off_arrive, counter_idx + 4 * (int)(epoch & 1));
       last = atomicInc(ctr, group - 1) == group - 1;
       if (last) __threadfence();  // other CTAs' writes before the flag stores
     }

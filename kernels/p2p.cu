@@ -62,7 +62,10 @@ __global__ void __launch_bounds__(512) p2p_kernel(const __grid_constant__ P2PPar
   const size_t bytes = P.bytes[item];
   const size_t pieces = bytes == 0 ? 1 : (bytes + slot - 1) / slot;
   uint64_t* myflags = ws.flags[me];
-  uint64_t* arrive = flag_slot(myflags, FlagLayout::off_p2p_arrive, item);
+  // Arrivals are counted per piece parity: the credit gate of piece n depends on the post of
+  // piece n-2, so a CTA is never more than one unposted piece ahead of its slowest sibling.
+  uint64_t* arrive2[2] = {flag_slot(myflags, FlagLayout::off_p2p_arrive, item),
+                          flag_slot(myflags, FlagLayout::off_p2p_arrive, item + P2PParams::kMaxItems)};
 
   if (P.is_send[item]) {
     const uint64_t base = P.base[item];  // pieces already sent to this peer by earlier launches
@@ -78,7 +81,7 @@ __global__ void __launch_bounds__(512) p2p_kernel(const __grid_constant__ P2PPar
       split_range(len, part, group, 16, lo, hi);
       char* dst = ws.mbox[peer] + ((size_t)me * 2 + (n & 1)) * slot;
       if (hi > lo) cta_copy(dst + lo, src + off + lo, hi - lo, false);
-      group_arrive(arrive, group, [&] {
+      group_arrive(arrive2[n & 1], group, [&] {
         st_release_sys(sent_remote, n + 1);
       });
     }
@@ -95,7 +98,7 @@ __global__ void __launch_bounds__(512) p2p_kernel(const __grid_constant__ P2PPar
       split_range(len, part, group, 16, lo, hi);
       const char* src = ws.mbox[me] + ((size_t)peer * 2 + (n & 1)) * slot;
       if (hi > lo) cta_copy(dstbuf + off + lo, src + lo, hi - lo, true);
-      group_arrive(arrive, group, [&] {
+      group_arrive(arrive2[n & 1], group, [&] {
         st_release_sys(acked_remote, n + 1);
       });
     }

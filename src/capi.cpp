@@ -331,6 +331,34 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
   });
 }
 
+int al_dev_time_collective(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op,
+                           int warmup, int iters, void* stream, float* out_ms) {
+  return guard([&] {
+    DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    if (c.is_emulated()) throw_al_exception("al_dev_time_collective: not for emulated communicators");
+    cudaStream_t s = pick_stream(&c, stream);
+    cudaEvent_t e0, e1;
+    AL_CHECK_CUDA(cudaEventCreate(&e0));
+    AL_CHECK_CUDA(cudaEventCreate(&e1));
+    const void* sp[1] = {send};
+    void* rp[1] = {recv};
+    for (int i = 0; i < warmup + iters; ++i) {
+      c.group().barrier();
+      AL_CHECK_CUDA(cudaEventRecord(e0, s));
+      if (al_dev_collective(comm, kind, 1, sp, rp, count, dtype, -1, -1, op, 0, 0, 0, nullptr, nullptr, nullptr, nullptr,
+                            1.0, 0, 0, (void*)s, nullptr) != 0)
+        throw_al_exception(g_err);
+      AL_CHECK_CUDA(cudaEventRecord(e1, s));
+      AL_CHECK_CUDA(cudaEventSynchronize(e1));
+      float ms = 0;
+      AL_CHECK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      if (i >= warmup) out_ms[i - warmup] = ms;
+    }
+    AL_CHECK_CUDA(cudaEventDestroy(e0));
+    AL_CHECK_CUDA(cudaEventDestroy(e1));
+  });
+}
+
 int al_dev_p2p(void* comm, int n, const int* is_send, const int* peer, const int* owner, void* const* buf,
                const size_t* bytes, void* stream, void** req_out) {
   return guard([&] {

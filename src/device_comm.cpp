@@ -261,7 +261,14 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       const RankArgs& a = ranks[0];
       sb_in = find_symm(a.send, bytes, &off_in);
       sb_out = find_symm(a.recv, bytes, &off_out);
-      zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0);
+      // The kernel works on whole 16-byte vectors.  A length that is not a multiple of 16 is only
+      // acceptable where the last vector ends in the block's own padding (symm_alloc pads to 16):
+      // anywhere else the tail vector would overwrite the caller's elements after `count`.
+      auto tail_ok = [&](const SymmBlock* b, size_t off) {
+        return bytes % 16 == 0 || round_up(off + bytes, 16) == b->bytes();
+      };
+      zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0) &&
+                  tail_ok(sb_in, off_in) && tail_ok(sb_out, off_out);
     }
     if (algo == AllreduceAlgo::automatic) {
       // Measured on 4 and 8 B200: the one-shot push wins for small messages (up to 256 KiB on

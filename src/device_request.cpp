@@ -86,6 +86,7 @@ Request end_nonblocking_stream(cudaStream_t comm_stream, cudaStream_t internal_s
 
 bool test_request(Request& req) {
   if (!req) return true;
+  if (req->failure) req->failure->check("host-transfer operation failed");
   bool done;
   if (req->flag) {
     done = (int32_t)((uint32_t)__atomic_load_n(req->flag, __ATOMIC_ACQUIRE) - req->ticket) >= 0;
@@ -94,12 +95,17 @@ bool test_request(Request& req) {
     if (e == cudaErrorNotReady) { (void)cudaGetLastError(); done = false; }
     else { AL_CHECK_CUDA(e); done = true; }
   }
-  if (done) req = nullptr;
+  if (done) {
+    // the host side of a host-transfer operation reports before it releases the stream
+    if (req->failure) req->failure->check("host-transfer operation failed");
+    req = nullptr;
+  }
   return done;
 }
 
 void wait_request(Request& req) {
   if (!req) return;
+  if (req->failure) req->failure->check("host-transfer operation failed");
   if (req->internal_stream != req->orig_stream) {
     if (req->flag)
       AL_CHECK_CUDA_DRV(cuda::drv().StreamWaitValue32((CUstream)req->orig_stream, req->flag_dev, req->ticket, CU_STREAM_WAIT_VALUE_GEQ));

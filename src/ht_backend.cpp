@@ -2,6 +2,7 @@
 #include "al/ht_backend.hpp"
 
 #include <algorithm>
+#include <cstring>
 
 #include "al/cuda/gpu_status_flag.hpp"
 #include "al/cuda/gpu_wait.hpp"
@@ -59,7 +60,8 @@ Extent extent_of(const Resolved& r, int rank, int size) {
 /** Engine state shared by collectives and point-to-point: stage 0 waits for the D2H flag. */
 class HTState final : public AlState {
  public:
-  HTState(cudaStream_t stream, const char* name) : stream_(stream), name_(name) {}
+  HTState(cudaStream_t stream, const char* name, std::shared_ptr<device::AsyncFailure> failure)
+      : failure_(std::move(failure)), stream_(stream), name_(name) {}
   ~HTState() override {
     for (void* p : pinned_) mempool.release_bytes(MemoryType::CUDA_PINNED_HOST, p);
   }
@@ -79,7 +81,10 @@ class HTState final : public AlState {
         } catch (const std::exception& e) {
           // The host communicator refused the operation (it failed earlier): release the
           // stream so that nothing on the device waits forever, and say why.
-          std::cerr << "[al] host-transfer operation could not start: " << e.what() << "\n";
+          // The failure is recorded BEFORE the stream is released, so whoever sees the operation's
+          // completion event also sees the error.
+          failure_->set(std::string("the host exchange could not start: ") + e.what());
+          poison_receive_buffers();
           wait.signal();
           phase_ = 3;
           return PEAction::cont;
@@ -95,8 +100,9 @@ class HTState final : public AlState {
       case 2:
         try {
           if (!HostBackend::test(host_req)) return PEAction::cont;
-        } catch (const al_exception& e) {
-          std::cerr << "[al] host-transfer operation failed: " << e.what() << "\n";
+        } catch (const std::exception& e) {
+          failure_->set(e.what());
+          poison_receive_buffers();
         }
         if (!early_release_) wait.signal();  // release the stream: H2D copy and end flag follow
         phase_ = 3;
@@ -111,6 +117,8 @@ class HTState final : public AlState {
     pinned_.push_back(p);
     return p;
   }
+  /** Host buffers whose contents go back to the device when the stream is released. */
+  void returns_to_device(void* host, size_t bytes) { back_.push_back({host, bytes}); }
 
   cuda::GPUStatusFlag start_flag, end_flag;
   cuda::GPUWait wait;
@@ -121,6 +129,16 @@ class HTState final : public AlState {
 
  private:
   void launch_host() { launcher(&host_req); }
+  /**
+   * The copies back to the device are already enqueued behind the stream's wait and cannot be
+   * withdrawn; after a failure they carry 0xFF bytes (NaN for floating-point types) instead of
+   * stale pool memory, so a result that is used in spite of the error is conspicuous.
+   */
+  void poison_receive_buffers() {
+    for (auto& b : back_) memset(b.first, 0xFF, b.second);
+  }
+  std::shared_ptr<device::AsyncFailure> failure_;
+  std::vector<std::pair<void*, size_t>> back_;
   cudaStream_t stream_;
   const char* name_;
   int phase_ = 0;
@@ -132,7 +150,8 @@ class HTState final : public AlState {
 void run_collective(Resolved&& r, HostTransferCommunicator& comm, cudaStream_t stream) {
   const Extent e = extent_of(r, comm.rank(), comm.size());
   const size_t esz = dtype_size(r.dt);
-  auto* st = new HTState(stream, "HTCollective");
+  comm.failure()->check("host-transfer communicator failed earlier");
+  auto* st = new HTState(stream, "HTCollective", comm.failure());
   void* hsend = e.send_elems ? st->pinned(e.send_elems * esz) : nullptr;
   void* hrecv = e.recv_elems ? st->pinned(e.recv_elems * esz) : nullptr;
   const void* dsend = r.send;
@@ -142,7 +161,10 @@ void run_collective(Resolved&& r, HostTransferCommunicator& comm, cudaStream_t s
   if (hrecv && r.vector) AL_CHECK_CUDA(cudaMemcpyAsync(hrecv, drecv, e.recv_elems * esz, cudaMemcpyDeviceToHost, stream));
   st->start_flag.record(stream);
   st->wait.wait(stream);
-  if (hrecv) AL_CHECK_CUDA(cudaMemcpyAsync(drecv, hrecv, e.recv_elems * esz, cudaMemcpyHostToDevice, stream));
+  if (hrecv) {
+    AL_CHECK_CUDA(cudaMemcpyAsync(drecv, hrecv, e.recv_elems * esz, cudaMemcpyHostToDevice, stream));
+    st->returns_to_device(hrecv, e.recv_elems * esz);
+  }
   st->end_flag.record(stream);
   st->early_release_ = hrecv == nullptr && r.kind != OpKind::barrier;  // a barrier holds the stream by definition
 
@@ -159,7 +181,8 @@ void run_collective(Resolved&& r, HostTransferCommunicator& comm, cudaStream_t s
 }
 
 void run_p2p(std::vector<host::P2PItem>&& items, HostTransferCommunicator& comm, cudaStream_t stream, const char* name) {
-  auto* st = new HTState(stream, name);
+  comm.failure()->check("host-transfer communicator failed earlier");
+  auto* st = new HTState(stream, name, comm.failure());
   st->unbounded_ = true;
   struct Back { void* host; void* dev; size_t bytes; };
   std::vector<Back> backs;
@@ -176,8 +199,10 @@ void run_p2p(std::vector<host::P2PItem>&& items, HostTransferCommunicator& comm,
   }
   st->start_flag.record(stream);
   st->wait.wait(stream);
-  for (auto& b : backs)
+  for (auto& b : backs) {
     if (b.bytes) AL_CHECK_CUDA(cudaMemcpyAsync(b.dev, b.host, b.bytes, cudaMemcpyHostToDevice, stream));
+    st->returns_to_device(b.host, b.bytes);
+  }
   st->end_flag.record(stream);
   st->early_release_ = backs.empty();
   auto shared = std::make_shared<std::vector<host::P2PItem>>(std::move(items));

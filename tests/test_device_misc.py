@@ -174,6 +174,13 @@ def test_host_transfer_backend(al, bin_dir, op):
     assert r.returncode == 0, r.stdout + r.stderr
 
 
+def test_host_transfer_failure_reaches_the_caller(al, bin_dir):
+    """A failed host exchange (the host communicator is aborted on the host) makes Test / Wait and later calls
+    throw, releases the stream, and leaves NaN instead of stale bytes in the receive buffer."""
+    r = subprocess.run([str(bin_dir / "test_ht_failure")], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "ht failure test: ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_single_gpu_tools(al, bin_dir):
     """Wait / event micro-benchmarks and the single-rank device examples run on this GPU."""
     for tool, needle in (("benchmark_waits", "signal-to-pass"), ("benchmark_events", "pinned flag"),

@@ -29,7 +29,8 @@ OPS = {"sum": 0, "prod": 1, "min": 2, "max": 3, "lor": 4, "land": 5, "lxor": 6, 
        "avg": 10}
 KINDS = {"allreduce": 0, "reduce": 1, "reduce_scatter": 2, "allgather": 3, "alltoall": 4, "bcast": 5, "gather": 6,
          "scatter": 7, "barrier": 8}
-ALGOS = {"auto": 0, "one_shot": 1, "two_shot": 2, "nvls": 3}
+ALGOS = {"auto": 0, "one_shot": 1, "two_shot": 2, "nvls": 3, "ll": 4}
+PATHS = {"auto": 0, "staged": 1, "window": 2, "ll": 3}  # data path of every collective but allreduce
 COMM_STREAM = C.c_void_p(-1 & (2 ** 64 - 1))
 
 
@@ -65,13 +66,15 @@ def _declare(lib) -> None:
         "al_dev_comm_set_timeout_ms": (i, [vp, d]), "al_dev_comm_stats": (i, [vp, u64p]),
         "al_dev_comm_status": (i, [vp, u64p]),
         "al_dev_collective": (i, [vp, i, i, vpp, vpp, sz, i, i, i, i, i, i, i, szp, szp, szp, szp, d, i, i, vp, vpp]),
+        "al_dev_register": (i, [vp, vp, sz]), "al_dev_register_emulated": (i, [vp, vpp, i, sz]),
+        "al_dev_unregister": (i, [vp, vp]),
         "al_dev_time_collective": (i, [vp, i, vp, vp, sz, i, i, i, i, vp, C.POINTER(C.c_float)]),
         "al_dev_p2p": (i, [vp, i, ip, ip, ip, vpp, szp, vp, vpp]),
         "al_dev_test": (i, [vpp, ip]), "al_dev_wait": (i, [vpp]),
         "al_dev_symm_alloc": (vp, [vp, sz]), "al_dev_symm_free": (i, [vp, vp]),
         "al_dev_symm_peer_ptr": (vp, [vp, vp, i]),
         "al_rma_attach": (vp, [vp, vp, i]), "al_rma_detach": (i, [vp, vp, i]),
-        "al_rma_put": (i, [vp, vp, i, vp, sz]), "al_rma_notify": (i, [vp, i]), "al_rma_wait": (i, [vp, i]),
+        "al_rma_put": (i, [vp, vp, i, vp, sz]), "al_rma_get": (i, [vp, vp, i, vp, sz]), "al_rma_notify": (i, [vp, i]), "al_rma_wait": (i, [vp, i]),
         "al_rma_sync": (i, [vp, i]),
         "al_halo_exchange": (i, [vp, vpp, sz, sz, sz, sz, i, i, vp]),
         "al_halo_pack": (i, [vp, vp, sz, sz, sz, sz, sz, i, vp]),

@@ -11,7 +11,7 @@ import ctypes as C
 from typing import Optional, Sequence
 
 from . import _lib
-from ._lib import ALGOS, DTYPES, KINDS, OPS, AlError, check, check_ptr, size_array
+from ._lib import ALGOS, DTYPES, KINDS, OPS, PATHS, AlError, check, check_ptr, size_array
 from .comm import Request, init
 
 
@@ -83,9 +83,10 @@ class DeviceComm:
         check(self._lib.al_dev_comm_abort(self._h, why.encode()))
 
     def stats(self) -> dict:
-        out = (C.c_uint64 * 10)()
+        out = (C.c_uint64 * 11)()
         check(self._lib.al_dev_comm_stats(self._h, out))
-        names = ["ops", "bytes", "kernels", "timeouts", "one_shot", "two_shot", "nvls", "nvls_zero_copy", "bulk_pipeline", "direct"]
+        names = ["ops", "bytes", "kernels", "timeouts", "one_shot", "two_shot", "nvls", "nvls_zero_copy", "bulk_pipeline",
+                 "window", "ll"]
         return dict(zip(names, [int(v) for v in out]))
 
     def status(self) -> dict:
@@ -168,7 +169,8 @@ class DeviceComm:
         req = C.c_void_p(None)
         check(self._lib.al_dev_collective(
             self._h, KINDS[kind], self.nlocal, self._ptrs(sends), self._ptrs(recvs), int(count), dt_in, dt_wire, dt_out,
-            OPS[op], int(root), 1 if inplace else 0, 1 if tables else 0, sc, sd, rc, rd, float(scale), ALGOS[algo],
+            OPS[op], int(root), 1 if inplace else 0, 1 if tables else 0, sc, sd, rc, rd, float(scale),
+            ALGOS[algo] if kind == "allreduce" else PATHS[algo],
             int(ctas), self._stream(stream), C.byref(req) if nonblocking else None))
         return Request(req, True, (sends, recvs)) if nonblocking else None
 
@@ -271,6 +273,28 @@ class DeviceComm:
     def sendrecv(self, send, dest, recv, src, **kw):
         return self.p2p([(True, dest, send), (False, src, recv)], **kw)
 
+    # ---- registered buffers -----------------------------------------------------------------------
+    def register(self, tensor) -> int:
+        """Collective (every rank, same order, each with its own tensor): make the tensor's memory addressable by
+        all ranks, so that reduce_scatter (as input) and allgather / alltoall / bcast (as output) on it skip the
+        staging area.  In emulation pass the list of all ranks' tensors.  Returns the window index, or -1 when the
+        memory cannot be shared (the tensor then simply keeps using the staged path).  Tensors from
+        :meth:`symm_empty` are registered already."""
+        if self.emulated:
+            ts = list(tensor)
+            arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+            w = self._lib.al_dev_register_emulated(self._h, arr, len(ts), ts[0].numel() * ts[0].element_size())
+        else:
+            w = self._lib.al_dev_register(self._h, C.c_void_p(tensor.data_ptr()), tensor.numel() * tensor.element_size())
+        if w == -2:
+            check(1)
+        return int(w)
+
+    def unregister(self, tensor) -> None:
+        """Collective: forget a registered tensor (before its memory is freed)."""
+        t = tensor[0] if isinstance(tensor, (list, tuple)) else tensor
+        check(self._lib.al_dev_unregister(self._h, C.c_void_p(t.data_ptr())))
+
     # ---- symmetric memory ------------------------------------------------------------------------
     def symm_empty(self, shape, dtype):
         """Collective: a tensor in symmetric (peer-mapped, multicast-bound when possible) memory.
@@ -329,6 +353,11 @@ class DeviceComm:
     def put(self, src, dest: int, remote_addr: int) -> None:
         check(self._lib.al_rma_put(self._h, C.c_void_p(src.data_ptr()), int(dest), C.c_void_p(remote_addr),
                                    src.numel() * src.element_size()))
+
+    def get(self, dst, src_rank: int, remote_addr: int) -> None:
+        """Fill ``dst`` from the buffer at ``remote_addr`` (an :meth:`attach` result for ``src_rank``), stream-ordered."""
+        check(self._lib.al_rma_get(self._h, C.c_void_p(dst.data_ptr()), int(src_rank), C.c_void_p(remote_addr),
+                                   dst.numel() * dst.element_size()))
 
     def notify(self, peer: int) -> None:
         check(self._lib.al_rma_notify(self._h, int(peer)))

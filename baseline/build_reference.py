@@ -91,6 +91,20 @@ def build_driver(prefix: Path, mpi: Path) -> Path:
     return so
 
 
+def driver_is_stale() -> bool:
+    so = REF_OUT / "lib" / "libref_driver.so"
+    return (not so.exists()) or so.stat().st_mtime < (HERE / "ref_driver.cpp").stat().st_mtime
+
+
+def rebuild_driver_only() -> Path:
+    """Recompile libref_driver.so against an already installed reference (no reference sources needed)."""
+    prefix = REF_OUT / "install"
+    mpi = REF_OUT / "mpi"
+    if not (prefix / "include" / "Al.hpp").exists() or not (mpi / "lib" / "libmpi.so").exists():
+        raise RuntimeError("the reference is not installed under baseline/_ref: run baseline/build_reference.py")
+    return build_driver(prefix, mpi)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("AL_REFERENCE_SRC", "/root/reference"))

@@ -24,6 +24,24 @@ OPS = {"sum": 0, "prod": 1, "min": 2, "max": 3, "avg": 4}
 
 def unavailable_reason() -> str | None:
     """None when the reference arm can run; otherwise one line saying why not."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("al_build_reference", HERE / "build_reference.py")
+    br = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(br)
+    if br.driver_is_stale():
+        # Only rank 0 of a node rebuilds; the others wait for the file.
+        if int(os.environ.get("LOCAL_RANK", "0")) == 0:
+            try:
+                br.rebuild_driver_only()
+            except Exception as e:  # noqa: BLE001
+                return (f"{DRIVER.relative_to(HERE.parent)} is missing or older than baseline/ref_driver.cpp and could "
+                        f"not be rebuilt ({str(e).splitlines()[-1][:200]}): run `python baseline/build_reference.py`")
+        else:
+            import time
+            for _ in range(600):
+                if not br.driver_is_stale():
+                    break
+                time.sleep(0.1)
     if not DRIVER.exists():
         return (f"{DRIVER.relative_to(HERE.parent)} is missing: run `python baseline/build_reference.py` "
                 "(builds the MPI stand-in, the unmodified reference with its NCCL backend and the C driver)")

@@ -391,44 +391,62 @@ static void test_bulk_tile_plans() {
           for (int q = 0; q < p; ++q)
             CHECK(memcmp(&recv[(size_t)r][(size_t)q * slice], &send[(size_t)q][(size_t)r * slice], slice) == 0);
       }
-      // ---- direct allgather / alltoall: straight into the receive buffers ----------------------------------
-      {
-        const unsigned nct = 1 + rng() % 7;
-        std::vector<Bytes> s1((size_t)p, Bytes(slice)), sp((size_t)p, Bytes(slice * (size_t)p));
-        std::vector<Bytes> r1((size_t)p, Bytes(slice * (size_t)p, 0)), r2((size_t)p, Bytes(slice * (size_t)p, 0));
-        std::vector<std::vector<int>> hits((size_t)p, std::vector<int>(slice * (size_t)p, 0));
-        for (int r = 0; r < p; ++r) { fill(s1[(size_t)r], r + 80); fill(sp[(size_t)r], r + 120); }
-        for (int r = 0; r < p; ++r)
-          for (unsigned cta = 0; cta < nct; ++cta) {
-            const Share sh = share_of(slice, slice, 0, cta, nct, tile);
-            for (size_t k = 0; k < sh.tiles; ++k) {
-              const Move m = ag_direct(sh, k, r, slice, tile);
-              CHECK(ok16(m) && m.src + m.bytes <= slice && m.dst + m.bytes <= slice * (size_t)p);
-              for (int d = 0; d < p; ++d) memcpy(&r1[(size_t)d][m.dst], &s1[(size_t)r][m.src], m.bytes);
-            }
-            for (size_t t = 0; t < fan_tiles(sh, p); ++t) {
-              const Move m = a2a_direct(sh, t, r, p, slice, tile);
-              CHECK(ok16(m) && m.peer >= 0 && m.peer < p);
-              memcpy(&r2[(size_t)m.peer][m.dst], &sp[(size_t)r][m.src], m.bytes);
-              for (size_t i = 0; i < m.bytes; ++i) hits[(size_t)m.peer][m.dst + i]++;
-            }
-          }
-        for (int r = 0; r < p; ++r) {
-          bool once = true;
-          for (int h : hits[(size_t)r]) once = once && h == 1;
-          CHECK(once);
-          for (int q = 0; q < p; ++q) {
-            CHECK(memcmp(&r1[(size_t)r][(size_t)q * slice], s1[(size_t)q].data(), slice) == 0);
-            CHECK(memcmp(&r2[(size_t)r][(size_t)q * slice], &sp[(size_t)q][(size_t)r * slice], slice) == 0);
-          }
-        }
-      }
     }
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// "Last CTA posts" arrival counters of the device kernels, modelled on the host.
+//
+// A group of G CTAs runs R rounds; in each round a CTA does its share and then arrives; the CTA whose
+// arrival completes the round's count posts the round's flag.  The schedules of the library only gate
+// round k+2 on the post of round k (the gate goes through the peers), so a fast CTA can arrive for round
+// k+1 before a slow sibling arrived for round k.  The kernels count arrivals in two counters chosen by
+// the round's parity, each wrapping at G (kernels/common.cuh, arrive_and_post): every round must be posted
+// exactly once, by its last arrival, whatever the interleaving.  A single wrapping counter is shown to
+// fail under the same schedules, which is why the parity matters.
+// ---------------------------------------------------------------------------------------------------
+static void test_arrival_counters() {
+  std::mt19937 rng(4711);
+  int single_counter_failures = 0;
+  for (int trial = 0; trial < 400; ++trial) {
+    const int G = 2 + (int)(rng() % 7), R = 3 + (int)(rng() % 10);
+    for (int mode = 0; mode < 2; ++mode) {  // 0: parity counters (the library), 1: one counter (the old scheme)
+      std::vector<int> next((size_t)G, 0);          // round each CTA arrives for next
+      std::vector<int> arrived((size_t)R, 0), posted((size_t)R, 0);
+      unsigned ctr[2] = {0, 0};
+      bool ok = true;
+      int done = 0;
+      while (done < G) {
+        // pick a CTA that may proceed: round k needs the post of round k-2
+        std::vector<int> ready;
+        for (int c = 0; c < G; ++c)
+          if (next[(size_t)c] < R && (next[(size_t)c] < 2 || posted[(size_t)next[(size_t)c] - 2])) ready.push_back(c);
+        if (ready.empty()) { ok = false; break; }  // nobody can move: a round was never posted
+        // skew: prefer the lowest-numbered CTAs most of the time so that some run ahead
+        const int c = ready[(rng() % 4) ? 0 : rng() % ready.size()];
+        const int k = next[(size_t)c]++;
+        arrived[(size_t)k]++;
+        unsigned& n = ctr[mode == 0 ? (k & 1) : 0];
+        const bool last = n == (unsigned)G - 1;
+        n = last ? 0 : n + 1;                       // atomicInc(ctr, G - 1)
+        if (last) {
+          if (arrived[(size_t)k] != G || posted[(size_t)k]) ok = false;  // posted early, or twice
+          posted[(size_t)k] = 1;
+        }
+        if (next[(size_t)c] == R) ++done;
+      }
+      for (int k = 0; k < R; ++k) ok = ok && posted[(size_t)k] == 1;
+      if (mode == 0) CHECK(ok);
+      else if (!ok) ++single_counter_failures;
+    }
+  }
+  CHECK(single_counter_failures > 0);  // the schedules really do exercise the hazard
+}
+
 int main() {
   test_meta();
+  test_arrival_counters();
   test_spsc();
   test_mpsc();
   test_allocator();

@@ -34,6 +34,17 @@
 
 namespace Al {
 
+// Algorithm enum of an operation on a backend (include/aluminum/traits/traits_base.hpp:186-214 of the reference).
+template <AlOperation Op> struct OpAlgoType<Op, HostBackend> { using type = HostAlgo; };
+#ifdef AL_HAS_CUDA
+template <AlOperation Op> struct OpAlgoType<Op, HostTransferBackend> { using type = HostAlgo; };
+template <AlOperation Op> struct OpAlgoType<Op, DeviceBackend> { using type = DeviceAlgo; };
+template <> struct OpAlgoType<AlOperation::allreduce, DeviceBackend> { using type = DeviceAllreduceAlgo; };
+static_assert(std::is_same<OpAlgoType<AlOperation::allgather, DeviceBackend>::type, DeviceBackend::allgather_algo_type>::value, "traits");
+static_assert(std::is_same<OpAlgoType<AlOperation::allreduce, DeviceBackend>::type, DeviceBackend::allreduce_algo_type>::value, "traits");
+#endif
+
+
 namespace internal {
 template <typename T>
 constexpr DType dtype_of() {
@@ -55,8 +66,12 @@ template <typename Backend, typename T>
 void Allreduce(const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
                typename Backend::allreduce_algo_type algo = Backend::allreduce_algo_type::automatic) {
   AL_API_ENTER("allreduce");
+  if (!reduction_supported(internal::dtype_of<T>(), op))
+    throw_al_exception("allreduce: operator ", reduction_name(op), " is not defined for ", dtype_name(internal::dtype_of<T>()));
   debug::check_buffer(sendbuf, count); debug::check_buffer(recvbuf, count);
-  Backend::run_allreduce(internal::resolve_uniform(internal::OpKind::allreduce, internal::dtype_of<T>(), sendbuf, recvbuf, count, op, 0, comm.rank(), comm.size()), comm, nullptr, algo);
+  internal::Resolved r = internal::resolve_uniform(internal::OpKind::allreduce, internal::dtype_of<T>(), sendbuf, recvbuf, count, op, 0, comm.rank(), comm.size());
+  debug::check_resolved(r, r.send != nullptr, r.recv != nullptr, comm.rank(), comm.size());
+  Backend::run_allreduce(std::move(r), comm, nullptr, algo);
 }
 template <typename Backend, typename T>
 void Allreduce(T* buffer, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
@@ -68,8 +83,12 @@ void NonblockingAllreduce(const T* sendbuf, T* recvbuf, size_t count, ReductionO
                           typename Backend::req_type& req,
                           typename Backend::allreduce_algo_type algo = Backend::allreduce_algo_type::automatic) {
   AL_API_ENTER("nonblocking-allreduce");
+  if (!reduction_supported(internal::dtype_of<T>(), op))
+    throw_al_exception("allreduce: operator ", reduction_name(op), " is not defined for ", dtype_name(internal::dtype_of<T>()));
   debug::check_buffer(sendbuf, count); debug::check_buffer(recvbuf, count);
-  Backend::run_allreduce(internal::resolve_uniform(internal::OpKind::allreduce, internal::dtype_of<T>(), sendbuf, recvbuf, count, op, 0, comm.rank(), comm.size()), comm, &req, algo);
+  internal::Resolved r = internal::resolve_uniform(internal::OpKind::allreduce, internal::dtype_of<T>(), sendbuf, recvbuf, count, op, 0, comm.rank(), comm.size());
+  debug::check_resolved(r, r.send != nullptr, r.recv != nullptr, comm.rank(), comm.size());
+  Backend::run_allreduce(std::move(r), comm, &req, algo);
 }
 template <typename Backend, typename T>
 void NonblockingAllreduce(T* buffer, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
@@ -83,21 +102,27 @@ namespace internal {
 /** Shared body of every uniform collective except allreduce (which carries an algorithm). */
 template <typename Backend, typename T>
 void uniform_op(const char* name, OpKind kind, const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op,
-                int root, typename Backend::comm_type& comm, typename Backend::req_type* req) {
+                int root, typename Backend::comm_type& comm, typename Backend::req_type* req, int algo = 0) {
   AL_API_SCOPE(name);
   api_enter<Backend, T>(name, comm);
   debug::check_rank(root, comm.size());
-  Backend::run(resolve_uniform(kind, dtype_of<T>(), sendbuf, recvbuf, count, op, root, comm.rank(), comm.size()), comm, req);
+  if ((kind == OpKind::reduce || kind == OpKind::reduce_scatter) && !reduction_supported(dtype_of<T>(), op))
+    throw_al_exception(name, ": operator ", reduction_name(op), " is not defined for ", dtype_name(dtype_of<T>()));
+  Resolved r = resolve_uniform(kind, dtype_of<T>(), sendbuf, recvbuf, count, op, root, comm.rank(), comm.size());
+  debug::check_resolved(r, r.send != nullptr, r.recv != nullptr, comm.rank(), comm.size());
+  Backend::run(std::move(r), comm, req, algo);
 }
 template <typename Backend, typename T>
 void vector_op(const char* name, OpKind kind, const T* sendbuf, T* recvbuf, std::vector<size_t> sc,
                std::vector<size_t> sd, std::vector<size_t> rc, std::vector<size_t> rd, ReductionOperator op, int root,
-               typename Backend::comm_type& comm, typename Backend::req_type* req) {
+               typename Backend::comm_type& comm, typename Backend::req_type* req, int algo = 0) {
   AL_API_SCOPE(name);
   api_enter<Backend, T>(name, comm);
   debug::check_rank(root, comm.size());
-  Backend::run(resolve_vector(kind, dtype_of<T>(), sendbuf, recvbuf, std::move(sc), std::move(sd), std::move(rc),
-                              std::move(rd), op, root, comm.rank(), comm.size()), comm, req);
+  Resolved r = resolve_vector(kind, dtype_of<T>(), sendbuf, recvbuf, std::move(sc), std::move(sd), std::move(rc),
+                              std::move(rd), op, root, comm.rank(), comm.size());
+  debug::check_resolved(r, r.send != nullptr, r.recv != nullptr, comm.rank(), comm.size());
+  Backend::run(std::move(r), comm, req, algo);
 }
 }  // namespace internal
 
@@ -106,50 +131,50 @@ void vector_op(const char* name, OpKind kind, const T* sendbuf, T* recvbuf, std:
 // ============================ Reduce =========================================
 template <typename Backend, typename T>
 void Reduce(const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op, int root, typename Backend::comm_type& comm,
-            typename Backend::reduce_algo_type = Backend::reduce_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("reduce", internal::OpKind::reduce, sendbuf, recvbuf, count, op, root, comm, nullptr);
+            typename Backend::reduce_algo_type algo = Backend::reduce_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("reduce", internal::OpKind::reduce, sendbuf, recvbuf, count, op, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Reduce(T* buffer, size_t count, ReductionOperator op, int root, typename Backend::comm_type& comm,
-            typename Backend::reduce_algo_type = Backend::reduce_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("reduce", internal::OpKind::reduce, internal::IN_PLACE<T>(), buffer, count, op, root, comm, nullptr);
+            typename Backend::reduce_algo_type algo = Backend::reduce_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("reduce", internal::OpKind::reduce, internal::IN_PLACE<T>(), buffer, count, op, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingReduce(const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op, int root,
                        typename Backend::comm_type& comm, typename Backend::req_type& req,
-                       typename Backend::reduce_algo_type = Backend::reduce_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-reduce", internal::OpKind::reduce, sendbuf, recvbuf, count, op, root, comm, &req);
+                       typename Backend::reduce_algo_type algo = Backend::reduce_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-reduce", internal::OpKind::reduce, sendbuf, recvbuf, count, op, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingReduce(T* buffer, size_t count, ReductionOperator op, int root, typename Backend::comm_type& comm,
                        typename Backend::req_type& req,
-                       typename Backend::reduce_algo_type = Backend::reduce_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-reduce", internal::OpKind::reduce, internal::IN_PLACE<T>(), buffer, count, op, root, comm, &req);
+                       typename Backend::reduce_algo_type algo = Backend::reduce_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-reduce", internal::OpKind::reduce, internal::IN_PLACE<T>(), buffer, count, op, root, comm, &req, (int)algo);
 }
 
 // ============================ Reduce_scatter ==================================
 /** `count` is the length each rank receives; the send buffer holds count * size elements. */
 template <typename Backend, typename T>
 void Reduce_scatter(const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
-                    typename Backend::reduce_scatter_algo_type = Backend::reduce_scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("reduce_scatter", internal::OpKind::reduce_scatter, sendbuf, recvbuf, count, op, 0, comm, nullptr);
+                    typename Backend::reduce_scatter_algo_type algo = Backend::reduce_scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("reduce_scatter", internal::OpKind::reduce_scatter, sendbuf, recvbuf, count, op, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Reduce_scatter(T* buffer, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
-                    typename Backend::reduce_scatter_algo_type = Backend::reduce_scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("reduce_scatter", internal::OpKind::reduce_scatter, internal::IN_PLACE<T>(), buffer, count, op, 0, comm, nullptr);
+                    typename Backend::reduce_scatter_algo_type algo = Backend::reduce_scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("reduce_scatter", internal::OpKind::reduce_scatter, internal::IN_PLACE<T>(), buffer, count, op, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingReduce_scatter(const T* sendbuf, T* recvbuf, size_t count, ReductionOperator op,
                                typename Backend::comm_type& comm, typename Backend::req_type& req,
-                               typename Backend::reduce_scatter_algo_type = Backend::reduce_scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-reduce_scatter", internal::OpKind::reduce_scatter, sendbuf, recvbuf, count, op, 0, comm, &req);
+                               typename Backend::reduce_scatter_algo_type algo = Backend::reduce_scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-reduce_scatter", internal::OpKind::reduce_scatter, sendbuf, recvbuf, count, op, 0, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingReduce_scatter(T* buffer, size_t count, ReductionOperator op, typename Backend::comm_type& comm,
                                typename Backend::req_type& req,
-                               typename Backend::reduce_scatter_algo_type = Backend::reduce_scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-reduce_scatter", internal::OpKind::reduce_scatter, internal::IN_PLACE<T>(), buffer, count, op, 0, comm, &req);
+                               typename Backend::reduce_scatter_algo_type algo = Backend::reduce_scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-reduce_scatter", internal::OpKind::reduce_scatter, internal::IN_PLACE<T>(), buffer, count, op, 0, comm, &req, (int)algo);
 }
 
 // ============================ Reduce_scatterv =================================
@@ -185,49 +210,49 @@ void NonblockingReduce_scatterv(T* buffer, std::vector<size_t> counts, Reduction
 /** `count` is each rank's contribution; the receive buffer holds count * size elements. */
 template <typename Backend, typename T>
 void Allgather(const T* sendbuf, T* recvbuf, size_t count, typename Backend::comm_type& comm,
-               typename Backend::allgather_algo_type = Backend::allgather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("allgather", internal::OpKind::allgather, sendbuf, recvbuf, count, AL_SUM, 0, comm, nullptr);
+               typename Backend::allgather_algo_type algo = Backend::allgather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("allgather", internal::OpKind::allgather, sendbuf, recvbuf, count, AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Allgather(T* buffer, size_t count, typename Backend::comm_type& comm,
-               typename Backend::allgather_algo_type = Backend::allgather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("allgather", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, nullptr);
+               typename Backend::allgather_algo_type algo = Backend::allgather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("allgather", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAllgather(const T* sendbuf, T* recvbuf, size_t count, typename Backend::comm_type& comm,
                           typename Backend::req_type& req,
-                          typename Backend::allgather_algo_type = Backend::allgather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-allgather", internal::OpKind::allgather, sendbuf, recvbuf, count, AL_SUM, 0, comm, &req);
+                          typename Backend::allgather_algo_type algo = Backend::allgather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-allgather", internal::OpKind::allgather, sendbuf, recvbuf, count, AL_SUM, 0, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAllgather(T* buffer, size_t count, typename Backend::comm_type& comm, typename Backend::req_type& req,
-                          typename Backend::allgather_algo_type = Backend::allgather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-allgather", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, &req);
+                          typename Backend::allgather_algo_type algo = Backend::allgather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-allgather", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, &req, (int)algo);
 }
 
 // ============================ Allgatherv ======================================
 template <typename Backend, typename T>
 void Allgatherv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs,
                 typename Backend::comm_type& comm,
-                typename Backend::allgatherv_algo_type = Backend::allgatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("allgatherv", internal::OpKind::allgather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr);
+                typename Backend::allgatherv_algo_type algo = Backend::allgatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("allgatherv", internal::OpKind::allgather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Allgatherv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, typename Backend::comm_type& comm,
-                typename Backend::allgatherv_algo_type = Backend::allgatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("allgatherv", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr);
+                typename Backend::allgatherv_algo_type algo = Backend::allgatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("allgatherv", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAllgatherv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs,
                            typename Backend::comm_type& comm, typename Backend::req_type& req,
-                           typename Backend::allgatherv_algo_type = Backend::allgatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-allgatherv", internal::OpKind::allgather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req);
+                           typename Backend::allgatherv_algo_type algo = Backend::allgatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-allgatherv", internal::OpKind::allgather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAllgatherv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs,
                            typename Backend::comm_type& comm, typename Backend::req_type& req,
-                           typename Backend::allgatherv_algo_type = Backend::allgatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-allgatherv", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req);
+                           typename Backend::allgatherv_algo_type algo = Backend::allgatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-allgatherv", internal::OpKind::allgather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req, (int)algo);
 }
 
 // ============================ Barrier =========================================
@@ -252,160 +277,160 @@ void NonblockingBarrier(typename Backend::comm_type& comm, typename Backend::req
 // ============================ Bcast ===========================================
 template <typename Backend, typename T>
 void Bcast(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
-           typename Backend::bcast_algo_type = Backend::bcast_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("bcast", internal::OpKind::bcast, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr);
+           typename Backend::bcast_algo_type algo = Backend::bcast_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("bcast", internal::OpKind::bcast, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingBcast(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
                       typename Backend::req_type& req,
-                      typename Backend::bcast_algo_type = Backend::bcast_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-bcast", internal::OpKind::bcast, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req);
+                      typename Backend::bcast_algo_type algo = Backend::bcast_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-bcast", internal::OpKind::bcast, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req, (int)algo);
 }
 
 // ============================ Alltoall ========================================
 /** `count` is the length of the slice exchanged with each peer. */
 template <typename Backend, typename T>
 void Alltoall(const T* sendbuf, T* recvbuf, size_t count, typename Backend::comm_type& comm,
-              typename Backend::alltoall_algo_type = Backend::alltoall_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("alltoall", internal::OpKind::alltoall, sendbuf, recvbuf, count, AL_SUM, 0, comm, nullptr);
+              typename Backend::alltoall_algo_type algo = Backend::alltoall_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("alltoall", internal::OpKind::alltoall, sendbuf, recvbuf, count, AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Alltoall(T* buffer, size_t count, typename Backend::comm_type& comm,
-              typename Backend::alltoall_algo_type = Backend::alltoall_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("alltoall", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, nullptr);
+              typename Backend::alltoall_algo_type algo = Backend::alltoall_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("alltoall", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAlltoall(const T* sendbuf, T* recvbuf, size_t count, typename Backend::comm_type& comm,
                          typename Backend::req_type& req,
-                         typename Backend::alltoall_algo_type = Backend::alltoall_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-alltoall", internal::OpKind::alltoall, sendbuf, recvbuf, count, AL_SUM, 0, comm, &req);
+                         typename Backend::alltoall_algo_type algo = Backend::alltoall_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-alltoall", internal::OpKind::alltoall, sendbuf, recvbuf, count, AL_SUM, 0, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAlltoall(T* buffer, size_t count, typename Backend::comm_type& comm, typename Backend::req_type& req,
-                         typename Backend::alltoall_algo_type = Backend::alltoall_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-alltoall", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, &req);
+                         typename Backend::alltoall_algo_type algo = Backend::alltoall_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-alltoall", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, count, AL_SUM, 0, comm, &req, (int)algo);
 }
 
 // ============================ Alltoallv =======================================
 template <typename Backend, typename T>
 void Alltoallv(const T* sendbuf, std::vector<size_t> send_counts, std::vector<size_t> send_displs, T* recvbuf,
                std::vector<size_t> recv_counts, std::vector<size_t> recv_displs, typename Backend::comm_type& comm,
-               typename Backend::alltoallv_algo_type = Backend::alltoallv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("alltoallv", internal::OpKind::alltoall, sendbuf, recvbuf, std::move(send_counts), std::move(send_displs), std::move(recv_counts), std::move(recv_displs), AL_SUM, 0, comm, nullptr);
+               typename Backend::alltoallv_algo_type algo = Backend::alltoallv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("alltoallv", internal::OpKind::alltoall, sendbuf, recvbuf, std::move(send_counts), std::move(send_displs), std::move(recv_counts), std::move(recv_displs), AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Alltoallv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, typename Backend::comm_type& comm,
-               typename Backend::alltoallv_algo_type = Backend::alltoallv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("alltoallv", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr);
+               typename Backend::alltoallv_algo_type algo = Backend::alltoallv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("alltoallv", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAlltoallv(const T* sendbuf, std::vector<size_t> send_counts, std::vector<size_t> send_displs,
                           T* recvbuf, std::vector<size_t> recv_counts, std::vector<size_t> recv_displs,
                           typename Backend::comm_type& comm, typename Backend::req_type& req,
-                          typename Backend::alltoallv_algo_type = Backend::alltoallv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-alltoallv", internal::OpKind::alltoall, sendbuf, recvbuf, std::move(send_counts), std::move(send_displs), std::move(recv_counts), std::move(recv_displs), AL_SUM, 0, comm, &req);
+                          typename Backend::alltoallv_algo_type algo = Backend::alltoallv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-alltoallv", internal::OpKind::alltoall, sendbuf, recvbuf, std::move(send_counts), std::move(send_displs), std::move(recv_counts), std::move(recv_displs), AL_SUM, 0, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingAlltoallv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs,
                           typename Backend::comm_type& comm, typename Backend::req_type& req,
-                          typename Backend::alltoallv_algo_type = Backend::alltoallv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-alltoallv", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req);
+                          typename Backend::alltoallv_algo_type algo = Backend::alltoallv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-alltoallv", internal::OpKind::alltoall, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, 0, comm, &req, (int)algo);
 }
 
 // ============================ Gather / Gatherv ================================
 template <typename Backend, typename T>
 void Gather(const T* sendbuf, T* recvbuf, size_t count, int root, typename Backend::comm_type& comm,
-            typename Backend::gather_algo_type = Backend::gather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("gather", internal::OpKind::gather, sendbuf, recvbuf, count, AL_SUM, root, comm, nullptr);
+            typename Backend::gather_algo_type algo = Backend::gather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("gather", internal::OpKind::gather, sendbuf, recvbuf, count, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Gather(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
-            typename Backend::gather_algo_type = Backend::gather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("gather", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr);
+            typename Backend::gather_algo_type algo = Backend::gather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("gather", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingGather(const T* sendbuf, T* recvbuf, size_t count, int root, typename Backend::comm_type& comm,
                        typename Backend::req_type& req,
-                       typename Backend::gather_algo_type = Backend::gather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-gather", internal::OpKind::gather, sendbuf, recvbuf, count, AL_SUM, root, comm, &req);
+                       typename Backend::gather_algo_type algo = Backend::gather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-gather", internal::OpKind::gather, sendbuf, recvbuf, count, AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingGather(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
                        typename Backend::req_type& req,
-                       typename Backend::gather_algo_type = Backend::gather_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-gather", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req);
+                       typename Backend::gather_algo_type algo = Backend::gather_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-gather", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void Gatherv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs, int root,
              typename Backend::comm_type& comm,
-             typename Backend::gatherv_algo_type = Backend::gatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("gatherv", internal::OpKind::gather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, nullptr);
+             typename Backend::gatherv_algo_type algo = Backend::gatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("gatherv", internal::OpKind::gather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Gatherv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, int root,
              typename Backend::comm_type& comm,
-             typename Backend::gatherv_algo_type = Backend::gatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("gatherv", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, nullptr);
+             typename Backend::gatherv_algo_type algo = Backend::gatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("gatherv", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingGatherv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs, int root,
                         typename Backend::comm_type& comm, typename Backend::req_type& req,
-                        typename Backend::gatherv_algo_type = Backend::gatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-gatherv", internal::OpKind::gather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, &req);
+                        typename Backend::gatherv_algo_type algo = Backend::gatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-gatherv", internal::OpKind::gather, sendbuf, recvbuf, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingGatherv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, int root,
                         typename Backend::comm_type& comm, typename Backend::req_type& req,
-                        typename Backend::gatherv_algo_type = Backend::gatherv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-gatherv", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, &req);
+                        typename Backend::gatherv_algo_type algo = Backend::gatherv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-gatherv", internal::OpKind::gather, internal::IN_PLACE<T>(), buffer, {}, {}, std::move(counts), std::move(displs), AL_SUM, root, comm, &req, (int)algo);
 }
 
 // ============================ Scatter / Scatterv ==============================
 template <typename Backend, typename T>
 void Scatter(const T* sendbuf, T* recvbuf, size_t count, int root, typename Backend::comm_type& comm,
-             typename Backend::scatter_algo_type = Backend::scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("scatter", internal::OpKind::scatter, sendbuf, recvbuf, count, AL_SUM, root, comm, nullptr);
+             typename Backend::scatter_algo_type algo = Backend::scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("scatter", internal::OpKind::scatter, sendbuf, recvbuf, count, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Scatter(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
-             typename Backend::scatter_algo_type = Backend::scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("scatter", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr);
+             typename Backend::scatter_algo_type algo = Backend::scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("scatter", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingScatter(const T* sendbuf, T* recvbuf, size_t count, int root, typename Backend::comm_type& comm,
                         typename Backend::req_type& req,
-                        typename Backend::scatter_algo_type = Backend::scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-scatter", internal::OpKind::scatter, sendbuf, recvbuf, count, AL_SUM, root, comm, &req);
+                        typename Backend::scatter_algo_type algo = Backend::scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-scatter", internal::OpKind::scatter, sendbuf, recvbuf, count, AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingScatter(T* buffer, size_t count, int root, typename Backend::comm_type& comm,
                         typename Backend::req_type& req,
-                        typename Backend::scatter_algo_type = Backend::scatter_algo_type::automatic) {
-  internal::uniform_op<Backend, T>("nonblocking-scatter", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req);
+                        typename Backend::scatter_algo_type algo = Backend::scatter_algo_type::automatic) {
+  internal::uniform_op<Backend, T>("nonblocking-scatter", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, count, AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void Scatterv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs, int root,
               typename Backend::comm_type& comm,
-              typename Backend::scatterv_algo_type = Backend::scatterv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("scatterv", internal::OpKind::scatter, sendbuf, recvbuf, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, nullptr);
+              typename Backend::scatterv_algo_type algo = Backend::scatterv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("scatterv", internal::OpKind::scatter, sendbuf, recvbuf, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void Scatterv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, int root,
               typename Backend::comm_type& comm,
-              typename Backend::scatterv_algo_type = Backend::scatterv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("scatterv", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, nullptr);
+              typename Backend::scatterv_algo_type algo = Backend::scatterv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("scatterv", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, nullptr, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingScatterv(const T* sendbuf, T* recvbuf, std::vector<size_t> counts, std::vector<size_t> displs,
                          int root, typename Backend::comm_type& comm, typename Backend::req_type& req,
-                         typename Backend::scatterv_algo_type = Backend::scatterv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-scatterv", internal::OpKind::scatter, sendbuf, recvbuf, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, &req);
+                         typename Backend::scatterv_algo_type algo = Backend::scatterv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-scatterv", internal::OpKind::scatter, sendbuf, recvbuf, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, &req, (int)algo);
 }
 template <typename Backend, typename T>
 void NonblockingScatterv(T* buffer, std::vector<size_t> counts, std::vector<size_t> displs, int root,
                          typename Backend::comm_type& comm, typename Backend::req_type& req,
-                         typename Backend::scatterv_algo_type = Backend::scatterv_algo_type::automatic) {
-  internal::vector_op<Backend, T>("nonblocking-scatterv", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, &req);
+                         typename Backend::scatterv_algo_type algo = Backend::scatterv_algo_type::automatic) {
+  internal::vector_op<Backend, T>("nonblocking-scatterv", internal::OpKind::scatter, internal::IN_PLACE<T>(), buffer, std::move(counts), std::move(displs), {}, {}, AL_SUM, root, comm, &req, (int)algo);
 }
 
 // ============================ point-to-point ==================================

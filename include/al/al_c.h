@@ -94,19 +94,31 @@ const char* al_dev_comm_backing(void* comm);
 int al_dev_comm_set_timeout_ms(void* comm, double ms);
 /** Every later call on the communicator fails (why may be NULL). */
 int al_dev_comm_abort(void* comm, const char* why);
-/** Fills out[0..9]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, direct. */
+/** Fills out[0..10]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, window, ll. */
 int al_dev_comm_stats(void* comm, uint64_t* out);
 /** Status record: out[0]=code, [1]=rank, [2]=peer, [3]=where, [4]=epoch, [5]=seen. Never fails. */
 int al_dev_comm_status(void* comm, uint64_t* out);
 /**
  * nlocal entries in send / recv (1 outside emulation).  Count tables, when
  * vector != 0, hold nlocal * size entries each (row per local rank).
- * dt_wire / dt_out < 0 mean "same as dt_in".  algo: 0 auto, 1 one-shot, 2 two-shot, 3 NVLS.
+ * dt_wire / dt_out < 0 mean "same as dt_in".  algo, for allreduce: 0 auto, 1 one-shot, 2 two-shot,
+ * 3 NVLS, 4 low-latency packets; for every other collective it selects the data path: 0 auto, 1 staged,
+ * 2 window (registered buffers), 3 low-latency packets.
  */
 int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send, void* const* recv, size_t count,
                       int dt_in, int dt_wire, int dt_out, int op, int root, int inplace, int vector,
                       const size_t* send_counts, const size_t* send_displs, const size_t* recv_counts,
                       const size_t* recv_displs, double scale, int algo, int ctas, void* stream, void** req_out);
+/**
+ * Collective over the communicator: make [ptr, ptr+bytes) of every rank addressable by all ranks (CUDA IPC for
+ * cudaMalloc memory; symm_alloc memory is registered already).  Returns the window index (>= 0), -1 when some
+ * rank's memory cannot be shared (nobody registers then; the buffer keeps using the staging path), -2 on error.
+ */
+int al_dev_register(void* comm, void* ptr, size_t bytes);
+/** Emulated communicators: the n = size buffers of all ranks at once. */
+int al_dev_register_emulated(void* comm, void* const* ptrs, int n, size_t bytes);
+/** Collective: forget a registered buffer; call it before the memory is freed. */
+int al_dev_unregister(void* comm, void* ptr);
 /**
  * Benchmark helper: `warmup` untimed then `iters` timed out-of-place calls of one collective, each
  * preceded by a host barrier of the communicator's ranks and bracketed by a CUDA event pair on
@@ -129,6 +141,8 @@ void* al_dev_symm_peer_ptr(void* comm, void* local_ptr, int peer);
 void* al_rma_attach(void* comm, void* local_buf, int peer);
 int al_rma_detach(void* comm, void* remote_buf, int peer);
 int al_rma_put(void* comm, const void* src, int dest, void* dest_remote, size_t bytes);
+/** Copy `bytes` out of `src_remote` (from al_rma_attach for rank src_rank) into local `dst`, stream-ordered. */
+int al_rma_get(void* comm, void* dst, int src_rank, const void* src_remote, size_t bytes);
 int al_rma_notify(void* comm, int peer);
 int al_rma_wait(void* comm, int peer);
 int al_rma_sync(void* comm, int peer);

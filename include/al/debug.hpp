@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "al/base.hpp"
+#include "al/resolve.hpp"
 #include "al/tuning.hpp"
 
 namespace Al {
@@ -36,6 +37,37 @@ template <typename T>
 void check_overlap(const T* a, size_t na, const T* b, size_t nb) {
   if (!on() || !a || !b || internal::is_in_place(a)) return;
   if (a < b + nb && b < a + na) throw_al_exception("send and receive buffers overlap");
+}
+/**
+ * Checks of one resolved collective, whatever the operation: a buffer that the operation reads or
+ * writes on this rank must not be null (on rooted operations only the significant side is looked
+ * at: the root's receive buffer of a gather, a non-root's send buffer of a reduce, ...), and the
+ * out-of-place forms must not be given overlapping send and receive ranges.
+ */
+inline void check_resolved(const internal::Resolved& r, bool send_given, bool recv_given, int rank, int size) {
+  if (!on()) return;
+  if (r.root < 0 || r.root >= size) throw_al_exception("root ", r.root, " out of range for a communicator of ", size);
+  // what the operation needs on this rank, from the counts alone (extent_of answers 0 for a null pointer)
+  internal::Resolved probe = r;
+  probe.send = probe.send ? probe.send : (const void*)1;
+  probe.recv = probe.recv ? probe.recv : (void*)1;
+  const internal::Extent need = internal::extent_of(probe, rank, size);
+  const bool reads = r.kind != internal::OpKind::barrier && !(r.kind == internal::OpKind::scatter && rank != r.root) &&
+                     !(r.kind == internal::OpKind::bcast && rank != r.root);
+  const bool writes = r.kind != internal::OpKind::barrier && !((r.kind == internal::OpKind::reduce || r.kind == internal::OpKind::gather) && rank != r.root) &&
+                      !(r.kind == internal::OpKind::bcast && rank == r.root) &&
+                      !(r.kind == internal::OpKind::scatter && rank == r.root && r.in_place);
+  if (reads && need.send_elems > 0 && !send_given)
+    throw_al_exception(internal::op_kind_name(r.kind), ": null send buffer with ", need.send_elems, " elements to send on rank ", rank);
+  if (writes && need.recv_elems > 0 && !recv_given)
+    throw_al_exception(internal::op_kind_name(r.kind), ": null receive buffer with ", need.recv_elems, " elements to receive on rank ", rank);
+  if (!r.in_place && r.send && r.recv && need.send_elems && need.recv_elems) {
+    const size_t esz = dtype_size(r.dt);
+    const char* a = (const char*)r.send;
+    const char* b = (const char*)r.recv;
+    if (a < b + need.recv_elems * esz && b < a + need.send_elems * esz)
+      throw_al_exception(internal::op_kind_name(r.kind), ": send and receive buffers overlap (use the in-place form)");
+  }
 }
 inline void check_rank(int rank, int size) {
   if (!on()) return;

@@ -32,7 +32,20 @@ namespace internal {
 namespace device {
 
 /** Algorithm selector of the device allreduce (the reference's `algo` argument, made real). */
-enum class AllreduceAlgo : int { automatic = 0, one_shot, two_shot, nvls };
+enum class AllreduceAlgo : int { automatic = 0, one_shot, two_shot, nvls, ll };
+
+/**
+ * Data path of the other collectives (their `algo` argument):
+ *   staged     through the communicator's staging area (any buffer; large uniform messages are
+ *              pipelined, optionally by the bulk-copy engine - see the tuning table);
+ *   window     reduce_scatter / allgather / alltoall / bcast straight on registered buffers
+ *              (RegisterMemory or symm_alloc); an error if this rank's buffer is not registered.
+ *   ll         small reduce_scatter / allgather / alltoall as low-latency packets (kernels/ll.cu);
+ *              an error if the message does not fit (kLLPayloadBytes from one rank to another).
+ * `automatic` takes packets up to tuning().ll_max_bytes, the window path for registered buffers from
+ * tuning().window_min_bytes on, staging otherwise.  AllreduceAlgo::ll is the same for allreduce.
+ */
+enum class CollPath : int { automatic = 0, staged, window, ll };
 
 /** Arguments of one collective for one local rank. */
 struct RankArgs {
@@ -50,6 +63,7 @@ struct CollDesc {
   bool vector = false;
   double scale = 1.0;     ///< extra factor applied to reduction results (on top of 1/p for avg)
   AllreduceAlgo algo = AllreduceAlgo::automatic;
+  CollPath path = CollPath::automatic;
   int ctas = 0;           ///< 0 = choose from the tuning table
 };
 
@@ -67,7 +81,8 @@ struct CommStats {
   uint64_t ops = 0, bytes = 0, kernels = 0, timeouts = 0;
   uint64_t ar_one_shot = 0, ar_two_shot = 0, ar_nvls = 0, ar_nvls_zero_copy = 0;
   uint64_t bulk_pipeline = 0;   ///< operations run by the bulk-copy pipeline kernel
-  uint64_t direct = 0;          ///< allgather / alltoall stored straight into symmetric receive buffers
+  uint64_t window = 0;          ///< operations that ran straight on registered buffers (window kernels)
+  uint64_t ll = 0;              ///< operations that ran as low-latency packets
 };
 
 }  // namespace device
@@ -114,6 +129,22 @@ class DeviceCommunicator {
   /** Collective allocation of symmetric memory (multicast-bound when possible). Returns this rank's pointer. */
   void* symm_alloc(size_t bytes);
   void symm_free(void* ptr);
+  /**
+   * Make a device buffer addressable by every rank of the communicator, so that reduce_scatter (as send
+   * buffer) and allgather / alltoall / bcast (as receive buffer) run on it without staging.  Collective:
+   * every rank calls it, in the same order, each with its own buffer (sizes may differ).  Memory from
+   * cudaMalloc is shared through CUDA IPC handles; memory from symm_alloc() is already shared (and is
+   * registered automatically when it is allocated).  Returns the window index, or -1 when some rank's
+   * memory could not be shared (then no rank registers it and the buffer keeps using the staging path).
+   * Role: ncclCommRegister behind Al::RegisterMemory (src/nccl_impl.cpp:83-109 of the reference).
+   */
+  int register_buffer(void* ptr, size_t bytes);
+  /** Collective: forget a registered buffer (must be called before the memory is freed). */
+  void unregister_buffer(void* ptr);
+  /** Emulation: the buffers of all ranks at once (one process, one device). */
+  int register_buffers_emulated(const std::vector<void*>& ptrs, size_t bytes);
+  /** Window containing [ptr, ptr+bytes) of local rank `local_rank`, or -1; *offset = distance from its start. */
+  int find_window(const void* ptr, size_t bytes, size_t* offset, int local_rank = 0) const;
   /** The symmetric block containing `ptr`, or nullptr. */
   const internal::device::SymmBlock* find_symm(const void* ptr, size_t bytes, size_t* offset) const;
 
@@ -137,6 +168,13 @@ class DeviceCommunicator {
   internal::device::CommStats stats() const;
   /** Bound of device-side waits for subsequent launches (milliseconds). */
   void set_wait_timeout_ms(double ms);
+  /**
+   * Latency breakdown: with `on`, the small-message kernels of this communicator record %globaltimer at
+   * entry / data sent / first data seen / exit into four device words; read_stamps() synchronises the
+   * device and returns them (nanoseconds).  Off by default: the kernels then only test a null pointer.
+   */
+  void enable_stamps(bool on);
+  void read_stamps(uint64_t out[4]) const;
   /** Workspace description (used by RMA and halo code). */
   const internal::device::Workspace& workspace() const;
   uint64_t next_halo_epoch();

@@ -42,15 +42,23 @@ bool collective_supported(DType in, DType wire, DType out, ReductionOperator op)
 bool bulk_pipeline_supported(DevColl kind, DType dt, ReductionOperator op);
 void launch_bulk_pipeline(const CollParams& P, DType dt, int ctas, int threads, int local_ranks, cudaStream_t stream);
 
-// ---- direct allgather / alltoall (kernels/direct.cu) ----------------------------------
+// ---- low-latency kernel (kernels/ll.cu) ------------------------------------------------------
 /**
- * Uniform allgather / alltoall (counts in bytes) whose receive buffers are symmetric
- * memory: P.recv[r] must hold, for EVERY rank r of the communicator, the address in this
- * process of rank r's receive buffer (16-byte aligned); nothing is staged.
- * bulk_engine additionally needs 16-byte aligned send pointers and slices that are a
- * multiple of 16 bytes.
+ * Small uniform allreduce / reduce_scatter (same in, wire and out type) and allgather / alltoall (dt = u8,
+ * counts in bytes): at most kLLPayloadBytes from one rank to another, count > 0.
  */
-void launch_direct(const CollParams& P, bool bulk_engine, int ctas, int threads, int local_ranks, cudaStream_t stream);
+bool ll_supported(DevColl kind, DType dt, ReductionOperator op);
+void launch_ll(const LLParams& P, DType dt, int ctas, int threads, int local_ranks, cudaStream_t stream);
+
+// ---- window kernels (kernels/window.cu) ----------------------------------------------
+/**
+ * Uniform reduce_scatter (f32 / f16 / bf16; sum, avg, min, max) and allgather / alltoall / bcast (counts in
+ * bytes) straight on registered buffers: no staging.  P.windows must point to the communicator's window
+ * table in device memory and the descriptors of the registered side must be filled in (see WinParams).
+ */
+bool window_supported(DevColl kind, DType dt, ReductionOperator op);
+void launch_window(const WinParams& P, DType dt, ReductionOperator op, int ctas, int threads, int local_ranks,
+                   cudaStream_t stream);
 
 // ---- NVLS allreduce (kernels/nvls.cu) ------------------------------------------
 struct NvlsParams {

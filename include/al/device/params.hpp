@@ -58,26 +58,76 @@ struct FlagLayout {
 enum StatusCode : uint32_t {
   kStatusOk = 0,
   kStatusTimeout = 1,      ///< a flag wait exceeded its time budget
-  kStatusPoisoned = 2      ///< an earlier kernel of this communicator had failed; this one did nothing
+  kStatusPoisoned = 2,     ///< an earlier kernel of this communicator had failed; this one did nothing
+  kStatusMismatch = 3      ///< the ranks entered one operation with different protocols (e.g. one rank passed a
+                           ///< registered / symmetric buffer and another a private one); `seen` = the other tag
 };
+
+/**
+ * Protocol tag every kernel publishes when it enters an operation, so that ranks which chose
+ * different kernels for the same operation find out at once instead of waiting for flags that
+ * never come.  The choice depends on rank-local facts (is this rank's buffer registered?), which
+ * is why it has to be compared.
+ */
+enum ProtoTag : uint64_t {
+  kProtoNone = 0,
+  kProtoStaged = 1,        ///< generic kernel through the staging halves (any algorithm of it)
+  kProtoNvlsStaged = 2,    ///< NVLS allreduce through the multicast-bound staging
+  kProtoNvlsZeroCopy = 3,  ///< NVLS allreduce on symmetric user buffers
+  kProtoWindow = 4         ///< reduce_scatter / allgather / alltoall / bcast straight on registered buffers
+};
+
+/**
+ * The four meta words rank r publishes in slot [parity][r] of every rank's flag area:
+ *   word 0  chunk count of the operation (with the first A flag)
+ *   word 1  ProtoTag << 8 | DevColl kind (with "entered")
+ *   word 2  descriptor of the receive buffer, word 3 of the send buffer (window kernels)
+ */
+constexpr int kMetaChunks = 0, kMetaProto = 1, kMetaRecvDesc = 2, kMetaSendDesc = 3;
+
+/** Registered buffers ("windows"): every rank can address every rank's buffer of a window. */
+constexpr int kMaxWindows = 32;
+struct WindowTable {
+  char* peer[kMaxWindows][kMaxRanks];    ///< address, in this process, of rank r's buffer of window w (nullptr: free slot)
+  size_t bytes[kMaxWindows][kMaxRanks];  ///< its length
+  char* mc[kMaxWindows];                 ///< NVLink-multicast alias of the window (same offset on every rank), or nullptr
+};
+/** Buffer descriptor: (window + 1) << 48 | byte offset inside this rank's buffer of the window; 0 = not registered. */
+constexpr uint64_t make_desc(int window, size_t offset) { return ((uint64_t)(window + 1) << 48) | (uint64_t)offset; }
+constexpr int desc_window(uint64_t d) { return (int)(d >> 48) - 1; }
+constexpr size_t desc_offset(uint64_t d) { return (size_t)(d & ((uint64_t{1} << 48) - 1)); }
 
 /** Written by a kernel into pinned host memory; read by the host in Wait/Test and before each launch. */
 struct DeviceStatus {
   uint32_t code;    ///< StatusCode
   uint32_t rank;    ///< rank that gave up
   uint32_t peer;    ///< rank it was waiting for
-  uint32_t where;   ///< 0: A flags, 1: B flags, 2: C flags, 3: p2p credit, 4: p2p data, 5: rma, 6: a bulk copy that did not complete
+  uint32_t where;   ///< 0: A flags, 1: B flags, 2: C flags, 3: p2p credit, 4: p2p data, 5: rma, 6: a bulk copy that did not complete, 7: protocol comparison
   uint64_t epoch;   ///< epoch it was waiting for
   uint64_t seen;    ///< value it last saw
 };
+
+/**
+ * Low-latency packets (small allreduce / reduce_scatter / allgather / alltoall): every 8 bytes carry 4 bytes
+ * of payload and the 4-byte epoch of the operation, written and read as 16-byte vectors whose two halves
+ * are each delivered whole.  The receiver polls the data itself, so there is no flag round and no fence
+ * between the data and a flag (the role of NCCL's LL protocol, which the reference gets from ncclAllReduce
+ * & co. at these sizes).  One slot per (parity of the operation number, source rank).
+ */
+constexpr size_t kLLPayloadBytes = 16384;
+constexpr size_t kLLSlotBytes = 2 * kLLPayloadBytes;
+constexpr size_t kLLAreaBytes = 2 * (size_t)kMaxRanks * kLLSlotBytes;
 
 /** Workspace of one communicator as seen from the launching process. */
 struct Workspace {
   char* stage[kMaxRanks];        ///< staging base (two halves, contiguous) of every rank
   uint64_t* flags[kMaxRanks];    ///< flag area of every rank
   char* mbox[kMaxRanks];         ///< p2p mailbox area of every rank: [src][2 slots]
+  char* ll[kMaxRanks];           ///< low-latency packet area of every rank: [parity][src][kLLSlotBytes]
   char* mc_stage;                ///< NVLink-multicast alias of the staging area, or nullptr
   DeviceStatus* status;          ///< pinned host record (device-visible address)
+  uint64_t* stamps;              ///< nullptr, or 4 words of this GPU's memory that the small-message kernels fill with
+                                 ///< %globaltimer at entry / data sent / data seen / exit (latency breakdowns)
   size_t half_bytes;             ///< size of one staging half
   size_t mbox_slot_bytes;        ///< size of one mailbox slot
   int p;                         ///< communicator size
@@ -122,6 +172,44 @@ struct CollParams {
   int pipelined;                 ///< 1: half of the CTAs publish while the other half consumes (large uniform ops)
   size_t slot_elems;             ///< elements moved per slot and chunk (0 = the slot's capacity)
   int n_pub;                     ///< bulk-copy pipeline: number of publishing CTAs (0 = half of the grid)
+};
+
+/**
+ * Arguments of one launch of the window kernel: uniform reduce_scatter / allgather / alltoall / bcast
+ * whose remote side is a registered buffer.  Indexed by rank like CollParams (one entry outside emulation).
+ */
+struct WinParams {
+  Workspace ws;
+  const WindowTable* windows;    ///< device memory of the launching process
+  const void* send[kMaxRanks];
+  void* recv[kMaxRanks];
+  uint64_t send_desc[kMaxRanks]; ///< 0 when the send buffer is private
+  uint64_t recv_desc[kMaxRanks];
+  size_t count;                  ///< elements per rank slice (bcast: the whole vector)
+  uint64_t seq;
+  uint64_t timeout_ns;
+  double scale;
+  int int_div;
+  int kind;                      ///< DevColl: reduce_scatter, allgather, alltoall or bcast
+  int op;
+  int root;
+  int rank0;
+  int allow_multimem;            ///< 0: plain peer loads / stores only (tuning, tests of rank failure)
+};
+
+/** Arguments of one launch of the low-latency kernel (kernels/ll.cu).  Indexed by rank like CollParams. */
+struct LLParams {
+  Workspace ws;
+  const void* send[kMaxRanks];
+  void* recv[kMaxRanks];
+  size_t count;                  ///< elements: the vector (allreduce) or one rank's slice (the others)
+  uint64_t seq;
+  uint64_t timeout_ns;
+  double scale;
+  int int_div;
+  int kind;                      ///< DevColl: allreduce, reduce_scatter, allgather or alltoall
+  int op;
+  int rank0;
 };
 
 /** Arguments of one point-to-point launch (any mix of sends and receives). */

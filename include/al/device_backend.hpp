@@ -82,7 +82,8 @@ void wait_request(Request& req);
 }  // namespace internal
 
 using DeviceAllreduceAlgo = internal::device::AllreduceAlgo;
-enum class DeviceAlgo { automatic };
+/** `algo` argument of every device collective but allreduce: automatic, staged or window (see CollPath). */
+using DeviceAlgo = internal::device::CollPath;
 
 class DeviceBackend {
  public:
@@ -98,13 +99,14 @@ class DeviceBackend {
   using scatter_algo_type = DeviceAlgo;  using scatterv_algo_type = DeviceAlgo;
   static std::string Name() { return "DeviceBackend"; }
 
-  static void run(internal::Resolved&& r, comm_type& comm, req_type* req,
+  static void run(internal::Resolved&& r, comm_type& comm, req_type* req, int path = 0,
                   DeviceAllreduceAlgo algo = DeviceAllreduceAlgo::automatic) {
     using namespace internal::device;
     CollDesc d;
     d.kind = (DevColl)(int)r.kind;
     d.in = d.wire = d.out = r.dt;
     d.op = r.op; d.root = r.root; d.count = r.count; d.vector = r.vector; d.algo = algo;
+    d.path = (CollPath)path;
     std::vector<RankArgs> ra(1);
     ra[0].send = r.send; ra[0].recv = r.recv;
     ra[0].send_counts = std::move(r.send_counts); ra[0].send_displs = std::move(r.send_displs);
@@ -118,7 +120,7 @@ class DeviceBackend {
     }
   }
   static void run_allreduce(internal::Resolved&& r, comm_type& comm, req_type* req, DeviceAllreduceAlgo algo) {
-    run(std::move(r), comm, req, algo);
+    run(std::move(r), comm, req, 0, algo);
   }
   using p2p_item = internal::device::P2PDesc;
   static p2p_item make_send(const void* buf, size_t bytes, int peer) {
@@ -139,9 +141,14 @@ class DeviceBackend {
   }
   static bool test(req_type& req) { return internal::device::test_request(req); }
   static void wait(req_type& req) { internal::device::wait_request(req); }
-  /** Memory registration is implicit for buffers obtained from comm.symm_alloc(); other buffers are staged. */
-  static void register_memory(void*, size_t, comm_type&) {}
-  static void unregister_memory(void*, comm_type&) {}
+  /**
+   * Collective over the communicator (every rank calls it, in the same order, with its own buffer):
+   * the buffer becomes addressable by every rank, and reduce_scatter / allgather / alltoall / bcast on
+   * it skip the staging area.  Role of ncclCommRegister in the reference (src/nccl_impl.cpp:83-109),
+   * which is a local call there; buffers from comm.symm_alloc() need no registration.
+   */
+  static void register_memory(void* buf, size_t bytes, comm_type& comm) { (void)comm.register_buffer(buf, bytes); }
+  static void unregister_memory(void* buf, comm_type& comm) { comm.unregister_buffer(buf); }
 };
 
 }  // namespace Al

@@ -36,7 +36,7 @@ class HostBackend {
   static std::string Name() { return "HostBackend"; }
 
   /** Run a resolved collective; `req == nullptr` blocks the caller. */
-  static void run(internal::Resolved&& r, comm_type& comm, req_type* req) {
+  static void run(internal::Resolved&& r, comm_type& comm, req_type* req, int /*algo*/ = 0) {
     internal::host::CollArgs a;
     a.kind = (internal::host::Coll)(int)r.kind;
     a.send = r.send; a.recv = r.recv; a.dt = r.dt; a.op = r.op; a.root = r.root; a.count = r.count;

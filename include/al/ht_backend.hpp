@@ -103,7 +103,7 @@ class HostTransferBackend {
   using scatter_algo_type = HostAlgo;  using scatterv_algo_type = HostAlgo;
   static std::string Name() { return "HostTransferBackend"; }
 
-  static void run(internal::Resolved&& r, comm_type& comm, req_type* req) {
+  static void run(internal::Resolved&& r, comm_type& comm, req_type* req, int /*algo*/ = 0) {
     using namespace internal::device;
     if (req) {
       cudaStream_t s = begin_nonblocking_on(comm.get_stream(), comm.internal_stream());

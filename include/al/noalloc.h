@@ -32,6 +32,13 @@
  *    between them) race on the staging slots: order them yourself.
  *  - Inputs and outputs are the caller's; an output may alias its own rank's input.
  *  - No cudaMalloc, cudaFree, cudaHostAlloc or other allocating call is made.
+ *  - Every wait inside the kernel is bounded (2 s).  If one runs out - which needs a GPU so
+ *    oversubscribed that the cooperative grid's blocks stop making progress - the kernel
+ *    marks the scratch as failed and returns without writing the outputs, and so does every
+ *    later call: the launch itself still reports success, because the host never blocks.
+ *    A caller that must know synchronises its stream and asks al_noalloc_status(); a
+ *    non-zero code means the outputs of the calls since the last good status are not valid.
+ *    al_noalloc_reset() clears the mark (and the whole array) once nothing is in flight.
  *
  * Returns 0 on success; otherwise non-zero and al_noalloc_last_error() describes
  * the problem (thread-local string, valid until the next call on this thread).
@@ -48,6 +55,17 @@ extern "C" {
 #define AL_NOALLOC_SCRATCH_BYTES (8 * (4096 + 2 * 8 * 32768))
 
 int al_noalloc_allreduce_f32(const float* const* inputs, float* const* outputs, int p, size_t count, void* stream);
+/**
+ * Reads the failure mark of the current device's scratch into *code: 0 = healthy, 1 = a wait
+ * inside an earlier call ran out of time.  Copies a few words device-to-host with cudaMemcpy
+ * into the caller's variable; allocates nothing.  Synchronise the streams you used first.
+ */
+int al_noalloc_status(int* code);
+/**
+ * Zeroes the scratch array of the current device on `stream` and restarts the epochs.  Call it
+ * only when no al_noalloc_allreduce_f32 call is in flight on that device.  Allocates nothing.
+ */
+int al_noalloc_reset(void* stream);
 const char* al_noalloc_last_error(void);
 
 #ifdef __cplusplus

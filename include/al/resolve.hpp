@@ -37,7 +37,48 @@ struct Resolved {
   int root = 0;
   ReductionOperator op = ReductionOperator::sum;
   DType dt = DType::u8;
+  bool in_place = false;  ///< the call used the single-buffer form: send and recv alias on purpose
 };
+
+/** Elements of the (resolved) send and receive buffers that the operation reads / writes on `rank`. */
+struct Extent { size_t send_elems = 0, recv_elems = 0; };
+inline Extent extent_of(const Resolved& r, int rank, int size) {
+  Extent e;
+  const size_t p = (size_t)size;
+  auto span = [&](const std::vector<size_t>& c, const std::vector<size_t>& d) {
+    size_t m = 0;
+    for (size_t i = 0; i < c.size(); ++i) m = m > (d.empty() ? 0 : d[i]) + c[i] ? m : (d.empty() ? 0 : d[i]) + c[i];
+    return m;
+  };
+  switch (r.kind) {
+    case OpKind::allreduce: case OpKind::reduce: e.send_elems = e.recv_elems = r.count; break;
+    case OpKind::bcast: e.send_elems = rank == r.root ? r.count : 0; e.recv_elems = rank == r.root ? 0 : r.count; break;
+    case OpKind::reduce_scatter:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
+      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
+      break;
+    case OpKind::allgather:
+      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
+      break;
+    case OpKind::alltoall:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = e.recv_elems = r.count * p; }
+      break;
+    case OpKind::gather:
+      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
+      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
+      break;
+    case OpKind::scatter:
+      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
+      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
+      break;
+    case OpKind::barrier: break;
+  }
+  if (!r.send) e.send_elems = 0;
+  if (!r.recv) e.recv_elems = 0;
+  return e;
+}
 
 inline const char* op_kind_name(OpKind k) {
   static const char* n[] = {"allreduce", "reduce", "reduce_scatter", "allgather", "alltoall",
@@ -55,6 +96,7 @@ inline Resolved resolve_uniform(OpKind kind, DType dt, const void* send, void* r
   Resolved r;
   r.kind = kind; r.dt = dt; r.count = count; r.op = op; r.root = root;
   const bool ip = is_in_place(send);
+  r.in_place = ip || kind == OpKind::bcast;
   switch (kind) {
     case OpKind::allreduce: case OpKind::reduce: case OpKind::reduce_scatter: case OpKind::alltoall:
       r.send = ip ? recv : send; r.recv = recv; break;
@@ -91,6 +133,7 @@ inline Resolved resolve_vector(OpKind kind, DType dt, const void* send, void* re
   Resolved r;
   r.kind = kind; r.dt = dt; r.op = op; r.root = root; r.vector = true;
   const bool ip = is_in_place(send);
+  r.in_place = ip;
   const size_t p = (size_t)size;
   switch (kind) {
     case OpKind::reduce_scatter:  // counts = per-rank output lengths, inputs contiguous in rank order

@@ -29,6 +29,7 @@ void detach(void* remote_buf, int peer, DeviceCommunicator& comm);
 void notify(int peer, DeviceCommunicator& comm);
 void wait(int peer, DeviceCommunicator& comm);
 void put(const void* src, int dest, void* dest_remote, size_t bytes, DeviceCommunicator& comm);
+void get(void* dst, int src_rank, const void* src_remote, size_t bytes, DeviceCommunicator& comm);
 /** Drop the bookkeeping (signal counters, imported mappings) kept for a communicator that is going away. */
 void forget(const void* comm_impl) noexcept;
 }  // namespace rma
@@ -62,6 +63,20 @@ inline void Sync(const int* peers, int num_peers, DeviceCommunicator& comm) {
 template <typename T>
 void Put(const T* srcbuf, int dest, T* destbuf, size_t count, DeviceCommunicator& comm) {
   internal::rma::put(srcbuf, dest, destbuf, count * sizeof(T), comm);
+}
+
+/**
+ * The other direction: copy `count` elements out of `srcbuf`, an address obtained from
+ * AttachRemoteBuffer for rank `src`, into local `destbuf`.  Stream-ordered like Put; the owner of
+ * `srcbuf` tells the reader when the data may be read (Notify / Wait or Sync) and learns the same
+ * way when the read is over.  The reference's interface stops at Put; its north star (put / get over
+ * CUDA IPC) and DistConv-style pull patterns want this verb.  Loads over NVLink stall the issuing
+ * threads (stores are posted), so a Get moves about half of a Put's bandwidth: prefer Put where the
+ * producer can drive the transfer.
+ */
+template <typename T>
+void Get(T* destbuf, int src, const T* srcbuf, size_t count, DeviceCommunicator& comm) {
+  internal::rma::get(destbuf, src, srcbuf, count * sizeof(T), comm);
 }
 
 }  // namespace ext

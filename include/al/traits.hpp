@@ -57,9 +57,18 @@ constexpr bool IsRootedOp(AlOperation op) {
 /** Every backend of this library implements every operation. */
 template <AlOperation Op, typename Backend> struct IsOpSupported : std::true_type {};
 
-/** Only allreduce on the device backend has a real choice of algorithms. */
+/**
+ * Operations with a real choice behind their `algo` argument: on the device backend allreduce
+ * (one-shot / two-shot / NVLS) and the four operations that can run on registered buffers
+ * (staged / window).  The enum itself is OpAlgoType<Op, Backend>::type, defined with the backends.
+ */
 template <AlOperation Op, typename Backend> struct OpSupportsAlgos : std::false_type {};
 template <> struct OpSupportsAlgos<AlOperation::allreduce, DeviceBackend> : std::true_type {};
+template <> struct OpSupportsAlgos<AlOperation::reduce_scatter, DeviceBackend> : std::true_type {};
+template <> struct OpSupportsAlgos<AlOperation::allgather, DeviceBackend> : std::true_type {};
+template <> struct OpSupportsAlgos<AlOperation::alltoall, DeviceBackend> : std::true_type {};
+template <> struct OpSupportsAlgos<AlOperation::bcast, DeviceBackend> : std::true_type {};
+template <AlOperation Op, typename Backend> struct OpAlgoType;
 
 template <typename Backend> struct AlBackendName;
 template <> struct AlBackendName<HostBackend> { static constexpr const char* value = "host"; };
@@ -81,12 +90,27 @@ constexpr bool reduction_supported(DType dt, ReductionOperator op) {
   return !((op == ReductionOperator::bor || op == ReductionOperator::band || op == ReductionOperator::bxor) &&
            dtype_is_float(dt));
 }
+/** Is the operator available on the backend for at least one datatype?  (All are, everywhere.) */
 template <typename Backend, ReductionOperator Op> struct IsReductionOpSupported : std::true_type {};
+/**
+ * The table that matches what the kernels and host loops accept: operator x datatype x backend.
+ * Bitwise operators need an integer type on every backend; everything else is available wherever the
+ * datatype is.  Al::Allreduce & co. throw the same verdict at run time (the operator is a run-time
+ * argument), so `IsReductionSupported<B, float, bor>` being false is what a caller can test up front.
+ */
+template <typename Backend, typename T, ReductionOperator Op> struct IsReductionSupported
+    : std::integral_constant<bool, IsTypeSupported<Backend, T>::value && reduction_supported(TypeMap<T>::value, Op)> {};
 
 static_assert(IsReductionOp(AlOperation::reduce_scatterv) && IsVectorOp(AlOperation::reduce_scatterv), "traits");
 static_assert(IsRootedOp(AlOperation::bcast) && !IsRootedOp(AlOperation::allreduce), "traits");
 static_assert(IsTypeSupported<HostBackend, long double>::value, "traits");
 static_assert(!IsTypeSupported<DeviceBackend, long double>::value, "traits");
 static_assert(IsTypeSupported<DeviceBackend, float>::value && IsTypeSupported<DeviceBackend, bfloat16_t>::value, "traits");
+static_assert(!IsReductionSupported<DeviceBackend, float, ReductionOperator::bor>::value, "traits");
+static_assert(IsReductionSupported<DeviceBackend, int, ReductionOperator::bor>::value, "traits");
+static_assert(IsReductionSupported<DeviceBackend, float, ReductionOperator::avg>::value, "traits");
+static_assert(!IsReductionSupported<DeviceBackend, long double, ReductionOperator::sum>::value, "traits");
+static_assert(IsReductionSupported<HostBackend, long double, ReductionOperator::sum>::value, "traits");
+static_assert(OpSupportsAlgos<AlOperation::allgather, DeviceBackend>::value && !OpSupportsAlgos<AlOperation::gather, DeviceBackend>::value, "traits");
 
 }  // namespace Al

@@ -52,8 +52,12 @@ struct Tuning {
   bool bulk_pipeline = false;                  ///< AL_DEV_BULK_PIPELINE: pipelined reduce_scatter / allgather / alltoall move their data with the bulk copy engine (cp.async.bulk) when every buffer is 16-byte aligned
   int bulk_pub_ctas = 16;                      ///< AL_DEV_BULK_PUB_CTAS: publishing CTAs of that kernel (one issuing thread each)
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
-  bool direct_symmetric = false;               ///< AL_DEV_DIRECT: uniform allgather / alltoall whose receive buffer comes from symm_alloc() (same block and offset on every rank) are stored straight into the peers' buffers, without staging
-  bool direct_bulk = false;                    ///< AL_DEV_DIRECT_BULK: ... with the bulk copy engine instead of SM store loops
+  size_t ll_max_bytes = size_t{8} << 10;       ///< AL_LL_MAX: uniform allreduce / reduce_scatter / allgather / alltoall of at most this many bytes per pair of ranks travel as low-latency packets (hard limit 16 KiB; 0 = never)
+  int ll_max_ctas = 4;                         ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
+  bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
+  size_t window_min_bytes = size_t{256} << 10; ///< AL_WINDOW_MIN: ... from this total message size on (smaller ones are faster through staging: one flag round instead of two)
+  int window_ctas = 64;                        ///< AL_WINDOW_CTAS: CTA budget of a window kernel
+  bool window_multimem = true;                 ///< AL_WINDOW_MULTIMEM: let window kernels use multimem.st / multimem.ld_reduce when all ranks pass the same offset of one multicast-bound window
   // ---- diagnostics ------------------------------------------------------------
   bool trace = false;                          ///< AL_TRACE: record every API call
   bool debug_checks = false;                   ///< AL_DEBUG: argument checks on every call

@@ -39,6 +39,9 @@ __global__ void __launch_bounds__(512) bulk_pipeline_kernel(const __grid_constan
   const int p = ws.p;
   const int rank = P.rank0 + (int)blockIdx.y;
   if (poisoned(ws, rank)) return;
+  // same protocol (and the same announcement) as the pipelined schedule of the generic kernel
+  const uint64_t my_proto = proto_word(kProtoStaged, P.kind, P.two_phase | (P.pipelined << 1));
+  if (blockIdx.x == 0) post_entered(ws, rank, P.seq, my_proto, 0, 0);
 
   const DevColl kind = (DevColl)P.kind;
   const CountTable& Tb = P.tab[rank];
@@ -101,13 +104,14 @@ __global__ void __launch_bounds__(512) bulk_pipeline_kernel(const __grid_constan
         __threadfence_system();
       }
       if (stage_failed(ok, 6, c)) return;
-      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_pub, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G);
+      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_pub, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
     }
   } else {
     // ------------------------------- consumers ----------------------------------
     const unsigned part = blockIdx.x - n_pub;
     for (uint64_t c = 0; c < G; ++c) {
       if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
       const int par = (int)((P.seq + c) & 1);
       char* mystage = ws.stage[rank] + (size_t)par * half;
       const size_t base = c * slot_e, len = clamp_len(count, base, slot_e);

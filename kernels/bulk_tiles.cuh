@@ -111,30 +111,6 @@ AL_HD Move gather_consume(const Share& s, size_t t, int p, size_t slice, size_t 
   return m;
 }
 
-// ---- direct kernel (direct.cu): one "chunk" covering the whole slice, no staging ------------
-
-/** Allgather, tile k: the rank's contribution goes to slice [rank] of every receive buffer. */
-AL_HD Move ag_direct(const Share& s, size_t k, int rank, size_t slice, size_t tile) {
-  Move m;
-  m.src = s.lo + k * tile;
-  m.dst = (size_t)rank * slice + s.lo + k * tile;
-  m.bytes = tile_bytes(s, k, tile);
-  m.peer = -1;
-  return m;
-}
-
-/** Alltoall, tile t: slice d of the send buffer goes to slice [rank] of rank d's receive buffer. */
-AL_HD Move a2a_direct(const Share& s, size_t t, int rank, int p, size_t slice, size_t tile) {
-  const int d = (rank + 1 + (int)(t % (size_t)p)) % p;
-  const size_t k = t / (size_t)p;
-  Move m;
-  m.src = (size_t)d * slice + s.lo + k * tile;
-  m.dst = (size_t)rank * slice + s.lo + k * tile;
-  m.bytes = tile_bytes(s, k, tile);
-  m.peer = d;
-  return m;
-}
-
 }  // namespace plan
 }  // namespace device
 }  // namespace internal

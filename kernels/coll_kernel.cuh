@@ -25,9 +25,16 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   const int p = ws.p;
   const int rank = P.rank0 + (int)blockIdx.y;
   if (poisoned(ws, rank)) return;
+  stamp(ws, 0);
 
   const DevColl kind = (DevColl)P.kind;
   const CountTable& T = P.tab[rank];
+  // Operations that also exist as window kernels (registered buffers) announce which protocol this
+  // rank runs, so that a rank that chose the other one is not left waiting (see protocols_agree).
+  const uint64_t my_proto = proto_word(kProtoStaged, P.kind, P.two_phase | (P.pipelined << 1));
+  const bool announces = kind == DevColl::reduce_scatter || kind == DevColl::allgather || kind == DevColl::alltoall ||
+                         kind == DevColl::bcast;
+  if (announces && blockIdx.x == 0) post_entered(ws, rank, P.seq, my_proto, 0, 0);
   const size_t half = ws.half_bytes;
   const size_t full_e = half / sizeof(Tw);
   const size_t cap_b = (half / (size_t)p) / 256 * 256;           // one slot per source rank
@@ -226,11 +233,12 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       for (uint64_t c = 0; c < G; ++c) {
         if (c >= 2 && !wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, c - 1), P.timeout_ns)) return;
         publish(c, blockIdx.x, n_pub);
-        arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_pub, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G);
+        arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_pub, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
       }
     } else {
       for (uint64_t c = 0; c < G; ++c) {
         if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+        if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
         consume(c, blockIdx.x - n_pub, n_con);
         arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_con, make_epoch(P.seq, c + 1), false, 0, 0);
       }
@@ -247,9 +255,12 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
   for (uint64_t c = 0; c < G; ++c) {
     publish(c, cta, nct);
     const uint64_t e = make_epoch(P.seq, c + 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, nct, e, c == 0, (int)(P.seq & 1), P.local_chunks[rank]);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, nct, e, c == 0, (int)(P.seq & 1), P.local_chunks[rank], my_proto);
+    if (c == 0) stamp(ws, 1);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
     if (c == 0) {
+      stamp(ws, 2);
+      if (p > 1 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
       if (threadIdx.x == 0) {
         uint64_t g = 1;
         for (int r = 0; r < p; ++r) {
@@ -299,6 +310,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
     }
   }
 
+  stamp(ws, 3);
   if (G > 1) {
     // Both halves were used: make sure every peer is done with them before the
     // next launch (which may start on either half) writes into them.

@@ -40,6 +40,11 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
+/** Latency breakdown: one thread of the launch records the global timer at point `i` (0..3) when asked to. */
+__device__ __forceinline__ void stamp(const Workspace& ws, int i) {
+  if (ws.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ws.stamps[i] = global_ns();
+}
+
 __device__ __forceinline__ uint64_t make_epoch(uint64_t seq, uint64_t sub) { return (seq << 24) | sub; }
 
 __device__ __forceinline__ uint64_t* flag_slot(uint64_t* area, size_t off, int idx) {
@@ -64,6 +69,25 @@ __device__ __forceinline__ void report_timeout(const Workspace& ws, int rank, in
       s->seen = seen;
       __threadfence_system();
       s->code = kStatusTimeout;
+      __threadfence_system();
+    }
+  }
+}
+
+/** Record a failure other than a time-out (same rules: first one wins, later kernels return at once). */
+__device__ __forceinline__ void report_status(const Workspace& ws, int rank, uint32_t code, int peer, uint32_t where,
+                                              uint64_t epoch, uint64_t seen) {
+  unsigned long long* local = (unsigned long long*)flag_slot(ws.flags[rank], FlagLayout::off_status, 0);
+  if (atomicCAS(local, 0ull, (unsigned long long)code) == 0ull) {
+    DeviceStatus* s = ws.status;
+    if (s) {
+      s->rank = (uint32_t)rank;
+      s->peer = (uint32_t)peer;
+      s->where = where;
+      s->epoch = epoch;
+      s->seen = seen;
+      __threadfence_system();
+      s->code = code;
       __threadfence_system();
     }
   }
@@ -116,7 +140,7 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* slot, uint64_t epoch, 
  */
 __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, size_t off, int counter_idx,
                                                 unsigned group, uint64_t epoch, bool with_meta, int meta_par,
-                                                uint64_t meta_value) {
+                                                uint64_t meta_value, uint64_t meta_proto = 0) {
   __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -132,8 +156,11 @@ __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, s
   __syncthreads();
   if (s_last && threadIdx.x < ws.p) {
     const int dst = threadIdx.x;
-    if (with_meta)
-      st_relaxed_sys(flag_slot(ws.flags[dst], FlagLayout::off_meta, meta_par * kMaxRanks + rank), meta_value);
+    if (with_meta) {
+      uint64_t* m = flag_slot(ws.flags[dst], FlagLayout::off_meta, meta_par * kMaxRanks + rank);
+      st_relaxed_sys(m + kMetaChunks, meta_value);
+      if (meta_proto) st_relaxed_sys(m + kMetaProto, meta_proto);
+    }
     st_release_sys(flag_slot(ws.flags[dst], off, rank), epoch);
   }
 }
@@ -154,6 +181,64 @@ __device__ __forceinline__ bool wait_all(const Workspace& ws, int rank, size_t o
   }
   __syncthreads();
   return s_ok != 0;
+}
+
+// ---------------------------------------------------------------------------
+// protocol agreement
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t proto_word(ProtoTag tag, int kind, int variant = 0) {
+  return ((uint64_t)tag << 8) | (uint64_t)(kind & 0xff) | ((uint64_t)(variant & 0xff) << 16);
+}
+
+/**
+ * "I have entered operation `seq`": one CTA (the caller picks it) stores this rank's protocol word
+ * and buffer descriptors into every rank's meta slot and then the B flag.  The stream order of the
+ * poster guarantees that its earlier work on its buffers is complete, so peers that see the flag may
+ * write into (or read from) its registered buffers.  Nobody has to wait for it: kernels that go
+ * through staging post it and carry on.
+ */
+__device__ __forceinline__ void post_entered(const Workspace& ws, int rank, uint64_t seq, uint64_t proto,
+                                             uint64_t recv_desc, uint64_t send_desc) {
+  if (threadIdx.x < ws.p) {
+    const int dst = threadIdx.x;
+    uint64_t* m = flag_slot(ws.flags[dst], FlagLayout::off_meta, (int)(seq & 1) * kMaxRanks + rank);
+    st_relaxed_sys(m + kMetaProto, proto);
+    st_relaxed_sys(m + kMetaRecvDesc, recv_desc);
+    st_relaxed_sys(m + kMetaSendDesc, send_desc);
+    st_release_sys(flag_slot(ws.flags[dst], FlagLayout::off_B, rank), make_epoch(seq, 1));
+  }
+}
+
+/**
+ * After a wait that made every rank's protocol word visible: do all ranks run the protocol `mine`?
+ * Block-uniform answer.  On disagreement the failure is recorded as kStatusMismatch (peer = first
+ * rank that differs, seen = its word) and this rank's A and C flags are pushed to the operation's
+ * last possible epoch, so that a peer which is waiting for them under the other protocol wakes up,
+ * compares the words as well and returns - nobody is left to a time-out.
+ */
+__device__ __forceinline__ bool protocols_agree(const Workspace& ws, int rank, uint64_t seq, uint64_t mine) {
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = -1;
+  __syncthreads();
+  if (threadIdx.x < ws.p) {
+    const uint64_t* m = flag_slot(ws.flags[rank], FlagLayout::off_meta, (int)(seq & 1) * kMaxRanks + threadIdx.x);
+    if (ld_relaxed_sys(m + kMetaProto) != mine) atomicMax(&s_bad, (int)threadIdx.x);
+  }
+  __syncthreads();
+  const int bad = s_bad;
+  if (bad < 0) return true;
+  if (threadIdx.x < ws.p) {
+    if (threadIdx.x == 0) {
+      const uint64_t* m = flag_slot(ws.flags[rank], FlagLayout::off_meta, (int)(seq & 1) * kMaxRanks + bad);
+      report_status(ws, rank, kStatusMismatch, bad, 7, mine, ld_relaxed_sys(m + kMetaProto));
+    }
+    const uint64_t last = make_epoch(seq, 0xFFFFFE);
+    st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_A, rank), last);
+    st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_B, rank), last);
+    st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_C, rank), last);
+  }
+  __syncthreads();
+  return false;
 }
 
 }  // namespace device

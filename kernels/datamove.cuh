@@ -262,7 +262,8 @@ __device__ __forceinline__ A finish_acc(A a, double scale, int int_div) {
  * destinations dsts[d] (all holding To elements; several destinations are used
  * when a reduced slice is pushed to every peer).  Sources are staging memory
  * (16-byte aligned); contributions are folded in rank order so every rank
- * computes bit-identical results.  A destination may alias one of the sources.
+ * computes bit-identical results.  A destination may alias one of the sources.  Sources that are
+ * not 16-byte aligned are read element by element.
  */
 template <typename Tw, typename To, typename Red>
 __device__ __forceinline__ void cta_reduce(To* const* dsts, int ndst, char* const* bases, size_t byte_off, int p,
@@ -274,6 +275,8 @@ __device__ __forceinline__ void cta_reduce(To* const* dsts, int ndst, char* cons
   constexpr size_t out_align = out_bytes < 16 ? out_bytes : 16;
   bool aligned = true;
   for (int d = 0; d < ndst; ++d) aligned = aligned && ((uintptr_t)dsts[d] % out_align == 0);
+  // staging sources always are 16-byte aligned; registered user buffers (window kernels) need not be
+  for (int r = 0; r < p; ++r) aligned = aligned && ((uintptr_t)(bases[r] + byte_off) % 16 == 0);
   const size_t nvec = aligned ? n / VEC : 0;
   union InPack { uint4 u; Tw e[VEC]; };
   union OutPack { uint4 u[(out_bytes + 15) / 16]; To e[VEC]; };

@@ -71,7 +71,7 @@ extern "C" int al_noalloc_allreduce_f32(const float* const* inputs, float* const
   P.ws.half_bytes = kHalfBytes;
   P.ws.mbox_slot_bytes = 0;
   P.ws.mc_stage = nullptr;
-  P.ws.status = nullptr;  // no pinned status record: a timed-out wait only marks the flag area
+  P.ws.status = nullptr;  // no pinned status record: a timed-out wait only marks the flag area (al_noalloc_status reads it)
   for (int r = 0; r < p; ++r) {
     unsigned char* rb = D.base + (size_t)r * kRankBytes;
     P.ws.flags[r] = (uint64_t*)rb;
@@ -106,5 +106,52 @@ extern "C" int al_noalloc_allreduce_f32(const float* const* inputs, float* const
   if (p > 1) e = cudaLaunchCooperativeKernel((const void*)k, grid, block, args, 0, (cudaStream_t)stream);
   else e = cudaLaunchKernel((const void*)k, grid, block, args, 0, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("launch failed: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// status and recovery
+// ---------------------------------------------------------------------------------------------
+namespace {
+/** Device address of the scratch on the current device (looked up on first use), or nullptr + error. */
+PerDevice* current_device_state() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { fail(std::string("cudaGetDevice: ") + cudaGetErrorString(e)); return nullptr; }
+  if (dev < 0 || dev >= kMaxDevices) { fail("al_noalloc: device index out of range"); return nullptr; }
+  PerDevice& D = g_dev[dev];
+  if (!D.base) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) { fail(std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e)); return nullptr; }
+    D.base = (unsigned char*)ptr;
+  }
+  return &D;
+}
+}  // namespace
+
+extern "C" int al_noalloc_status(int* code) {
+  if (!code) return fail("al_noalloc_status: null argument");
+  std::lock_guard<std::mutex> lock(g_mu);
+  PerDevice* D = current_device_state();
+  if (!D) return 1;
+  *code = 0;
+  for (int r = 0; r < AL_NOALLOC_MAX_RANKS; ++r) {
+    unsigned long long word = 0;
+    const unsigned char* src = D->base + (size_t)r * kRankBytes + FlagLayout::off_status * sizeof(uint64_t);
+    const cudaError_t e = cudaMemcpy(&word, src, sizeof(word), cudaMemcpyDeviceToHost);  // pageable destination: nothing is allocated
+    if (e != cudaSuccess) return fail(std::string("cudaMemcpy: ") + cudaGetErrorString(e));
+    if (word != 0 && *code == 0) *code = (int)word;
+  }
+  return 0;
+}
+
+extern "C" int al_noalloc_reset(void* stream) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  PerDevice* D = current_device_state();
+  if (!D) return 1;
+  const cudaError_t e = cudaMemsetAsync(D->base, 0, AL_NOALLOC_SCRATCH_BYTES, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  D->seq = 0;  // flags and epochs start over together
   return 0;
 }

@@ -18,55 +18,13 @@
 #include "al/cuda/cuda.hpp"
 #include "al/device/kernels.hpp"
 #include "datamove.cuh"
+#include "multimem.cuh"
 
 namespace Al {
 namespace internal {
 namespace device {
 
 namespace {
-
-enum class NvOp { add, min, max };
-
-template <typename T, NvOp OP> struct MM;
-
-template <> struct MM<float, NvOp::add> {
-  static __device__ __forceinline__ uint4 ld(const void* mc) {
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
-    return v;
-  }
-};
-#define AL_MM_16(T, TOK, OP, OPTOK)                                                                       \
-  template <> struct MM<T, NvOp::OP> {                                                                    \
-    static __device__ __forceinline__ uint4 ld(const void* mc) {                                          \
-      uint4 v;                                                                                            \
-      asm volatile("multimem.ld_reduce.relaxed.sys.global." OPTOK ".v4." TOK " {%0,%1,%2,%3}, [%4];"      \
-                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");                    \
-      return v;                                                                                           \
-    }                                                                                                     \
-  };
-AL_MM_16(__nv_bfloat16, "bf16x2", add, "add.acc::f32")
-AL_MM_16(__nv_bfloat16, "bf16x2", min, "min")
-AL_MM_16(__nv_bfloat16, "bf16x2", max, "max")
-AL_MM_16(__half, "f16x2", add, "add.acc::f32")
-AL_MM_16(__half, "f16x2", min, "min")
-AL_MM_16(__half, "f16x2", max, "max")
-#undef AL_MM_16
-
-__device__ __forceinline__ void mm_st(void* mc, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
-               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-
-template <typename T>
-__device__ __forceinline__ uint4 scale_pack(uint4 v, float s) {
-  union { uint4 u; T e[16 / sizeof(T)]; } x;
-  x.u = v;
-#pragma unroll
-  for (int k = 0; k < (int)(16 / sizeof(T)); ++k) x.e[k] = Elem<T>::down(Elem<T>::up(x.e[k]) * s);
-  return x.u;
-}
 
 /**
  * Reduce-and-replicate the 16-byte vectors [v_lo, v_hi) of the multicast range.
@@ -106,9 +64,12 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
   if (P.mc_in != nullptr) {
     // ---- zero-copy: operate on the user's symmetric buffers --------------------
     const uint64_t e = make_epoch(P.seq, 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, true, (int)(P.seq & 1), 1);
+    // The choice between this flavour and the staged one depends on this rank's own buffers: compare.
+    const uint64_t my_proto = proto_word(kProtoNvlsZeroCopy, (int)DevColl::allreduce);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, true, (int)(P.seq & 1), 1, my_proto);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
-    const size_t nvec = (P.count * sizeof(T) + 15) >> 4;  // symmetric allocations are padded to 16 bytes
+    if (!protocols_agree(ws, rank, P.seq, my_proto)) return;
+    const size_t nvec = (P.count * sizeof(T) + 15) >> 4;  // a tail vector only ever covers the block's own padding
     size_t s_lo, s_hi;
     split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
     reduce_vectors<T, OP>(P.mc_in, P.mc_out, s_lo, s_hi, scale, blockIdx.x, gridDim.x);
@@ -124,6 +85,7 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
   const T* send = (const T*)P.send;
   T* recv = (T*)P.recv;
   const uint64_t G = P.chunks;
+  const uint64_t my_proto = proto_word(kProtoNvlsStaged, (int)DevColl::allreduce);
   for (uint64_t c = 0; c < G; ++c) {
     const int par = (int)((P.seq + c) & 1);
     char* mystage = ws.stage[rank] + (size_t)par * half;
@@ -134,8 +96,9 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
     if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
 
     const uint64_t e = make_epoch(P.seq, c + 1);
-    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, c == 0, (int)(P.seq & 1), G);
+    arrive_and_post(ws, rank, FlagLayout::off_A, 0, gridDim.x, e, c == 0, (int)(P.seq & 1), G, my_proto);
     if (!wait_all(ws, rank, FlagLayout::off_A, 0, e, P.timeout_ns)) return;
+    if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
 
     const size_t nvec = (len * sizeof(T) + 15) >> 4;  // the tail vector may include stale bytes: harmless
     size_t s_lo, s_hi;
@@ -181,6 +144,7 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
   if (n_red > n - 2) n_red = n - 2;
   const unsigned n_in = (n - n_red) / 2, n_out = n - n_red - n_in;
   const unsigned b = blockIdx.x;
+  const uint64_t my_proto = proto_word(kProtoNvlsStaged, (int)DevColl::allreduce, 1);
 
   if (b < n_in) {
     for (uint64_t c = 0; c < G; ++c) {
@@ -199,11 +163,12 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
       size_t lo, hi;
       split_range(len, b, n_in, 16 / sizeof(T), lo, hi);
       if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
-      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G);
+      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
     }
   } else if (b < n_in + n_red) {
     for (uint64_t c = 0; c < G; ++c) {
       if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
       char* mc = ws.mc_stage + (size_t)((P.seq + c) & 1) * half;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       const size_t nvec = (len * sizeof(T) + 15) >> 4;

@@ -99,7 +99,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
   X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(direct_symmetric) X(direct_bulk)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_bytes) X(ll_max_ctas) X(window_enable) X(window_min_bytes) X(window_ctas) X(window_multimem)
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {
@@ -274,7 +274,7 @@ int al_dev_comm_stats(void* comm, uint64_t* out) {
     device::CommStats s = ((DeviceCommunicator*)comm)->stats();
     out[0] = s.ops; out[1] = s.bytes; out[2] = s.kernels; out[3] = s.timeouts;
     out[4] = s.ar_one_shot; out[5] = s.ar_two_shot; out[6] = s.ar_nvls; out[7] = s.ar_nvls_zero_copy;
-    out[8] = s.bulk_pipeline; out[9] = s.direct;
+    out[8] = s.bulk_pipeline; out[9] = s.window; out[10] = s.ll;
   });
 }
 int al_dev_comm_status(void* comm, uint64_t* out) {
@@ -302,7 +302,8 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
     d.count = count;
     d.vector = vector != 0;
     d.scale = scale;
-    d.algo = (device::AllreduceAlgo)algo;
+    if ((OpKind)kind == OpKind::allreduce) d.algo = (device::AllreduceAlgo)algo;
+    else d.path = (device::CollPath)algo;
     d.ctas = ctas;
     std::vector<device::RankArgs> ra((size_t)nlocal);
     for (int lr = 0; lr < nlocal; ++lr) {
@@ -329,6 +330,21 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
       c.collective(d, ra, pick_stream(&c, stream));
     }
   });
+}
+
+int al_dev_register(void* comm, void* ptr, size_t bytes) {
+  int w = -1;
+  if (guard([&] { w = ((DeviceCommunicator*)comm)->register_buffer(ptr, bytes); }) != 0) return -2;
+  return w;
+}
+int al_dev_register_emulated(void* comm, void* const* ptrs, int n, size_t bytes) {
+  int w = -1;
+  if (guard([&] { w = ((DeviceCommunicator*)comm)->register_buffers_emulated(std::vector<void*>(ptrs, ptrs + n), bytes); }) != 0)
+    return -2;
+  return w;
+}
+int al_dev_unregister(void* comm, void* ptr) {
+  return guard([&] { ((DeviceCommunicator*)comm)->unregister_buffer(ptr); });
 }
 
 int al_dev_time_collective(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op,
@@ -430,6 +446,9 @@ int al_rma_detach(void* comm, void* remote_buf, int peer) {
 }
 int al_rma_put(void* comm, const void* src, int dest, void* dest_remote, size_t bytes) {
   return guard([&] { rma::put(src, dest, dest_remote, bytes, *(DeviceCommunicator*)comm); });
+}
+int al_rma_get(void* comm, void* dst, int src_rank, const void* src_remote, size_t bytes) {
+  return guard([&] { rma::get(dst, src_rank, src_remote, bytes, *(DeviceCommunicator*)comm); });
 }
 int al_rma_notify(void* comm, int peer) { return guard([&] { rma::notify(peer, *(DeviceCommunicator*)comm); }); }
 int al_rma_wait(void* comm, int peer) { return guard([&] { rma::wait(peer, *(DeviceCommunicator*)comm); }); }

@@ -33,6 +33,16 @@ struct DeviceCommunicator::Impl {
   cudaEvent_t chain_event = nullptr;
   std::vector<uint64_t> p2p_sent, p2p_recvd;  // [nlocal][p]
   std::vector<std::unique_ptr<SymmBlock>> user_blocks;
+  // Registered buffers.  Slot w describes window w on every rank; the device copy is what kernels read.
+  struct Window {
+    bool used = false;
+    void* local[kMaxRanks] = {};       // start of each LOCAL rank's buffer (index = rank; one entry outside emulation)
+    const SymmBlock* block = nullptr;  // set when the window is a whole symm_alloc block
+    std::vector<void*> opened;         // CUDA IPC mappings to close
+  };
+  Window windows[kMaxWindows];
+  WindowTable table_host{};
+  WindowTable* table_dev = nullptr;
   CommStats stats;
   std::atomic<bool> aborted{false};
   std::string abort_msg;
@@ -40,6 +50,8 @@ struct DeviceCommunicator::Impl {
 
   size_t off_stage() const { return FlagLayout::bytes; }
   size_t off_mbox() const { return FlagLayout::bytes + 2 * ws.half_bytes; }
+  size_t off_ll() const { return off_mbox() + (size_t)p * 2 * ws.mbox_slot_bytes; }
+  uint64_t* stamps_dev = nullptr;
 
   void setup(std::unique_ptr<SymmBlock> b, int p_, int rank0_, int nlocal_) {
     p = p_; rank0 = rank0_; nlocal = nlocal_;
@@ -52,6 +64,7 @@ struct DeviceCommunicator::Impl {
       ws.flags[r] = (uint64_t*)base;
       ws.stage[r] = base + off_stage();
       ws.mbox[r] = base + off_mbox();
+      ws.ll[r] = base + off_ll();
     }
     ws.mc_stage = block->mc() ? (char*)block->mc() + off_stage() : nullptr;
     void* hp = nullptr;
@@ -63,18 +76,54 @@ struct DeviceCommunicator::Impl {
     ws.status = (DeviceStatus*)dp;
     timeout_ns = (uint64_t)(tuning().dev_wait_timeout_ms * 1e6);
     AL_CHECK_CUDA(cudaEventCreateWithFlags(&chain_event, cudaEventDisableTiming));
+    AL_CHECK_CUDA(cudaMalloc((void**)&table_dev, sizeof(WindowTable)));
+    AL_CHECK_CUDA(cudaMemset(table_dev, 0, sizeof(WindowTable)));
     p2p_sent.assign((size_t)nlocal * (size_t)p, 0);
     p2p_recvd.assign((size_t)nlocal * (size_t)p, 0);
   }
 
   ~Impl() {
     internal::rma::forget(this);
+    for (auto& w : windows)
+      for (void* m : w.opened) AL_WARN_CUDA(cudaIpcCloseMemHandle(m));
+    if (table_dev) AL_WARN_CUDA(cudaFree(table_dev));
+    if (stamps_dev) AL_WARN_CUDA(cudaFree(stamps_dev));
     if (chain_event) AL_WARN_CUDA(cudaEventDestroy(chain_event));
     if (status_host) AL_WARN_CUDA(cudaFreeHost(status_host));
   }
 
   static size_t block_bytes(int p, size_t half, size_t slot) {
-    return FlagLayout::bytes + 2 * half + (size_t)p * 2 * slot;
+    return FlagLayout::bytes + 2 * half + (size_t)p * 2 * slot + kLLAreaBytes;
+  }
+
+  int free_window() const {
+    for (int w = 0; w < kMaxWindows; ++w)
+      if (!windows[w].used) return w;
+    return -1;
+  }
+  void push_table() {
+    AL_CHECK_CUDA(cudaMemcpy(table_dev, &table_host, sizeof(WindowTable), cudaMemcpyHostToDevice));
+  }
+  void clear_window(int w) {
+    for (void* m : windows[w].opened) AL_WARN_CUDA(cudaIpcCloseMemHandle(m));
+    windows[w] = Window();
+    for (int r = 0; r < kMaxRanks; ++r) { table_host.peer[w][r] = nullptr; table_host.bytes[w][r] = 0; }
+    table_host.mc[w] = nullptr;
+  }
+  /** A whole symmetric block becomes window `w` (same slot on every rank: blocks are allocated collectively). */
+  void add_block_window(const SymmBlock* b) {
+    const int w = free_window();
+    if (w < 0) return;
+    Window& W = windows[w];
+    W.used = true;
+    W.block = b;
+    for (int r = 0; r < p; ++r) {
+      table_host.peer[w][r] = (char*)b->peer(r);
+      table_host.bytes[w][r] = b->bytes();
+    }
+    for (int lr = 0; lr < nlocal; ++lr) W.local[rank0 + lr] = b->peer(rank0 + lr);
+    table_host.mc[w] = (char*)b->mc();
+    push_table();
   }
 
   /** Make `stream` wait for the communicator's previous operation if that ran on another stream. */
@@ -164,6 +213,24 @@ const char* DeviceCommunicator::memory_backing() const { return impl_->block->ba
 const Workspace& DeviceCommunicator::workspace() const { return impl_->ws; }
 uint64_t DeviceCommunicator::next_halo_epoch() { return ++impl_->halo_epoch; }
 
+void DeviceCommunicator::enable_stamps(bool on) {
+  Impl& I = *impl_;
+  std::lock_guard<std::mutex> lock(I.mu);
+  if (on && !I.stamps_dev) {
+    AL_CHECK_CUDA(cudaMalloc((void**)&I.stamps_dev, 4 * sizeof(uint64_t)));
+    AL_CHECK_CUDA(cudaMemset(I.stamps_dev, 0, 4 * sizeof(uint64_t)));
+  }
+  I.ws.stamps = on ? I.stamps_dev : nullptr;
+}
+
+void DeviceCommunicator::read_stamps(uint64_t out[4]) const {
+  const Impl& I = *impl_;
+  for (int i = 0; i < 4; ++i) out[i] = 0;
+  if (!I.stamps_dev) return;
+  AL_CHECK_CUDA(cudaDeviceSynchronize());
+  AL_CHECK_CUDA(cudaMemcpy(out, I.stamps_dev, 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+}
+
 void DeviceCommunicator::set_wait_timeout_ms(double ms) {
   impl_->timeout_ns = (uint64_t)(std::max(0.001, ms) * 1e6);
 }
@@ -187,10 +254,18 @@ void DeviceCommunicator::check_status() const {
   if (code == kStatusOk) return;
   DeviceStatus s = status();
   static const char* where[] = {"data-ready flags", "reduced-slice flags", "closing barrier", "send credit",
-                                "incoming data", "RMA / halo signal", "bulk copy completion"};
+                                "incoming data", "RMA / halo signal", "bulk copy completion", "protocol comparison"};
+  if (code == kStatusMismatch) {
+    static const char* proto[] = {"none", "staging", "NVLS through staging", "NVLS on symmetric buffers", "registered buffers (window)"};
+    const unsigned mine = (unsigned)((s.epoch >> 8) & 0xff), theirs = (unsigned)((s.seen >> 8) & 0xff);
+    throw_al_exception("device communicator failed: ranks ", s.rank, " and ", s.peer, " entered one operation on different "
+                       "paths (", proto[mine < 5 ? mine : 0], " vs ", proto[theirs < 5 ? theirs : 0],
+                       "): every rank must pass a registered / symmetric buffer, or none; the communicator is unusable, "
+                       "create a new one");
+  }
   impl_->stats.timeouts++;
   throw_al_exception("device communicator failed: rank ", s.rank, " timed out waiting for rank ", s.peer, " (",
-                     where[s.where < 7 ? s.where : 0], ", epoch ", s.epoch, ", last seen ", s.seen,
+                     where[s.where < 8 ? s.where : 0], ", epoch ", s.epoch, ", last seen ", s.seen,
                      "); the communicator is unusable, create a new one");
 }
 
@@ -285,36 +360,107 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   }
 
 
-  // Opt-in: a uniform allgather / alltoall whose receive buffers are symmetric memory (the same
-  // offset of the same symm_alloc() block on every rank - as for the zero-copy NVLS allreduce, every
-  // rank must pass the corresponding buffer) stores straight into the peers' buffers.
-  const SymmBlock* direct_block = nullptr;
-  size_t direct_off = 0;
-  if (tn.direct_symmetric && (d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector && p > 1 &&
-      in == DType::u8 && P.count > 0 && P.count % 16 == 0) {
-    const size_t total = P.count * (size_t)p;
-    const int me0 = I.emulated ? 0 : I.rank0;
-    const SymmBlock* b = find_symm(ranks[0].recv, total, &direct_off);
-    bool ok = b != nullptr && direct_off % 16 == 0;
-    for (int lr = 0; ok && lr < I.nlocal; ++lr) {
-      const RankArgs& a = ranks[(size_t)lr];
-      const char* rb = (const char*)b->peer(me0 + lr) + direct_off;
-      const char* sb = (const char*)a.send;
-      ok = a.recv == (const void*)rb && sb != nullptr;
-      if (!ok) break;
-      const size_t sbytes = d.kind == DevColl::allgather ? P.count : total;
-      const bool overlaps = sb < rb + total && rb < sb + sbytes;
-      const bool in_place_ag = d.kind == DevColl::allgather && sb == rb + (size_t)(me0 + lr) * P.count;
-      if (overlaps && !in_place_ag) ok = false;  // an in-place alltoall needs the staged path
+  // Small uniform allreduce / reduce_scatter / allgather / alltoall travel as low-latency packets.
+  // Eligibility depends on facts every rank shares (operation, count, type), so the ranks agree.
+  {
+    const bool ll_kind = d.kind == DevColl::allreduce || d.kind == DevColl::reduce_scatter ||
+                         d.kind == DevColl::allgather || d.kind == DevColl::alltoall;
+    const size_t pair_bytes = P.count * esz;  // what one rank sends to another
+    const bool fits = ll_kind && !d.vector && p > 1 && in == wire && wire == out && P.count > 0 &&
+                      pair_bytes <= kLLPayloadBytes && ll_supported(d.kind, wire, d.op);
+    const bool forced = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::ll : d.path == CollPath::ll;
+    const bool automatic = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::automatic : d.path == CollPath::automatic;
+    if (forced && !fits)
+      throw_al_exception("the low-latency path was requested but the operation does not qualify (uniform allreduce / "
+                         "reduce_scatter / allgather / alltoall of at most ", kLLPayloadBytes, " bytes per pair of ranks)");
+    if (fits && (forced || (automatic && pair_bytes <= tn.ll_max_bytes))) {
+      LLParams L{};
+      L.ws = I.ws;
+      for (int lr = 0; lr < I.nlocal; ++lr) {
+        L.send[I.rank0 + lr] = ranks[(size_t)lr].send;
+        L.recv[I.rank0 + lr] = ranks[(size_t)lr].recv;
+      }
+      L.count = P.count;
+      L.seq = P.seq;
+      L.timeout_ns = P.timeout_ns;
+      L.scale = P.scale;
+      L.int_div = P.int_div;
+      L.kind = P.kind;
+      L.op = P.op;
+      L.rank0 = I.rank0;
+      const size_t groups = ceil_div(pair_bytes, (size_t)16);
+      int lctas = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(groups, (size_t)256), (size_t)tn.ll_max_ctas));
+      if (I.nlocal > 1) lctas = std::max(1, std::min(lctas, I.sm_count / I.nlocal));
+      const int lthreads = groups <= 64 ? 64 : (groups <= 128 ? 128 : 256);
+      I.order_after_previous(stream);
+      I.stats.ops++;
+      I.stats.bytes += bytes ? bytes : pair_bytes;
+      I.stats.kernels++;
+      I.stats.ll++;
+      launch_ll(L, wire, lctas, lthreads, I.nlocal, stream);
+      return;
     }
-    if (ok) direct_block = b;
+  }
+
+  // Registered buffers: reduce_scatter (send side) and allgather / alltoall / bcast (receive side) run
+  // straight on them.  The decision looks at this rank's buffers only; the kernels compare protocols
+  // when they enter the operation, so ranks that disagree stop with a clear error.
+  bool use_window = false;
+  WinParams Wp{};
+  {
+    const bool kind_ok = d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather ||
+                         d.kind == DevColl::alltoall || d.kind == DevColl::bcast;
+    const size_t slice = P.count * esz;                                    // bytes per rank slice (bcast: the vector)
+    const size_t total = d.kind == DevColl::bcast ? slice : slice * (size_t)p;
+    const bool wanted = d.path == CollPath::window || (d.path == CollPath::automatic && tn.window_enable && total >= tn.window_min_bytes);
+    if (d.path == CollPath::window && (!kind_ok || d.vector || !(in == wire && wire == out) || !window_supported(d.kind, wire, d.op)))
+      throw_al_exception("the window path serves uniform reduce_scatter (f32 / f16 / bf16: sum, avg, min, max), allgather, alltoall and bcast only");
+    if (kind_ok && wanted && !d.vector && p > 1 && in == wire && wire == out && P.count > 0 &&
+        window_supported(d.kind, wire, d.op) && (d.kind != DevColl::reduce_scatter || slice % 16 == 0)) {
+      bool ok = true;
+      for (int lr = 0; ok && lr < I.nlocal; ++lr) {
+        const int r = I.rank0 + lr;
+        const RankArgs& a = ranks[(size_t)lr];
+        const char* sb = (const char*)a.send;
+        const char* rb = (const char*)a.recv;
+        size_t off = 0;
+        int w = -1;
+        Wp.send[r] = a.send;
+        Wp.recv[r] = a.recv;
+        switch (d.kind) {
+          case DevColl::reduce_scatter:
+            // in place (the result overwrites the start of the input other ranks still read) stays staged
+            ok = sb && rb && !(rb < sb + total && sb < rb + slice) && (w = find_window(sb, total, &off, lr)) >= 0;
+            if (ok) Wp.send_desc[r] = make_desc(w, off);
+            break;
+          case DevColl::allgather: {
+            const bool in_place = sb == rb + (size_t)r * slice;
+            ok = sb && rb && (in_place || !(sb < rb + total && rb < sb + slice)) && (w = find_window(rb, total, &off, lr)) >= 0;
+            if (ok) Wp.recv_desc[r] = make_desc(w, off);
+            break;
+          }
+          case DevColl::alltoall:
+            ok = sb && rb && !(sb < rb + total && rb < sb + total) && (w = find_window(rb, total, &off, lr)) >= 0;
+            if (ok) Wp.recv_desc[r] = make_desc(w, off);
+            break;
+          case DevColl::bcast:
+            ok = rb && (w = find_window(rb, total, &off, lr)) >= 0;
+            if (ok) { Wp.recv_desc[r] = make_desc(w, off); Wp.send[r] = a.recv; }
+            break;
+          default: ok = false;
+        }
+      }
+      use_window = ok;
+    }
+    if (d.path == CollPath::window && !use_window)
+      throw_al_exception("the window path was requested but this rank's buffer is not registered (or the buffers overlap)");
   }
 
   // Large uniform reduce_scatter / allgather / alltoall run pipelined: smaller chunks, half of the
   // grid publishing while the other half consumes.
   size_t slot_e = cap_e;
   if ((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
-      p > 1 && !direct_block && P.count * esz >= tn.pipeline_min_bytes) {
+      p > 1 && !use_window && P.count * esz >= tn.pipeline_min_bytes) {
     size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {
@@ -423,16 +569,24 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     if (algo == AllreduceAlgo::one_shot) I.stats.ar_one_shot++;
     else I.stats.ar_two_shot++;
   }
-  if (direct_block) {
-    bool bulk = tn.direct_bulk;
-    for (const RankArgs& a : ranks) bulk = bulk && (uintptr_t)a.send % 16 == 0;
-    for (int r = 0; r < p; ++r) {
-      P.recv[r] = (char*)direct_block->peer(r) + direct_off;
-      P.local_chunks[r] = 1;
-    }
-    const int dctas = bulk ? std::max(1, std::min(cap, 2 * tn.bulk_pub_ctas)) : ctas;
-    I.stats.direct++;
-    launch_direct(P, bulk, dctas, threads, I.nlocal, stream);
+  if (use_window) {
+    Wp.ws = I.ws;
+    Wp.windows = I.table_dev;
+    Wp.count = P.count;
+    Wp.seq = P.seq;
+    Wp.timeout_ns = P.timeout_ns;
+    Wp.scale = P.scale;
+    Wp.int_div = P.int_div;
+    Wp.kind = P.kind;
+    Wp.op = P.op;
+    Wp.root = P.root;
+    Wp.rank0 = I.rank0;
+    Wp.allow_multimem = tn.window_multimem ? 1 : 0;
+    const size_t moved = P.count * esz * (d.kind == DevColl::alltoall ? (size_t)p : 1);
+    int wctas = d.ctas > 0 ? d.ctas : (int)std::max<size_t>(1, std::min<size_t>(ceil_div(moved, (size_t)32768), (size_t)tn.window_ctas));
+    if (I.nlocal > 1) wctas = std::max(1, std::min(wctas, I.sm_count / I.nlocal));
+    I.stats.window++;
+    launch_window(Wp, wire, d.op, wctas, threads, I.nlocal, stream);
     return;
   }
   // Opt-in: the pipelined schedule with the copy engine moving the data.  A rank whose buffers do
@@ -548,6 +702,7 @@ void* DeviceCommunicator::symm_alloc(size_t bytes) {
   else b = SymmBlock::create(group_, padded, true);
   void* ptr = b->peer(I.emulated ? 0 : I.rank0);
   std::lock_guard<std::mutex> lock(I.mu);
+  I.add_block_window(b.get());
   I.user_blocks.push_back(std::move(b));
   return ptr;
 }
@@ -568,6 +723,12 @@ void DeviceCommunicator::symm_free(void* ptr) {
   if (!victim) throw_al_exception("symm_free: pointer was not returned by symm_alloc of this communicator");
   AL_CHECK_CUDA(cudaDeviceSynchronize());
   if (!I.emulated) group_.barrier();  // nobody may still be addressing the block
+  {
+    std::lock_guard<std::mutex> lock(I.mu);
+    for (int w = 0; w < kMaxWindows; ++w)
+      if (I.windows[w].used && I.windows[w].block == victim.get()) I.clear_window(w);
+    I.push_table();
+  }
   victim.reset();
 }
 
@@ -599,6 +760,144 @@ void* DeviceCommunicator::symm_peer_ptr(int index, int peer, size_t offset) cons
   if (index < 0 || (size_t)index >= I.user_blocks.size() || peer < 0 || peer >= I.p) return nullptr;
   if (offset >= I.user_blocks[(size_t)index]->bytes()) return nullptr;
   return (char*)I.user_blocks[(size_t)index]->peer(peer) + offset;
+}
+
+// ---------------------------------------------------------------------------
+// registered buffers
+// ---------------------------------------------------------------------------
+namespace {
+struct RegMsg {
+  int kind;            // 0: cannot be shared, 1: inside symmetric block `block_index`, 2: CUDA IPC handle
+  int block_index;
+  size_t offset;       // of the buffer inside the block / the IPC allocation
+  size_t bytes;
+  cudaIpcMemHandle_t handle;
+};
+}  // namespace
+
+int DeviceCommunicator::register_buffer(void* ptr, size_t bytes) {
+  Impl& I = *impl_;
+  if (I.emulated) throw_al_exception("register_buffer: use register_buffers_emulated on an emulated communicator");
+  check_status();
+  RegMsg mine{};
+  mine.bytes = bytes;
+  size_t off = 0;
+  if (ptr && bytes) {
+    if (find_symm(ptr, bytes, &off)) {
+      mine.kind = 1;
+      mine.block_index = symm_index(ptr);
+      mine.offset = off;
+    } else {
+      CUdeviceptr base = 0;
+      size_t size = 0;
+      const auto& dr = cuda::drv();
+      if (dr.MemGetAddressRange && dr.MemGetAddressRange(&base, &size, (CUdeviceptr)ptr) == CUDA_SUCCESS &&
+          cudaIpcGetMemHandle(&mine.handle, (void*)base) == cudaSuccess) {
+        mine.kind = 2;
+        mine.offset = (size_t)((CUdeviceptr)ptr - base);
+      } else {
+        (void)cudaGetLastError();  // memory that CUDA IPC cannot export (e.g. a VMM allocation): not registered
+      }
+    }
+  }
+  const int p = I.p;
+  std::vector<RegMsg> all((size_t)p);
+  group_.allgather(&mine, all.data(), sizeof(RegMsg));
+  bool ok = true;
+  for (const auto& m : all) ok = ok && m.kind != 0;
+  std::lock_guard<std::mutex> lock(I.mu);
+  const int w = ok ? I.free_window() : -1;
+  if (w < 0) return -1;  // consistent on every rank: same messages, same table occupancy
+  Impl::Window& W = I.windows[w];
+  bool same_block = true;
+  for (int r = 0; r < p; ++r) {
+    const RegMsg& m = all[(size_t)r];
+    same_block = same_block && m.kind == 1 && m.block_index == all[0].block_index && m.offset == all[0].offset;
+    char* addr = nullptr;
+    if (r == I.rank0) {
+      addr = (char*)ptr;
+    } else if (m.kind == 1) {
+      addr = (char*)symm_peer_ptr(m.block_index, r, m.offset);
+    } else {
+      void* base = nullptr;
+      if (cudaIpcOpenMemHandle(&base, m.handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) {
+        W.opened.push_back(base);
+        addr = (char*)base + m.offset;
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
+    I.table_host.peer[w][r] = addr;
+    I.table_host.bytes[w][r] = m.bytes;
+  }
+  // A mapping that failed on any rank voids the window on every rank.
+  int good = 1;
+  for (int r = 0; r < p; ++r) good = good && I.table_host.peer[w][r] != nullptr;
+  std::vector<int> goods((size_t)p);
+  group_.allgather(&good, goods.data(), sizeof(int));
+  for (int g : goods) good = good && g;
+  if (!good) {
+    I.clear_window(w);
+    return -1;
+  }
+  W.used = true;
+  W.local[I.rank0] = ptr;
+  if (same_block && all[0].kind == 1) {
+    const SymmBlock* b = I.user_blocks[(size_t)all[0].block_index].get();
+    if (b->mc()) I.table_host.mc[w] = (char*)b->mc() + all[0].offset;
+  }
+  I.push_table();
+  return w;
+}
+
+int DeviceCommunicator::register_buffers_emulated(const std::vector<void*>& ptrs, size_t bytes) {
+  Impl& I = *impl_;
+  if (!I.emulated) throw_al_exception("register_buffers_emulated: not an emulated communicator");
+  if ((int)ptrs.size() != I.p) throw_al_exception("register_buffers_emulated: one buffer per rank expected");
+  std::lock_guard<std::mutex> lock(I.mu);
+  const int w = I.free_window();
+  if (w < 0) return -1;
+  Impl::Window& W = I.windows[w];
+  W.used = true;
+  for (int r = 0; r < I.p; ++r) {
+    W.local[r] = ptrs[(size_t)r];
+    I.table_host.peer[w][r] = (char*)ptrs[(size_t)r];
+    I.table_host.bytes[w][r] = bytes;
+  }
+  I.push_table();
+  return w;
+}
+
+void DeviceCommunicator::unregister_buffer(void* ptr) {
+  Impl& I = *impl_;
+  int w = -1;
+  {
+    std::lock_guard<std::mutex> lock(I.mu);
+    for (int i = 0; i < kMaxWindows && w < 0; ++i)
+      if (I.windows[i].used && !I.windows[i].block && I.windows[i].local[I.emulated ? 0 : I.rank0] == ptr) w = i;
+  }
+  // Collective: every rank drains its work and all meet before any mapping goes away.
+  AL_CHECK_CUDA(cudaDeviceSynchronize());
+  if (!I.emulated) group_.barrier();
+  if (w < 0) return;  // was never registered (registration may have been refused on every rank)
+  std::lock_guard<std::mutex> lock(I.mu);
+  I.clear_window(w);
+  I.push_table();
+}
+
+int DeviceCommunicator::find_window(const void* ptr, size_t bytes, size_t* offset, int local_rank) const {
+  const Impl& I = *impl_;
+  const int r = I.rank0 + local_rank;
+  for (int w = 0; w < kMaxWindows; ++w) {
+    if (!I.windows[w].used) continue;
+    const char* base = (const char*)I.windows[w].local[r];
+    if (!base) continue;
+    if ((const char*)ptr >= base && (const char*)ptr + bytes <= base + I.table_host.bytes[w][r]) {
+      if (offset) *offset = (size_t)((const char*)ptr - base);
+      return w;
+    }
+  }
+  return -1;
 }
 
 uint64_t DeviceCommunicator::wait_timeout_ns() const { return impl_->timeout_ns; }

@@ -16,47 +16,6 @@ namespace ht {
 
 namespace {
 
-struct Extent { size_t send_elems = 0, recv_elems = 0; };
-
-/** How many elements of the (resolved) send and receive buffers the operation touches. */
-Extent extent_of(const Resolved& r, int rank, int size) {
-  Extent e;
-  const size_t p = (size_t)size;
-  auto span = [&](const std::vector<size_t>& c, const std::vector<size_t>& d) {
-    size_t m = 0;
-    for (size_t i = 0; i < c.size(); ++i) m = std::max(m, (d.empty() ? 0 : d[i]) + c[i]);
-    return m;
-  };
-  switch (r.kind) {
-    case OpKind::allreduce: case OpKind::reduce: e.send_elems = e.recv_elems = r.count; break;
-    case OpKind::bcast: e.send_elems = rank == r.root ? r.count : 0; e.recv_elems = rank == r.root ? 0 : r.count; break;
-    case OpKind::reduce_scatter:
-      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
-      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
-      break;
-    case OpKind::allgather:
-      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
-      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
-      break;
-    case OpKind::alltoall:
-      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = span(r.recv_counts, r.recv_displs); }
-      else { e.send_elems = e.recv_elems = r.count * p; }
-      break;
-    case OpKind::gather:
-      if (r.vector) { e.send_elems = r.send_counts[(size_t)rank]; e.recv_elems = span(r.recv_counts, r.recv_displs); }
-      else { e.send_elems = r.count; e.recv_elems = r.count * p; }
-      break;
-    case OpKind::scatter:
-      if (r.vector) { e.send_elems = span(r.send_counts, r.send_displs); e.recv_elems = r.recv_counts[(size_t)rank]; }
-      else { e.send_elems = r.count * p; e.recv_elems = r.count; }
-      break;
-    case OpKind::barrier: break;
-  }
-  if (!r.send) e.send_elems = 0;
-  if (!r.recv) e.recv_elems = 0;
-  return e;
-}
-
 /** Engine state shared by collectives and point-to-point: stage 0 waits for the D2H flag. */
 class HTState final : public AlState {
  public:

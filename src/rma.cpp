@@ -158,6 +158,20 @@ void put(const void* src, int dest, void* dest_remote, size_t bytes, DeviceCommu
   device::launch_put(dest_remote, src, bytes, ctas, comm.get_stream());
 }
 
+void get(void* dst, int src_rank, const void* src_remote, size_t bytes, DeviceCommunicator& comm) {
+  if (src_rank < 0 || bytes == 0) return;
+  if (!src_remote) throw_al_exception("get: source buffer is null (the peer attached no buffer)");
+  comm.check_status();
+  if (src_rank == comm.rank() && !comm.is_emulated()) {
+    AL_CHECK_CUDA(cudaMemcpyAsync(dst, src_remote, bytes, cudaMemcpyDeviceToDevice, comm.get_stream()));
+    return;
+  }
+  // The same copy kernel as put with the roles of the pointers exchanged: remote loads, local stores.
+  // More CTAs than a put of the same size: a load over NVLink occupies its thread for the round trip.
+  const int ctas = (int)std::max<size_t>(1, std::min<size_t>((bytes + 32767) / 32768, (size_t)tuning().max_ctas));
+  device::launch_put(dst, src_remote, bytes, ctas, comm.get_stream());
+}
+
 }  // namespace rma
 }  // namespace internal
 }  // namespace Al

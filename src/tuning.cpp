@@ -45,8 +45,12 @@ void Tuning::load_from_env() {
   bulk_pipeline = env_long("AL_DEV_BULK_PIPELINE", bulk_pipeline) != 0;
   bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
   bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
-  direct_symmetric = env_long("AL_DEV_DIRECT", direct_symmetric) != 0;
-  direct_bulk = env_long("AL_DEV_DIRECT_BULK", direct_bulk) != 0;
+  ll_max_bytes = (size_t)env_long("AL_LL_MAX", (long)ll_max_bytes);
+  ll_max_ctas = (int)env_long("AL_LL_CTAS", ll_max_ctas);
+  window_enable = env_long("AL_WINDOW", window_enable) != 0;
+  window_min_bytes = (size_t)env_long("AL_WINDOW_MIN", (long)window_min_bytes);
+  window_ctas = (int)env_long("AL_WINDOW_CTAS", window_ctas);
+  window_multimem = env_long("AL_WINDOW_MULTIMEM", window_multimem) != 0;
   trace = env_long("AL_TRACE", trace) != 0;
   debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
   signal_handler = env_long("AL_DISABLE_SIGNAL_HANDLER", 0) == 0;
@@ -109,8 +113,12 @@ std::string Tuning::describe() const {
      << "bulk_pipeline = " << bulk_pipeline << "\n"
      << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
      << "bulk_con_ctas = " << bulk_con_ctas << "\n"
-     << "direct_symmetric = " << direct_symmetric << "\n"
-     << "direct_bulk = " << direct_bulk << "\n"
+     << "ll_max_bytes = " << ll_max_bytes << "\n"
+     << "ll_max_ctas = " << ll_max_ctas << "\n"
+     << "window_enable = " << window_enable << "\n"
+     << "window_min_bytes = " << window_min_bytes << "\n"
+     << "window_ctas = " << window_ctas << "\n"
+     << "window_multimem = " << window_multimem << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
      << "signal_handler = " << signal_handler << "\n"

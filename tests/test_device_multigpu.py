@@ -17,7 +17,7 @@ def _ngpu():
                                 "alltoall", "alltoallv", "bcast", "gather", "scatterv", "barrier", "send", "sendrecv",
                                 "multisendrecv"])
 def test_ops_device_backend(bin_dir, op):
-    n = min(_ngpu(), 4)
+    n = _ngpu()
     if n < 2:
         pytest.skip("needs >= 2 GPUs")
     env = {**os.environ, "NCCL_NVLS_ENABLE": "0"}
@@ -39,8 +39,6 @@ def test_rma_ring_exchange_and_bandwidth(bin_dir):
         assert r.returncode == 0, " ".join(cmd) + r.stdout + r.stderr
 
 
-@pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
-                    reason="written after the last GPU run; set AL_TEST_UNVERIFIED=1 to run it")
 def test_rma_halo_exchange_on_a_2d_grid(bin_dir):
     n = min(_ngpu(), 4)
     if n < 2:
@@ -50,8 +48,6 @@ def test_rma_halo_exchange_on_a_2d_grid(bin_dir):
     assert r.returncode == 0 and "rma halo" in r.stdout and "FAIL" not in r.stdout, r.stdout + r.stderr
 
 
-@pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
-                    reason="written after the last GPU run; set AL_TEST_UNVERIFIED=1 to run it")
 def test_torch_distributed_backend_on_gpus(bin_dir):
     import sys
     from pathlib import Path
@@ -62,6 +58,21 @@ def test_torch_distributed_backend_on_gpus(bin_dir):
     r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "240", sys.executable, str(worker), "cuda"],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.count("torch backend ok") == n, r.stdout + r.stderr
+
+
+def test_data_paths_over_real_ranks(bin_dir):
+    """Packets, staged, pipelined and window paths, registration through CUDA IPC, multimem on symmetric
+    buffers, the NVLS tail rule, Get, from_ranks and the path-mismatch error, on every GPU of the machine."""
+    import sys
+    from pathlib import Path
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    worker = Path(__file__).resolve().parent / "workers" / "device_paths_worker.py"
+    env = {**os.environ, "AL_TEST_LARGE": os.environ.get("AL_TEST_LARGE", "1")}
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "420", sys.executable, str(worker)],
+                       capture_output=True, text=True, timeout=480, env=env)
+    assert r.returncode == 0 and r.stdout.count("device paths ok") == n, r.stdout[-4000:] + r.stderr[-4000:]
 
 
 def test_data_parallel_matches_single_process(bin_dir):

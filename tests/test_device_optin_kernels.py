@@ -1,22 +1,13 @@
-"""The opt-in kernels on ONE GPU with emulated ranks: the bulk-copy pipeline
-(kernels/bulk_pipeline.cu; tuning entry ``bulk_pipeline`` / ``AL_DEV_BULK_PIPELINE=1``) and the direct
-allgather / alltoall into symmetric receive buffers (kernels/direct.cu; ``direct_symmetric`` /
-``AL_DEV_DIRECT=1``, with ``direct_bulk`` / ``AL_DEV_DIRECT_BULK=1`` for its copy-engine flavour).
-
-They are off by default and so is this file: it runs only with ``AL_TEST_UNVERIFIED=1`` in the
-environment.  Results are compared with plain PyTorch references, exactly as for the generic kernel
-in test_device_emulated.py.
+"""The opt-in bulk-copy pipeline on ONE GPU with emulated ranks (kernels/bulk_pipeline.cu; tuning entry
+``bulk_pipeline`` / ``AL_DEV_BULK_PIPELINE=1``): large uniform reduce_scatter / allgather / alltoall whose
+data is moved by the bulk copy engine (cp.async.bulk) instead of SM store loops.  Off by default, switched
+on for this file.  Results are compared with plain PyTorch references, exactly as for the generic kernel in
+test_device_emulated.py.
 """
-import os
-
 import pytest
 import torch
 
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("AL_TEST_UNVERIFIED") != "1",
-                       reason="opt-in kernel: set AL_TEST_UNVERIFIED=1 to test them"),
-]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(scope="module")
@@ -25,7 +16,7 @@ def al():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     al.init()
-    old = {k: al.get_tuning(k) for k in ("pipeline_min_bytes", "bulk_pipeline", "direct_symmetric", "direct_bulk")}
+    old = {k: al.get_tuning(k) for k in ("pipeline_min_bytes", "bulk_pipeline")}
     al.set_tuning("pipeline_min_bytes", 16384)
     al.set_tuning("bulk_pipeline", 1)
     yield al
@@ -72,7 +63,7 @@ def test_bf16_reduce_scatter_and_fallback_for_odd_sizes(al):
     p = 4
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
-    n = 400_000
+    n = 4_000_000  # 8 MB per rank slice: more than one pipeline chunk
     xs = [rand(n * p, 330 + r).to(torch.bfloat16) for r in range(p)]
     rs = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(p)]
     comm.reduce_scatter(xs, rs)
@@ -91,55 +82,3 @@ def test_bf16_reduce_scatter_and_fallback_for_odd_sizes(al):
     for r in range(p):
         assert torch.equal(outs[r], torch.cat(ss))
     comm.close()
-
-
-@pytest.mark.parametrize("bulk", [0, 1])
-@pytest.mark.parametrize("p", [2, 8])
-def test_direct_allgather_alltoall_into_symmetric_buffers(al, p, bulk):
-    al.set_tuning("direct_symmetric", 1)
-    al.set_tuning("direct_bulk", bulk)
-    try:
-        comm = al.DeviceComm(emulate=p)
-        comm.set_timeout_ms(2000)
-        for n in (4, 1000, 1_500_004):  # per-rank slice in floats: multiples of 16 bytes
-            outs = comm.symm_empty((n * p,), torch.float32)
-            for it in range(2):
-                before = comm.stats()["direct"]
-                for o in outs:
-                    o.fill_(-1.0)
-                ss = [rand(n, 400 + r + it) for r in range(p)]
-                comm.allgather(ss, outs)
-                torch.cuda.synchronize()
-                assert comm.status()["code"] == 0, comm.status()
-                assert comm.stats()["direct"] == before + 1
-                for r in range(p):
-                    assert torch.equal(outs[r], torch.cat(ss))
-                xs = [rand(n * p, 410 + r + it) for r in range(p)]
-                comm.alltoall(xs, outs)
-                small = [torch.full((3,), float(r), device="cuda") for r in range(p)]
-                comm.allreduce(small)  # a staged operation right after
-                torch.cuda.synchronize()
-                assert comm.stats()["direct"] == before + 2
-                for r in range(p):
-                    assert torch.equal(outs[r], torch.cat([xs[q][r * n:(r + 1) * n] for q in range(p)]))
-                    assert torch.all(small[r] == sum(range(p)))
-            # in-place allgather: every rank's contribution already sits at its place
-            for r in range(p):
-                outs[r].zero_()
-                outs[r][r * n:(r + 1) * n] = float(r + 1)
-            comm.allgather([outs[r][r * n:(r + 1) * n] for r in range(p)], outs)
-            torch.cuda.synchronize()
-            want = torch.cat([torch.full((n,), float(r + 1), device="cuda") for r in range(p)])
-            for r in range(p):
-                assert torch.equal(outs[r], want)
-            # a private receive buffer takes the staged path
-            before = comm.stats()["direct"]
-            priv = [torch.zeros(n * p, device="cuda") for _ in range(p)]
-            comm.allgather([rand(n, 420 + r) for r in range(p)], priv)
-            torch.cuda.synchronize()
-            assert comm.stats()["direct"] == before
-            comm.symm_free(outs)
-        comm.close()
-    finally:
-        al.set_tuning("direct_symmetric", 0)
-        al.set_tuning("direct_bulk", 0)

@@ -66,6 +66,8 @@ def _declare(lib) -> None:
         "al_dev_comm_set_timeout_ms": (i, [vp, d]), "al_dev_comm_stats": (i, [vp, u64p]),
         "al_dev_comm_status": (i, [vp, u64p]),
         "al_dev_collective": (i, [vp, i, i, vpp, vpp, sz, i, i, i, i, i, i, i, szp, szp, szp, szp, d, i, i, vp, vpp]),
+        "al_dev_exchange_rows": (i, [vp, i, vpp, vpp, vpp, vpp, sz, sz, sz, szp, szp, szp, szp, szp, szp, vp, vpp]),
+        "al_dev_latency_breakdown": (i, [vp, i, vp, vp, sz, i, i, i, i, i, vp, C.POINTER(C.c_double)]),
         "al_dev_register": (i, [vp, vp, sz]), "al_dev_register_emulated": (i, [vp, vpp, i, sz]),
         "al_dev_unregister": (i, [vp, vp]),
         "al_dev_time_collective": (i, [vp, i, vp, vp, sz, i, i, i, i, vp, C.POINTER(C.c_float)]),

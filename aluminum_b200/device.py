@@ -83,10 +83,10 @@ class DeviceComm:
         check(self._lib.al_dev_comm_abort(self._h, why.encode()))
 
     def stats(self) -> dict:
-        out = (C.c_uint64 * 11)()
+        out = (C.c_uint64 * 12)()
         check(self._lib.al_dev_comm_stats(self._h, out))
         names = ["ops", "bytes", "kernels", "timeouts", "one_shot", "two_shot", "nvls", "nvls_zero_copy", "bulk_pipeline",
-                 "window", "ll"]
+                 "window", "ll", "rows"]
         return dict(zip(names, [int(v) for v in out]))
 
     def status(self) -> dict:
@@ -232,6 +232,59 @@ class DeviceComm:
                                                C.c_void_p(recv.data_ptr()), int(count), _code(recv), OPS[op],
                                                int(warmup), int(iters), self._stream(stream), out))
         return [float(v) for v in out]
+
+    def exchange_rows(self, send, recv, row_bytes: int, send_row_stride: int, recv_row_stride: int, send_rows,
+                      send_first, send_peer_off, recv_rows, recv_first, recv_peer_off, send_idx=None, recv_idx=None,
+                      nonblocking=False, stream=None):
+        """Alltoall(v) of strided or index-selected rows with the pack / unpack fused into the kernel.
+
+        Row ``k`` of what this rank sends to peer ``d`` is read at byte ``send_peer_off[d] + id * send_row_stride`` of
+        ``send`` with ``id = send_first[d] + k`` (or ``send_idx[send_first[d] + k]`` when an int64 index tensor is
+        given); row ``k`` received from rank ``r`` is written at ``recv_peer_off[r] + id * recv_row_stride`` of
+        ``recv`` likewise.  Tables have one entry per rank (one row of entries per local rank in emulation)."""
+        sends, recvs = self._as_list(send), self._as_list(recv)
+        sidx = self._as_list(send_idx) if send_idx is not None else None
+        ridx = self._as_list(recv_idx) if recv_idx is not None else None
+
+        def table(t):
+            rows = [t] if (self.nlocal == 1 and t and not isinstance(t[0], (list, tuple))) else t
+            flat = [int(v) for row in rows for v in row]
+            if len(flat) != self.nlocal * self.size:
+                raise AlError(f"exchange_rows: tables need {self.nlocal} row(s) of {self.size} entries")
+            return size_array(flat)
+
+        def idx_ptrs(lst):
+            if lst is None:
+                return None
+            arr = (C.c_void_p * self.nlocal)()
+            for i, t in enumerate(lst):
+                if t is not None and (str(t.dtype) != "torch.int64" or not t.is_cuda or not t.is_contiguous()):
+                    raise AlError("exchange_rows: index tensors must be contiguous CUDA int64 tensors")
+                arr[i] = t.data_ptr() if t is not None else None
+            return arr
+
+        sp = (C.c_void_p * self.nlocal)(*[t.data_ptr() for t in sends])
+        rp = (C.c_void_p * self.nlocal)(*[t.data_ptr() for t in recvs])
+        req = C.c_void_p(None)
+        check(self._lib.al_dev_exchange_rows(
+            self._h, self.nlocal, sp, rp, idx_ptrs(sidx), idx_ptrs(ridx), int(row_bytes), int(send_row_stride),
+            int(recv_row_stride), table(send_rows), table(send_first), table(send_peer_off), table(recv_rows),
+            table(recv_first), table(recv_peer_off), self._stream(stream), C.byref(req) if nonblocking else None))
+        return Request(req, True, (sends, recvs, sidx, ridx)) if nonblocking else None
+
+    def latency_breakdown(self, kind: str, send, recv, count: int, algo: str = "auto", warmup: int = 20,
+                          iters: int = 100, op: str = "sum", stream=None) -> dict:
+        """Median microseconds of one small collective, split into host enqueue, launch overhead and the kernel's
+        phases (entry -> data sent -> first data seen -> exit), from %globaltimer stamps inside the kernel."""
+        out = (C.c_double * 6)()
+        code = ALGOS[algo] if kind == "allreduce" else PATHS[algo]
+        check(self._lib.al_dev_latency_breakdown(self._h, KINDS[kind], C.c_void_p(send.data_ptr()),
+                                                 C.c_void_p(recv.data_ptr()), int(count), _code(recv), OPS[op], code,
+                                                 int(warmup), int(iters), self._stream(stream), out))
+        names = ["event_us", "host_enqueue_us", "kernel_send_us", "kernel_wait_us", "kernel_finish_us", "kernel_us"]
+        d = dict(zip(names, [float(v) for v in out]))
+        d["launch_overhead_us"] = d["event_us"] - d["kernel_us"]
+        return d
 
     # vector forms: counts / displacements in elements, one row per local rank in emulation
     def reduce_scatterv(self, send, recv, counts, op="sum", **kw):

@@ -11,15 +11,16 @@ import torch
 from ._util import local_ranks, unwrap, wrap
 
 
-def ring_pass(comm, bufs_send, bufs_recv):
-    """Every rank sends its buffer to rank+1 and receives rank-1's (one fused kernel launch)."""
+def ring_pass(comm, bufs_send, bufs_recv, nonblocking: bool = False):
+    """Every rank sends its buffer to rank+1 and receives rank-1's (one fused kernel launch).  With
+    ``nonblocking`` the transfer runs on the communicator's internal stream and a request is returned."""
     p = comm.size
     sends, recvs = wrap(comm, bufs_send), wrap(comm, bufs_recv)
     items = []
     for i, r in enumerate(local_ranks(comm)):
         items.append((True, (r + 1) % p, sends[i], r))
         items.append((False, (r - 1) % p, recvs[i], r))
-    comm.p2p(items)
+    return comm.p2p(items, nonblocking=nonblocking)
 
 
 def ring_attention(comm, q, k, v):
@@ -32,6 +33,8 @@ def ring_attention(comm, q, k, v):
     kv = [torch.stack([a, b]).contiguous() for a, b in zip(ks, vs)]
     nxt = [torch.empty_like(t) for t in kv]
     for step in range(p):
+        # Double buffering: the next key / value block travels (internal stream) while this one is used.
+        req = ring_pass(comm, kv, nxt, nonblocking=True) if step + 1 < p else None
         for i in range(len(qs)):
             kk, vv = kv[i][0].float(), kv[i][1].float()
             s = torch.einsum("qhd,khd->qhk", qs[i].float(), kk) * scale
@@ -40,7 +43,7 @@ def ring_attention(comm, q, k, v):
             acc[i] = acc[i] * torch.exp(lse[i] - new_lse).unsqueeze(-1) + \
                 torch.einsum("qhk,khd->qhd", torch.exp(s - new_lse.unsqueeze(-1)), vv)
             lse[i] = new_lse
-        if step + 1 < p:
-            ring_pass(comm, kv, nxt)  # double buffering: compute on one pair while the other is in flight
+        if req is not None:
+            req.wait()  # the compute stream waits for the transfer; the host does not
             kv, nxt = nxt, kv
     return unwrap(comm, [a.to(qs[0].dtype) for a in acc], q)

@@ -94,7 +94,7 @@ const char* al_dev_comm_backing(void* comm);
 int al_dev_comm_set_timeout_ms(void* comm, double ms);
 /** Every later call on the communicator fails (why may be NULL). */
 int al_dev_comm_abort(void* comm, const char* why);
-/** Fills out[0..10]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, window, ll. */
+/** Fills out[0..11]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, window, ll, rows. */
 int al_dev_comm_stats(void* comm, uint64_t* out);
 /** Status record: out[0]=code, [1]=rank, [2]=peer, [3]=where, [4]=epoch, [5]=seen. Never fails. */
 int al_dev_comm_status(void* comm, uint64_t* out);
@@ -109,6 +109,25 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
                       int dt_in, int dt_wire, int dt_out, int op, int root, int inplace, int vector,
                       const size_t* send_counts, const size_t* send_displs, const size_t* recv_counts,
                       const size_t* recv_displs, double scale, int algo, int ctas, void* stream, void** req_out);
+/**
+ * Alltoall(v) of strided or index-selected rows with the pack / unpack fused in.  Row k of what local rank lr
+ * sends to peer d is read at send[lr] + send_peer_off[d] + id * send_row_stride with id = send_first[d] + k, or
+ * send_idx[lr][send_first[d] + k] when an index array (device memory) is given; the receiving side mirrors it.
+ * The six tables hold nlocal * size entries (a row per local rank); offsets and strides are in bytes.
+ */
+int al_dev_exchange_rows(void* comm, int nlocal, const void* const* send, void* const* recv, const long long* const* send_idx,
+                         const long long* const* recv_idx, size_t row_bytes, size_t send_row_stride, size_t recv_row_stride,
+                         const size_t* send_rows, const size_t* send_first, const size_t* send_peer_off,
+                         const size_t* recv_rows, const size_t* recv_first, const size_t* recv_peer_off, void* stream,
+                         void** req_out);
+/**
+ * Where the time of a small collective goes.  Same loop as al_dev_time_collective, with the kernels'
+ * %globaltimer stamps switched on.  out_us[0..5] = medians in microseconds of: the event-pair time, the host
+ * time inside the enqueueing call, kernel entry -> data sent, data sent -> first data seen, first data seen ->
+ * kernel exit, kernel entry -> exit.  Event time minus kernel time is launch and front-end overhead.
+ */
+int al_dev_latency_breakdown(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op,
+                             int algo, int warmup, int iters, void* stream, double* out_us);
 /**
  * Collective over the communicator: make [ptr, ptr+bytes) of every rank addressable by all ranks (CUDA IPC for
  * cudaMalloc memory; symm_alloc memory is registered already).  Returns the window index (>= 0), -1 when some

@@ -67,6 +67,15 @@ struct CollDesc {
   int ctas = 0;           ///< 0 = choose from the tuning table
 };
 
+/** Arguments of a row exchange for one local rank (see RowsParams in al/device/params.hpp). */
+struct RowArgs {
+  const void* send = nullptr;
+  void* recv = nullptr;
+  const long long* send_idx = nullptr;   ///< device memory, or nullptr
+  const long long* recv_idx = nullptr;
+  std::vector<size_t> send_rows, send_first, send_peer_off, recv_rows, recv_first, recv_peer_off;  ///< one entry per rank
+};
+
 struct P2PDesc {
   bool is_send = false;
   int peer = -1;
@@ -83,6 +92,7 @@ struct CommStats {
   uint64_t bulk_pipeline = 0;   ///< operations run by the bulk-copy pipeline kernel
   uint64_t window = 0;          ///< operations that ran straight on registered buffers (window kernels)
   uint64_t ll = 0;              ///< operations that ran as low-latency packets
+  uint64_t rows = 0;            ///< row exchanges (alltoall with fused pack / unpack)
 };
 
 }  // namespace device
@@ -123,6 +133,12 @@ class DeviceCommunicator {
    */
   void collective(const internal::device::CollDesc& d, const std::vector<internal::device::RankArgs>& ranks,
                   cudaStream_t stream);
+  /**
+   * Alltoall(v) of strided or index-selected rows of `row_bytes` bytes with the pack / unpack fused in
+   * (sequence <-> head transposition, expert dispatch / combine).  Strides in bytes.
+   */
+  void exchange_rows(const std::vector<internal::device::RowArgs>& ranks, size_t row_bytes, size_t send_row_stride,
+                     size_t recv_row_stride, cudaStream_t stream);
   /** Enqueue point-to-point transfers that progress together. */
   void p2p(const std::vector<internal::device::P2PDesc>& items, cudaStream_t stream);
 

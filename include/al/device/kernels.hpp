@@ -50,6 +50,10 @@ void launch_bulk_pipeline(const CollParams& P, DType dt, int ctas, int threads, 
 bool ll_supported(DevColl kind, DType dt, ReductionOperator op);
 void launch_ll(const LLParams& P, DType dt, int ctas, int threads, int local_ranks, cudaStream_t stream);
 
+// ---- row exchange (kernels/rows.cu) --------------------------------------------------------------
+/** Alltoall(v) of strided / indexed rows through the staging area (see RowsParams). */
+void launch_rows(const RowsParams& P, int ctas, int threads, int local_ranks, cudaStream_t stream);
+
 // ---- window kernels (kernels/window.cu) ----------------------------------------------
 /**
  * Uniform reduce_scatter (f32 / f16 / bf16; sum, avg, min, max) and allgather / alltoall / bcast (counts in

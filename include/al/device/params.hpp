@@ -114,7 +114,7 @@ struct DeviceStatus {
  * between the data and a flag (the role of NCCL's LL protocol, which the reference gets from ncclAllReduce
  * & co. at these sizes).  One slot per (parity of the operation number, source rank).
  */
-constexpr size_t kLLPayloadBytes = 16384;
+constexpr size_t kLLPayloadBytes = 65536;
 constexpr size_t kLLSlotBytes = 2 * kLLPayloadBytes;
 constexpr size_t kLLAreaBytes = 2 * (size_t)kMaxRanks * kLLSlotBytes;
 
@@ -209,6 +209,36 @@ struct LLParams {
   int int_div;
   int kind;                      ///< DevColl: allreduce, reduce_scatter, allgather or alltoall
   int op;
+  int rank0;
+};
+
+/**
+ * Row exchange (kernels/rows.cu): an alltoall(v) whose slices are sets of equally long rows that need not be
+ * contiguous.  Row k of what a rank sends to peer d is read at
+ *     send + send_peer_off[d] + id * send_row_stride,   id = send_first[d] + k, or send_idx[send_first[d] + k]
+ * and row k of what it receives from rank r is written at
+ *     recv + recv_peer_off[r] + id * recv_row_stride,   id = recv_first[r] + k, or recv_idx[recv_first[r] + k]
+ * (offsets and strides in bytes, index arrays in device memory).  The pack before and the unpack after an
+ * alltoall - a transposition for sequence <-> head exchanges, a gather / scatter by token index for expert
+ * dispatch / combine - thereby happen inside the kernel's publish and consume steps.
+ */
+struct RowTable {
+  size_t send_rows[kMaxRanks], send_first[kMaxRanks], send_peer_off[kMaxRanks];
+  size_t recv_rows[kMaxRanks], recv_first[kMaxRanks], recv_peer_off[kMaxRanks];
+};
+struct RowsParams {
+  Workspace ws;
+  const void* send[kMaxRanks];
+  void* recv[kMaxRanks];
+  const long long* send_idx[kMaxRanks];  ///< nullptr: rows are taken in order
+  const long long* recv_idx[kMaxRanks];
+  RowTable tab[kMaxRanks];               ///< indexed by rank (local ranks only)
+  uint64_t local_chunks[kMaxRanks];
+  size_t row_bytes;
+  size_t send_row_stride;
+  size_t recv_row_stride;
+  uint64_t seq;
+  uint64_t timeout_ns;
   int rank0;
 };
 

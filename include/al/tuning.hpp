@@ -46,14 +46,15 @@ struct Tuning {
   int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
   int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
   size_t pipeline_min_bytes = size_t{32} << 20;  ///< AL_PIPELINE_MIN: per-rank slice from which reduce_scatter / allgather / alltoall split the grid into publishers and consumers
+  size_t ar_pipeline_min_bytes = size_t{8} << 20;  ///< AL_AR_PIPELINE_MIN: on two ranks the one-shot allreduce splits its grid into pushing and reducing CTAs from this size on
   size_t nvls_pipeline_min_bytes = size_t{128} << 20;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is pipelined from this size on
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
-  int p2p_max_ctas = 16;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)
+  int p2p_max_ctas = 64;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)
   bool bulk_pipeline = false;                  ///< AL_DEV_BULK_PIPELINE: pipelined reduce_scatter / allgather / alltoall move their data with the bulk copy engine (cp.async.bulk) when every buffer is 16-byte aligned
   int bulk_pub_ctas = 16;                      ///< AL_DEV_BULK_PUB_CTAS: publishing CTAs of that kernel (one issuing thread each)
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
-  size_t ll_max_bytes = size_t{8} << 10;       ///< AL_LL_MAX: uniform allreduce / reduce_scatter / allgather / alltoall of at most this many bytes per pair of ranks travel as low-latency packets (hard limit 16 KiB; 0 = never)
-  int ll_max_ctas = 4;                         ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
+  size_t ll_max_bytes = size_t{64} << 10;      ///< AL_LL_MAX: uniform allreduce / reduce_scatter / allgather / alltoall of at most this many bytes per pair of ranks travel as low-latency packets (hard limit 64 KiB; 0 = never)
+  int ll_max_ctas = 16;                        ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
   bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
   size_t window_min_bytes = size_t{256} << 10; ///< AL_WINDOW_MIN: ... from this total message size on (smaller ones are faster through staging: one flag round instead of two)
   int window_ctas = 64;                        ///< AL_WINDOW_CTAS: CTA budget of a window kernel

@@ -2,6 +2,7 @@
 // error codes and raw arrays into the C++ argument structures.
 #include "al/al_c.h"
 
+#include <algorithm>
 #include <sstream>
 
 #include "Al.hpp"
@@ -99,7 +100,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
   X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_bytes) X(ll_max_ctas) X(window_enable) X(window_min_bytes) X(window_ctas) X(window_multimem)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ar_pipeline_min_bytes) X(ll_max_bytes) X(ll_max_ctas) X(window_enable) X(window_min_bytes) X(window_ctas) X(window_multimem)
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {
@@ -274,7 +275,7 @@ int al_dev_comm_stats(void* comm, uint64_t* out) {
     device::CommStats s = ((DeviceCommunicator*)comm)->stats();
     out[0] = s.ops; out[1] = s.bytes; out[2] = s.kernels; out[3] = s.timeouts;
     out[4] = s.ar_one_shot; out[5] = s.ar_two_shot; out[6] = s.ar_nvls; out[7] = s.ar_nvls_zero_copy;
-    out[8] = s.bulk_pipeline; out[9] = s.window; out[10] = s.ll;
+    out[8] = s.bulk_pipeline; out[9] = s.window; out[10] = s.ll; out[11] = s.rows;
   });
 }
 int al_dev_comm_status(void* comm, uint64_t* out) {
@@ -328,6 +329,85 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
       *req_out = new device::Request(device::end_nonblocking(c, s));
     } else {
       c.collective(d, ra, pick_stream(&c, stream));
+    }
+  });
+}
+
+int al_dev_latency_breakdown(void* comm, int kind, const void* send, void* recv, size_t count, int dtype, int op,
+                             int algo, int warmup, int iters, void* stream, double* out_us) {
+  return guard([&] {
+    DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    if (c.is_emulated()) throw_al_exception("al_dev_latency_breakdown: not for emulated communicators");
+    cudaStream_t s = pick_stream(&c, stream);
+    cudaEvent_t e0, e1;
+    AL_CHECK_CUDA(cudaEventCreate(&e0));
+    AL_CHECK_CUDA(cudaEventCreate(&e1));
+    c.enable_stamps(true);
+    const void* sp[1] = {send};
+    void* rp[1] = {recv};
+    std::vector<double> col[6];
+    for (int i = 0; i < warmup + iters; ++i) {
+      c.group().barrier();
+      AL_CHECK_CUDA(cudaEventRecord(e0, s));
+      const double h0 = get_time();
+      if (al_dev_collective(comm, kind, 1, sp, rp, count, dtype, -1, -1, op, 0, 0, 0, nullptr, nullptr, nullptr, nullptr,
+                            1.0, algo, 0, (void*)s, nullptr) != 0)
+        throw_al_exception(g_err);
+      const double h1 = get_time();
+      AL_CHECK_CUDA(cudaEventRecord(e1, s));
+      AL_CHECK_CUDA(cudaEventSynchronize(e1));
+      float ms = 0;
+      AL_CHECK_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+      uint64_t t[4];
+      c.read_stamps(t);
+      if (i < warmup) continue;
+      col[0].push_back(ms * 1e3);
+      col[1].push_back((h1 - h0) * 1e6);
+      col[2].push_back((double)(t[1] - t[0]) * 1e-3);
+      col[3].push_back((double)(t[2] - t[1]) * 1e-3);
+      col[4].push_back((double)(t[3] - t[2]) * 1e-3);
+      col[5].push_back((double)(t[3] - t[0]) * 1e-3);
+    }
+    c.enable_stamps(false);
+    for (int k = 0; k < 6; ++k) {
+      std::sort(col[k].begin(), col[k].end());
+      out_us[k] = col[k].empty() ? 0.0 : col[k][col[k].size() / 2];
+    }
+    AL_CHECK_CUDA(cudaEventDestroy(e0));
+    AL_CHECK_CUDA(cudaEventDestroy(e1));
+  });
+}
+
+int al_dev_exchange_rows(void* comm, int nlocal, const void* const* send, void* const* recv, const long long* const* send_idx,
+                         const long long* const* recv_idx, size_t row_bytes, size_t send_row_stride, size_t recv_row_stride,
+                         const size_t* send_rows, const size_t* send_first, const size_t* send_peer_off,
+                         const size_t* recv_rows, const size_t* recv_first, const size_t* recv_peer_off, void* stream,
+                         void** req_out) {
+  return guard([&] {
+    DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    const size_t p = (size_t)c.size();
+    std::vector<device::RowArgs> ra((size_t)nlocal);
+    for (int lr = 0; lr < nlocal; ++lr) {
+      device::RowArgs& a = ra[(size_t)lr];
+      a.send = send[lr];
+      a.recv = recv[lr];
+      a.send_idx = send_idx ? send_idx[lr] : nullptr;
+      a.recv_idx = recv_idx ? recv_idx[lr] : nullptr;
+      const size_t row = (size_t)lr * p;
+      a.send_rows.assign(send_rows + row, send_rows + row + p);
+      a.send_first.assign(send_first + row, send_first + row + p);
+      a.send_peer_off.assign(send_peer_off + row, send_peer_off + row + p);
+      a.recv_rows.assign(recv_rows + row, recv_rows + row + p);
+      a.recv_first.assign(recv_first + row, recv_first + row + p);
+      a.recv_peer_off.assign(recv_peer_off + row, recv_peer_off + row + p);
+    }
+    if (trace::enabled()) trace::record_op("DeviceBackend", DType::u8, "exchange_rows", c.rank(), c.size(), row_bytes);
+    if (req_out) {
+      cudaStream_t s = device::begin_nonblocking(c);
+      c.exchange_rows(ra, row_bytes, send_row_stride, recv_row_stride, s);
+      *req_out = new device::Request(device::end_nonblocking(c, s));
+    } else {
+      c.exchange_rows(ra, row_bytes, send_row_stride, recv_row_stride, pick_stream(&c, stream));
     }
   });
 }

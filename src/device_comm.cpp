@@ -351,7 +351,9 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       const size_t one_shot_max = p == 2 ? tn.ar_oneshot_max_bytes * 8
                                   : (p <= 4 ? tn.ar_oneshot_max_bytes : std::min<size_t>(tn.ar_oneshot_max_bytes, 16384));
       if (bytes <= one_shot_max || p == 1) algo = AllreduceAlgo::one_shot;
-      else if (p == 2 && bytes >= (size_t{4} << 20) && !zero_copy) algo = AllreduceAlgo::two_shot;  // two ranks: the switch saves no traffic, measured 470 vs 380 GB/s
+      // Two ranks: neither the switch nor a two-shot saves traffic (every algorithm moves S bytes each way), so
+      // the one-shot push is used at every size; large messages run it pipelined (below).
+      else if (p == 2 && !zero_copy) algo = AllreduceAlgo::one_shot;
       else if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
       else algo = AllreduceAlgo::two_shot;
     }
@@ -458,9 +460,13 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
 
   // Large uniform reduce_scatter / allgather / alltoall run pipelined: smaller chunks, half of the
   // grid publishing while the other half consumes.
+  // The one-shot allreduce of two ranks joins them: half of the grid pushes chunk c+1 to the peer while the
+  // other half reduces chunk c, so the link never waits for the reduction.
   size_t slot_e = cap_e;
-  if ((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
-      p > 1 && !use_window && P.count * esz >= tn.pipeline_min_bytes) {
+  const bool ar_pipelined = d.kind == DevColl::allreduce && p == 2 && algo == AllreduceAlgo::one_shot &&
+                            d.algo == AllreduceAlgo::automatic && bytes >= tn.ar_pipeline_min_bytes;
+  if (((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
+       p > 1 && !use_window && P.count * esz >= tn.pipeline_min_bytes) || ar_pipelined) {
     size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {
@@ -497,7 +503,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     switch (d.kind) {
       case DevColl::allreduce:
         need = P.count; work = P.count;
-        chunk_unit = algo == AllreduceAlgo::nvls ? full_e : (algo == AllreduceAlgo::two_shot ? (size_t)p * cap2_e : cap_e);
+        chunk_unit = algo == AllreduceAlgo::nvls ? full_e : (algo == AllreduceAlgo::two_shot ? (size_t)p * cap2_e : slot_e);
         break;
       case DevColl::reduce: need = P.count; chunk_unit = cap_e; work = P.count; break;
       case DevColl::bcast: need = P.count; chunk_unit = full_e; work = P.count; break;
@@ -611,6 +617,69 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     }
   }
   launch_collective(P, in, wire, out, ctas, threads, I.nlocal, stream);
+}
+
+// ---------------------------------------------------------------------------
+// row exchange
+// ---------------------------------------------------------------------------
+void DeviceCommunicator::exchange_rows(const std::vector<RowArgs>& ranks, size_t row_bytes, size_t send_row_stride,
+                                       size_t recv_row_stride, cudaStream_t stream) {
+  Impl& I = *impl_;
+  std::lock_guard<std::mutex> lock(I.mu);
+  check_status();
+  if ((int)ranks.size() != I.nlocal)
+    throw_al_exception("expected arguments for ", I.nlocal, " local rank(s), got ", ranks.size());
+  const int p = I.p;
+  const size_t cap_b = (I.ws.half_bytes / (size_t)p) / 256 * 256;
+  if (row_bytes == 0 || row_bytes > cap_b)
+    throw_al_exception("exchange_rows: a row of ", row_bytes, " bytes does not fit a staging slot of ", cap_b, " bytes");
+  const size_t per_chunk = cap_b / row_bytes;
+  RowsParams R{};
+  R.ws = I.ws;
+  R.row_bytes = row_bytes;
+  R.send_row_stride = send_row_stride;
+  R.recv_row_stride = recv_row_stride;
+  R.seq = ++I.seq;
+  R.timeout_ns = I.timeout_ns;
+  R.rank0 = I.rank0;
+  size_t most_rows = 0, total_rows = 0;
+  for (int lr = 0; lr < I.nlocal; ++lr) {
+    const int r = I.rank0 + lr;
+    const RowArgs& a = ranks[(size_t)lr];
+    auto fill = [&](size_t* dst, const std::vector<size_t>& src, const char* what) {
+      if ((int)src.size() != p) throw_al_exception("exchange_rows: ", what, " must have one entry per rank");
+      for (int i = 0; i < p; ++i) dst[i] = src[(size_t)i];
+    };
+    RowTable& T = R.tab[r];
+    fill(T.send_rows, a.send_rows, "send_rows");
+    fill(T.send_first, a.send_first, "send_first");
+    fill(T.send_peer_off, a.send_peer_off, "send_peer_off");
+    fill(T.recv_rows, a.recv_rows, "recv_rows");
+    fill(T.recv_first, a.recv_first, "recv_first");
+    fill(T.recv_peer_off, a.recv_peer_off, "recv_peer_off");
+    R.send[r] = a.send;
+    R.recv[r] = a.recv;
+    R.send_idx[r] = a.send_idx;
+    R.recv_idx[r] = a.recv_idx;
+    size_t mx = 0;
+    for (int i = 0; i < p; ++i) {
+      mx = std::max(mx, std::max(T.send_rows[i], T.recv_rows[i]));
+      total_rows += T.send_rows[i];
+    }
+    most_rows = std::max(most_rows, mx);
+    R.local_chunks[r] = std::max<uint64_t>(1, ceil_div(mx, per_chunk));
+    if (R.local_chunks[r] >= (1u << 24) - 2) throw_al_exception("exchange_rows: too many rows for the configured staging size");
+  }
+  const size_t work = std::min(total_rows / (size_t)I.nlocal, per_chunk * (size_t)p) * row_bytes;
+  int ctas = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(work, (size_t)65536), (size_t)tuning().max_ctas));
+  if (I.nlocal > 1) ctas = std::max(1, std::min(ctas, I.sm_count / I.nlocal));
+  const int threads = work <= 16384 ? 128 : 512;
+  I.order_after_previous(stream);
+  I.stats.ops++;
+  I.stats.bytes += total_rows * row_bytes;
+  I.stats.kernels++;
+  I.stats.rows++;
+  launch_rows(R, ctas, threads, I.nlocal, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -45,6 +45,7 @@ void Tuning::load_from_env() {
   bulk_pipeline = env_long("AL_DEV_BULK_PIPELINE", bulk_pipeline) != 0;
   bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
   bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
+  ar_pipeline_min_bytes = (size_t)env_long("AL_AR_PIPELINE_MIN", (long)ar_pipeline_min_bytes);
   ll_max_bytes = (size_t)env_long("AL_LL_MAX", (long)ll_max_bytes);
   ll_max_ctas = (int)env_long("AL_LL_CTAS", ll_max_ctas);
   window_enable = env_long("AL_WINDOW", window_enable) != 0;
@@ -113,6 +114,7 @@ std::string Tuning::describe() const {
      << "bulk_pipeline = " << bulk_pipeline << "\n"
      << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
      << "bulk_con_ctas = " << bulk_con_ctas << "\n"
+     << "ar_pipeline_min_bytes = " << ar_pipeline_min_bytes << "\n"
      << "ll_max_bytes = " << ll_max_bytes << "\n"
      << "ll_max_ctas = " << ll_max_ctas << "\n"
      << "window_enable = " << window_enable << "\n"

@@ -75,6 +75,20 @@ def test_data_paths_over_real_ranks(bin_dir):
     assert r.returncode == 0 and r.stdout.count("device paths ok") == n, r.stdout[-4000:] + r.stderr[-4000:]
 
 
+def test_parallel_components_over_real_ranks(bin_dir):
+    """Tensor + sequence parallel training, Ulysses / expert exchanges, a two-stage pipeline with backward and
+    ring attention on real GPUs, each against the single-device computation."""
+    import sys
+    from pathlib import Path
+    n = min(_ngpu(), 4)
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs")
+    worker = Path(__file__).resolve().parent / "workers" / "parallel_worker.py"
+    r = subprocess.run([str(bin_dir / "alrun"), "-n", str(n), "--timeout", "300", sys.executable, str(worker)],
+                       capture_output=True, text=True, timeout=360)
+    assert r.returncode == 0 and r.stdout.count("parallel components ok") == n, r.stdout[-4000:] + r.stderr[-4000:]
+
+
 def test_data_parallel_matches_single_process(bin_dir):
     import sys
     from pathlib import Path

@@ -20,7 +20,7 @@ def al():
         pytest.skip("no CUDA device")
     al.init()
     old = al.get_tuning("ll_max_bytes")
-    al.set_tuning("ll_max_bytes", 16384)   # the largest message the packet slots hold (default: 8 KiB)
+    al.set_tuning("ll_max_bytes", 65536)   # the largest message the packet slots hold
     yield al
     al.set_tuning("ll_max_bytes", old)
 
@@ -47,7 +47,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
     esz = torch.empty((), dtype=dtype).element_size()
-    sizes = [1, 3, 4, 5, 33, 1000, 16384 // esz]
+    sizes = [1, 3, 4, 5, 33, 1000, 65536 // esz]
     before = comm.stats()["ll"]
     calls = 0
     for it, n in enumerate(sizes):
@@ -66,7 +66,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
                 assert torch.equal(ys[r], outs[r][:n])                          # both forms, and every rank, bit-identical
             assert all(torch.equal(outs[0], o) for o in outs)
         # reduce_scatter: n elements per rank
-        if n * esz <= 16384:
+        if n * esz <= 65536:
             xs = [rand(n * p, dtype, 50 + 10 * it + r) for r in range(p)]
             want = ref_reduce(xs, "sum")
             outs = [torch.zeros(n, dtype=dtype, device="cuda") for _ in range(p)]
@@ -87,7 +87,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
 def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
-    for it, n in enumerate([1, 2, 5, 64, 1023, 4096]):
+    for it, n in enumerate([1, 2, 5, 64, 1023, 16384]):
         for dtype in (torch.float32, torch.uint8 if n % 4 == 0 else torch.int16):
             ss = [rand(n, torch.float32, 100 + r + it).to(dtype) for r in range(p)]
             outs = [torch.zeros(n * p, dtype=dtype, device="cuda") for _ in range(p)]
@@ -117,7 +117,7 @@ def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     torch.testing.assert_close(xs[0], st.mean(0))
     torch.testing.assert_close(ys[p - 1], st.sum(0) * 0.25)
     # a message that does not fit is refused when the path is forced, and staged when it is not
-    big = [rand(5000, torch.float32, 1) for _ in range(p)]
+    big = [rand(20000, torch.float32, 1) for _ in range(p)]
     with pytest.raises(al.AlError):
         comm.allreduce(big, algo="ll")
     before = comm.stats()["ll"]
@@ -184,14 +184,14 @@ def test_window_allgather_alltoall_bcast(al, p, symmetric):
             comm.alltoall(xs, recv, algo="window")
             small = [torch.full((3,), float(r), device="cuda") for r in range(p)]
             comm.allreduce(small)                                              # a packet operation right after
-            bb = [o[off:off + n] for o in outs]
-            root = p - 1
-            bb[root].copy_(rand(n, torch.float32, 999))
             a2a_want = [torch.cat([xs[q][r * n:(r + 1) * n] for q in range(p)]) for r in range(p)]
             torch.cuda.synchronize()
             for r in range(p):
                 assert torch.equal(recv[r], a2a_want[r])
                 assert torch.all(small[r] == sum(range(p)))
+            bb = [o[off:off + n] for o in outs]
+            root = p - 1
+            bb[root].copy_(rand(n, torch.float32, 999))
             comm.bcast(bb, root=root, algo="window")
             torch.cuda.synchronize()
             for r in range(p):
@@ -274,4 +274,58 @@ def test_registration_table_is_bounded_and_reusable(al):
     assert comm.register(t) == ids[5]      # the freed slot is taken again
     for b in bufs:
         comm.unregister(b)                  # unknown or refused buffers are ignored
+    comm.close()
+
+
+def test_two_rank_allreduce_is_pipelined_above_threshold(al):
+    """On two ranks large allreduces run the one-shot push with half of the grid pushing while the other half
+    reduces; here the threshold is lowered so that a few MB already take that schedule (several chunks)."""
+    old = al.get_tuning("ar_pipeline_min_bytes")
+    al.set_tuning("ar_pipeline_min_bytes", 65536)
+    try:
+        comm = al.DeviceComm(emulate=2)
+        comm.set_timeout_ms(2000)
+        for n in (3_000_001, 5_000_000):
+            xs = [rand(n, torch.float32, 700 + r) for r in range(2)]
+            want = torch.stack(xs).sum(0)
+            outs = [torch.zeros(n, device="cuda") for _ in range(2)]
+            comm.allreduce(xs, outs)
+            ys = [x.clone() for x in xs]
+            comm.allreduce(ys, op="avg")      # in place, fused average
+            small = [torch.ones(5, device="cuda") for _ in range(2)]
+            comm.allreduce(small)
+            torch.cuda.synchronize()
+            assert comm.status()["code"] == 0
+            for r in range(2):
+                torch.testing.assert_close(outs[r], want)
+                torch.testing.assert_close(ys[r], want / 2)
+                assert torch.all(small[r] == 2)
+        comm.close()
+    finally:
+        al.set_tuning("ar_pipeline_min_bytes", old)
+
+
+@pytest.mark.parametrize("p", [2, 4, 8])
+def test_row_exchange_strided_indexed_and_chunked(al, p):
+    """exchange_rows against torch indexing: strided slices (sequence <-> head), index-selected rows (expert
+    dispatch / combine), uneven counts, and slices larger than a staging slot (several chunks)."""
+    from aluminum_b200.parallel import ulysses
+    old = al.get_tuning("dev_stage_bytes")
+    al.set_tuning("dev_stage_bytes", 1 << 20)       # 1 MiB halves: slots of 128 KiB on 8 ranks
+    comm = al.DeviceComm(emulate=p)
+    al.set_tuning("dev_stage_bytes", old)
+    comm.set_timeout_ms(2000)
+    for (s, h, d, dt) in ((8, 8, 4, torch.float32), (5, 16, 3, torch.bfloat16), (600, 8, 64, torch.float32)):
+        full = rand(s * p * h * d, torch.float32, s).to(dt).view(s * p, h, d)
+        shards = [t.contiguous() for t in full.chunk(p, dim=0)]
+        before = comm.stats()["rows"]
+        heads = ulysses.seq_to_head(comm, shards)
+        torch.cuda.synchronize()
+        for r in range(p):
+            assert torch.equal(heads[r], full[:, r * (h // p):(r + 1) * (h // p)])
+        back = ulysses.head_to_seq(comm, heads)
+        torch.cuda.synchronize()
+        for r in range(p):
+            assert torch.equal(back[r], shards[r])
+        assert comm.stats()["rows"] == before + 2 and comm.status()["code"] == 0
     comm.close()

@@ -21,6 +21,8 @@
 
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "al/bootstrap.hpp"
 
@@ -45,6 +47,11 @@ struct Api {
   int (*GroupStart)() = nullptr;
   int (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
+  // user-buffer registration, as Al::RegisterMemory<NCCLBackend> does (src/nccl_impl.cpp:83-109): optional symbols
+  int (*MemAlloc)(void**, size_t) = nullptr;
+  int (*MemFree)(void*) = nullptr;
+  int (*CommRegister)(Comm, void*, size_t, void**) = nullptr;
+  int (*CommDeregister)(Comm, void*) = nullptr;
   bool ok = false;
 };
 
@@ -59,6 +66,7 @@ inline Api& api() {
     L(AllReduce, "ncclAllReduce"); L(ReduceScatter, "ncclReduceScatter"); L(AllGather, "ncclAllGather");
     L(Broadcast, "ncclBroadcast"); L(Reduce, "ncclReduce"); L(Send, "ncclSend"); L(Recv, "ncclRecv");
     L(GroupStart, "ncclGroupStart"); L(GroupEnd, "ncclGroupEnd"); L(GetErrorString, "ncclGetErrorString");
+    L(MemAlloc, "ncclMemAlloc"); L(MemFree, "ncclMemFree"); L(CommRegister, "ncclCommRegister"); L(CommDeregister, "ncclCommDeregister");
 #undef L
     x.ok = x.GetUniqueId && x.CommInitRank && x.AllReduce && x.ReduceScatter && x.AllGather && x.Send && x.Recv &&
            x.GroupStart && x.GroupEnd;
@@ -86,6 +94,30 @@ class Communicator {
   int size() const { return size_; }
   cudaStream_t stream() const { return stream_; }
 
+  /**
+   * Memory that NCCL can use without its own staging copies: ncclMemAlloc + ncclCommRegister, the registered
+   * counterpart of this library's symm_alloc / RegisterMemory (what a user of the reference gets from
+   * Al::RegisterMemory<NCCLBackend> on an ncclMemAlloc'ed buffer).  nullptr when this NCCL lacks the calls.
+   */
+  void* alloc_registered(size_t bytes) {
+    if (!api().MemAlloc || !api().CommRegister) return nullptr;
+    void* p = nullptr;
+    check(api().MemAlloc(&p, bytes), "ncclMemAlloc");
+    void* handle = nullptr;
+    check(api().CommRegister(comm_, p, bytes, &handle), "ncclCommRegister");
+    registered_.push_back({p, handle});
+    return p;
+  }
+  void free_registered(void* p) {
+    for (auto it = registered_.begin(); it != registered_.end(); ++it) {
+      if (it->first != p) continue;
+      if (api().CommDeregister) check(api().CommDeregister(comm_, it->second), "ncclCommDeregister");
+      if (api().MemFree) check(api().MemFree(p), "ncclMemFree");
+      registered_.erase(it);
+      return;
+    }
+  }
+
   void allreduce(const void* s, void* r, size_t n, int dt, int op) { check(api().AllReduce(s, r, n, dt, op, comm_, stream_), "ncclAllReduce"); }
   void reduce_scatter(const void* s, void* r, size_t n, int dt, int op) { check(api().ReduceScatter(s, r, n, dt, op, comm_, stream_), "ncclReduceScatter"); }
   void allgather(const void* s, void* r, size_t n, int dt) { check(api().AllGather(s, r, n, dt, comm_, stream_), "ncclAllGather"); }
@@ -111,6 +143,7 @@ class Communicator {
   int rank_, size_;
   cudaStream_t stream_;
   Comm comm_ = nullptr;
+  std::vector<std::pair<void*, void*>> registered_;
 };
 
 }  // namespace nccl_equiv

@@ -1,6 +1,8 @@
 // bandwidth - uni-directional point-to-point bandwidth between every ordered pair of ranks, one
 // pair at a time, printed as a source x destination matrix in GiB/s.
-//   alrun -n 8 bandwidth [--backend device|host] [--bytes 268435456] [--iters 10]
+//   alrun -n 8 bandwidth [--backend device|host] [--bytes 268435456] [--iters 10] [--register]
+// --register registers the buffers with the communicator first (Al::RegisterMemory): large messages then go
+// straight into the receive buffer instead of through the mailbox ring.
 // Parity: benchmark/bandwidth.cpp:95-137,193-273 of the reference.
 #include "../cpp_tests/test_common.hpp"
 
@@ -18,6 +20,8 @@ int run(const Args& a) {
   const long iters = a.num("iters", 10);
   Buffer<Backend, float> buf(n);
   buf.upload(std::vector<float>(n, (float)me), comm);
+  const bool reg = a.has("register");
+  if (reg) Al::RegisterMemory<Backend>(buf.data(), n, comm);
   std::vector<double> mat((size_t)(p * p), 0.0);
   for (int s = 0; s < p; ++s)
     for (int d = 0; d < p; ++d) {
@@ -38,8 +42,10 @@ int run(const Args& a) {
     }
   std::vector<double> all((size_t)(p * p));
   Al::Allreduce<Al::HostBackend>((const double*)mat.data(), all.data(), mat.size(), Al::ReductionOperator::max, hc);
+  if (reg) Al::UnregisterMemory<Backend>(buf.data(), comm);
   if (me == 0) {
-    printf("%s send/recv bandwidth, %zu bytes, GiB/s (row = source, column = destination)\n", Backend::Name().c_str(), bytes);
+    printf("%s send/recv bandwidth%s, %zu bytes, GiB/s (row = source, column = destination)\n", Backend::Name().c_str(),
+           reg ? " (registered buffers)" : "", bytes);
     for (int s = 0; s < p; ++s) {
       for (int d = 0; d < p; ++d) printf("%8.1f", all[(size_t)(s * p + d)]);
       printf("\n");

@@ -1,7 +1,7 @@
 // benchmark_ops - times one operation of one backend over a sweep of message sizes.
 //
 //   alrun -n 8 benchmark_ops --backend device|nccl|host|ht --op allreduce --datatype float
-//         [--algo auto|one_shot|two_shot|nvls] [--inplace] [--nonblocking] [--symmetric]
+//         [--algo auto|one_shot|two_shot|nvls|ll] [--inplace] [--nonblocking] [--symmetric] [--register] [--check]
 //         [--min-bytes 8 --max-bytes 1073741824] [--num-warmup 20] [--num-iters 100]
 //         [--reduction-op sum] [--out FILE] [--summarize]
 //
@@ -13,6 +13,9 @@
 // median / mean / min / max per size together with the bus bandwidth
 // (allreduce S/t*2(p-1)/p, reduce_scatter / allgather / alltoall S/t*(p-1)/p with S the
 // full buffer).  `--backend nccl` runs the reference backend's NCCL call sequence.
+// --symmetric allocates the buffers with symm_alloc (device) / ncclMemAlloc + ncclCommRegister (nccl);
+// --register registers cudaMalloc'ed buffers with Al::RegisterMemory (device backend);
+// --check compares the result of every size with the serial oracle on a sample of positions.
 //
 // Output columns follow the reference's schema (benchmark/benchmark_utils.hpp:155-181)
 // with the statistics appended:
@@ -118,15 +121,37 @@ int run_gpu(const Args& a, const std::string& backend) {
   const size_t max_elems = std::max<size_t>(1, max_b / sizeof(T));
   T *sbuf = nullptr, *rbuf = nullptr;
   const size_t alloc = (max_elems + (size_t)p) * sizeof(T);
+  bool nccl_registered = false;
   if (symmetric && dcomm) {
     sbuf = (T*)dcomm->symm_alloc(alloc);
     rbuf = (T*)dcomm->symm_alloc(alloc);
+  } else if (symmetric && ncomm && (sbuf = (T*)ncomm->alloc_registered(alloc)) != nullptr) {
+    rbuf = (T*)ncomm->alloc_registered(alloc);
+    nccl_registered = true;
   } else {
     AL_CHECK_CUDA(cudaMalloc((void**)&sbuf, alloc));
     AL_CHECK_CUDA(cudaMalloc((void**)&rbuf, alloc));
   }
   fill_device(sbuf, max_elems, me);
   AL_CHECK_CUDA(cudaMemset(rbuf, 0, alloc));
+  const bool registered = a.has("register") && dcomm && !symmetric;
+  if (registered) {
+    Al::RegisterMemory<Al::DeviceBackend>(sbuf, max_elems + (size_t)p, *dcomm);
+    Al::RegisterMemory<Al::DeviceBackend>(rbuf, max_elems + (size_t)p, *dcomm);
+  }
+  // --check: every rank's input block (fill_device repeats one block of at most 1 Mi elements)
+  const bool checking = a.has("check") && !inplace;
+  const size_t block = std::min<size_t>(max_elems, 1 << 20);
+  std::vector<std::vector<double>> blocks;
+  if (checking) {
+    for (int r = 0; r < p; ++r) {
+      std::minstd_rand rng((unsigned)r + 1);
+      std::vector<double> b(block);
+      for (auto& v : b) v = to_double(from_double<T>(((double)(rng() % 20001) - 10000.0) / 10000.0));
+      blocks.push_back(std::move(b));
+    }
+  }
+  long check_failures = 0;
 
   std::ofstream file;
   if (me == 0 && a.has("out")) file.open(a.str("out", ""), std::ios::app);
@@ -148,6 +173,7 @@ int run_gpu(const Args& a, const std::string& backend) {
   if (algo_name == "one_shot") algo = Al::DeviceAllreduceAlgo::one_shot;
   else if (algo_name == "two_shot") algo = Al::DeviceAllreduceAlgo::two_shot;
   else if (algo_name == "nvls") algo = Al::DeviceAllreduceAlgo::nvls;
+  else if (algo_name == "ll") algo = Al::DeviceAllreduceAlgo::ll;
   const std::string algo_s = algo_name + (cap > 0 ? "/c" + cap_s : "");
   if (algo == Al::DeviceAllreduceAlgo::nvls && dcomm && !dcomm->has_multicast()) continue;
   for (size_t bytes = std::max(min_b, sizeof(T)); bytes <= max_b; bytes *= 2) {
@@ -220,6 +246,34 @@ int run_gpu(const Args& a, const std::string& backend) {
     }
     dog.disarm();
     if (dcomm) dcomm->check_status();
+    if (checking && (op == "allreduce" || sliced)) {
+      // expected value of output element i from the ranks' input blocks (input element j of rank r = blocks[r][j % block])
+      auto in = [&](int r, size_t j) { return blocks[(size_t)r][j % block]; };
+      auto expect = [&](size_t i) -> double {
+        if (op == "allgather") return in((int)(i / per), i % per);
+        if (op == "alltoall") return in((int)(i / per), (size_t)me * per + i % per);
+        const size_t j = op == "allreduce" ? i : (size_t)me * per + i;
+        double acc = in(0, j);
+        for (int r = 1; r < p; ++r) {
+          const double v = in(r, j);
+          acc = rop == ReductionOperator::max ? std::max(acc, v) : (rop == ReductionOperator::min ? std::min(acc, v) : acc + v);
+        }
+        return rop == ReductionOperator::avg ? acc / p : acc;
+      };
+      const size_t out_n = op == "allreduce" ? total : (op == "reduce_scatter" ? per : per * (size_t)p);
+      const size_t head = std::min<size_t>(out_n, 65536), tail = std::min<size_t>(out_n - head, 4096);
+      std::vector<T> h(head + tail);
+      AL_CHECK_CUDA(cudaMemcpy(h.data(), rbuf, head * sizeof(T), cudaMemcpyDeviceToHost));
+      if (tail) AL_CHECK_CUDA(cudaMemcpy(h.data() + head, rbuf + out_n - tail, tail * sizeof(T), cudaMemcpyDeviceToHost));
+      const double tol = sizeof(T) == 2 ? 0.05 * p : 1e-4 * p;
+      for (size_t k = 0; k < h.size(); ++k) {
+        const size_t i = k < head ? k : out_n - tail + (k - head);
+        if (std::fabs(to_double(h[k]) - expect(i)) > tol) {
+          if (check_failures++ == 0)
+            fprintf(stderr, "[rank %d] %s %zu bytes: element %zu is %g, expected %g\n", me, op.c_str(), bytes, i, to_double(h[k]), expect(i));
+        }
+      }
+    }
     // max over ranks, iteration by iteration
     std::vector<double> worst(times.size());
     Al::Allreduce<Al::HostBackend>((const double*)times.data(), worst.data(), times.size(), ReductionOperator::max, hcomm);
@@ -234,11 +288,24 @@ int run_gpu(const Args& a, const std::string& backend) {
   }
   AL_CHECK_CUDA(cudaStreamSynchronize(stream));
   Al::Barrier<Al::HostBackend>(hcomm);
+  if (registered) {
+    Al::UnregisterMemory<Al::DeviceBackend>(sbuf, *dcomm);
+    Al::UnregisterMemory<Al::DeviceBackend>(rbuf, *dcomm);
+  }
   if (symmetric && dcomm) { dcomm->symm_free(sbuf); dcomm->symm_free(rbuf); }
+  else if (nccl_registered) { ncomm->free_registered(sbuf); ncomm->free_registered(rbuf); }
   else { cudaFree(sbuf); cudaFree(rbuf); }
+  if (checking) {
+    long all_failures = 0;
+    std::vector<double> mine{(double)check_failures}, sum(1);
+    Al::Allreduce<Al::HostBackend>((const double*)mine.data(), sum.data(), 1, ReductionOperator::sum, hcomm);
+    all_failures = (long)sum[0];
+    if (me == 0) fprintf(stderr, "benchmark_ops --check: %s\n", all_failures ? "MISMATCHES" : "all sampled results correct");
+    check_failures = all_failures;
+  }
   dcomm.reset(); htcomm.reset(); ncomm.reset();
   cudaStreamDestroy(stream);
-  return 0;
+  return check_failures ? 1 : 0;
 }
 
 /** Host backend: steady-clock timing (benchmark/benchmark_utils_mpi.hpp:35-45 of the reference). */

@@ -66,6 +66,9 @@ static int stress_host(const Args& a) {
 int main(int argc, char** argv) {
   Args a(argc, argv);
   try {
+    // Non-blocking operations run on pooled internal streams; with the default pool of one stream they would
+    // queue behind each other on the device.  One internal stream per compute stream unless the caller chose.
+    setenv("AL_CUDA_STREAM_POOL_SIZE", std::to_string(a.num("streams", 8)).c_str(), 0);
     Al::Initialize(argc, argv);
     if (a.str("backend", "device") == "host") {
       const int rc = stress_host(a);
@@ -75,12 +78,16 @@ int main(int argc, char** argv) {
     const int nops = (int)a.num("ops", 64), nstreams = (int)a.num("streams", 8), rounds = (int)a.num("rounds", 20);
     const double lo = std::log((double)a.num("min-bytes", 4096)), hi = std::log((double)a.num("max-bytes", 262144));
     Al::HostCommunicator hc;
+    // One communicator per operation (--comms, default = --ops) spread over the streams: operations of one
+    // communicator are chained by design, so only operations of different communicators are truly concurrent.
+    // The messages are small: give every communicator a small workspace.
+    const int ncomms = (int)a.num("comms", nops);
+    Al::tuning().dev_stage_bytes = std::max<size_t>((size_t)a.num("max-bytes", 262144) * 8, size_t{1} << 20);
+    Al::tuning().dev_mailbox_bytes = 65536;
     std::vector<cudaStream_t> streams((size_t)nstreams);
     std::vector<std::unique_ptr<Al::DeviceCommunicator>> comms;
-    for (auto& s : streams) {
-      AL_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-      comms.emplace_back(new Al::DeviceCommunicator(s));
-    }
+    for (auto& s : streams) AL_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    for (int i = 0; i < ncomms; ++i) comms.emplace_back(new Al::DeviceCommunicator(streams[(size_t)(i % nstreams)]));
     std::mt19937 rng(1);
     std::uniform_real_distribution<double> U(lo, hi);
     std::vector<size_t> counts((size_t)nops);
@@ -97,12 +104,16 @@ int main(int argc, char** argv) {
     for (int r = 0; r < rounds + 3; ++r) {
       Al::Barrier<Al::HostBackend>(hc);
       const double t0 = Al::get_time();
+      // every operation is issued before the first Wait: all of them are outstanding at once
+      std::vector<Al::DeviceBackend::req_type> reqs((size_t)nops);
       for (int i = 0; i < nops; ++i) {
-        Al::DeviceCommunicator& c = *comms[(size_t)(i % nstreams)];
-        Al::DeviceBackend::req_type req;
+        Al::DeviceCommunicator& c = *comms[(size_t)(i % ncomms)];
         AL_CHECK_CUDA(cudaEventRecord(e0[(size_t)i], c.get_stream()));
-        Al::NonblockingAllreduce<Al::DeviceBackend>(bufs[(size_t)i], counts[(size_t)i], Al::ReductionOperator::max, c, req);
-        Al::Wait<Al::DeviceBackend>(req);  // stream-side join, the host continues
+        Al::NonblockingAllreduce<Al::DeviceBackend>(bufs[(size_t)i], counts[(size_t)i], Al::ReductionOperator::max, c, reqs[(size_t)i]);
+      }
+      for (int i = 0; i < nops; ++i) {
+        Al::DeviceCommunicator& c = *comms[(size_t)(i % ncomms)];
+        Al::Wait<Al::DeviceBackend>(reqs[(size_t)i]);  // stream-side join, the host continues
         AL_CHECK_CUDA(cudaEventRecord(e1[(size_t)i], c.get_stream()));
       }
       for (auto s : streams) AL_CHECK_CUDA(cudaStreamSynchronize(s));
@@ -127,8 +138,8 @@ int main(int argc, char** argv) {
     std::sort(op_us.begin(), op_us.end());
     if (hc.rank() == 0) {
       const double med = worst[worst.size() / 2];
-      printf("stress ranks=%d streams=%d ops=%d memops=%s round_median_us=%.1f ops_per_s=%.0f op_p50_us=%.1f op_p99_us=%.1f\n",
-             hc.size(), nstreams, nops, getenv("AL_REQ_MEMOPS") ? getenv("AL_REQ_MEMOPS") : "0", med, nops / (med * 1e-6),
+      printf("stress ranks=%d streams=%d comms=%d ops=%d memops=%s round_median_us=%.1f ops_per_s=%.0f op_p50_us=%.1f op_p99_us=%.1f\n",
+             hc.size(), nstreams, ncomms, nops, getenv("AL_REQ_MEMOPS") ? getenv("AL_REQ_MEMOPS") : "0", med, nops / (med * 1e-6),
              op_us[op_us.size() / 2], op_us[(size_t)(op_us.size() * 0.99)]);
     }
     Al::Barrier<Al::HostBackend>(hc);

@@ -102,14 +102,50 @@ struct Buffer {
 };
 
 #ifdef AL_HAS_CUDA
+/**
+ * Device memory of the test buffers.  Blocks go back to a process-wide free list instead of cudaFree:
+ * cudaFree synchronises the whole device, and with several threads testing at once (--threads) that means
+ * waiting for another thread's collective, which in turn waits for a peer rank whose thread sits in the same
+ * cudaFree - every rank stuck.  (The reference's test vectors come from its caching pool for the same
+ * reason, test/cuda_vector.hpp:36-167.)  The list is released at process exit.
+ */
+class DevicePool {
+ public:
+  static DevicePool& get() { static DevicePool* p = new DevicePool; return *p; }
+  void* take(size_t bytes) {
+    const size_t key = round(bytes);
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      auto it = free_.find(key);
+      if (it != free_.end() && !it->second.empty()) {
+        void* p = it->second.back();
+        it->second.pop_back();
+        return p;
+      }
+    }
+    void* p = nullptr;
+    AL_CHECK_CUDA(cudaMalloc(&p, key));
+    return p;
+  }
+  void give(void* p, size_t bytes) {
+    std::lock_guard<std::mutex> lock(mu_);
+    free_[round(bytes)].push_back(p);
+  }
+
+ private:
+  static size_t round(size_t b) { size_t r = 256; while (r < b) r <<= 1; return r; }
+  std::mutex mu_;
+  std::map<size_t, std::vector<void*>> free_;
+};
+
 template <typename T>
 struct DeviceBuf {
   T* p = nullptr;
   size_t n = 0;
   explicit DeviceBuf(size_t n_ = 0) : n(n_) {
-    if (n) AL_CHECK_CUDA(cudaMalloc((void**)&p, n * sizeof(T)));
+    if (n) p = (T*)DevicePool::get().take(n * sizeof(T));
   }
-  ~DeviceBuf() { if (p) cudaFree(p); }
+  ~DeviceBuf() { if (p) DevicePool::get().give(p, n * sizeof(T)); }
   DeviceBuf(const DeviceBuf&) = delete;
   DeviceBuf& operator=(const DeviceBuf&) = delete;
   DeviceBuf(DeviceBuf&& o) noexcept : p(o.p), n(o.n) { o.p = nullptr; o.n = 0; }

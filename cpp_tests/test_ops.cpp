@@ -1,7 +1,7 @@
 // test_ops - runs any operation of any backend over a sweep of sizes and checks
 // every rank's result against a serial oracle computed in the test process.
 //
-//   alrun -n 4 test_ops --backend host|device|ht --op allreduce --datatype float
+//   alrun -n 4 test_ops --backend host|device|ht --op allreduce --datatype float [--register]
 //         [--inplace] [--nonblocking] [--reduction-op sum] [--root 0]
 //         [--size N | --min-size A --max-size B] [--odd-sizes] [--zero] [--trials K]
 //         [--threads N] [--permute 2,0,1,...]
@@ -23,6 +23,25 @@ struct Case {
   bool inplace, nonblocking;
   ReductionOperator redop;
   int root;
+  bool reg = false;  ///< --register: Al::RegisterMemory on the buffers of the collectives (test/test_ops.cpp:364-367,494 of the reference)
+};
+
+/**
+ * --register: registers a test buffer with the communicator for the life of the guard.  Registration is
+ * collective on the device backend (every rank registers its buffer of the same role, in the same order);
+ * the host backends ignore it.  A rank whose buffer is empty (rooted operations) still takes part.
+ */
+template <typename Backend, typename T>
+struct RegGuard {
+  typename Backend::comm_type& comm;
+  T* ptr = nullptr;
+  bool on;
+  RegGuard(bool enable, Buffer<Backend, T>& b, typename Backend::comm_type& c) : comm(c), ptr(b.data()), on(enable) {
+    if (on) Al::RegisterMemory<Backend>(ptr, b.size(), comm);
+  }
+  ~RegGuard() {
+    if (on) Al::UnregisterMemory<Backend>(ptr, comm);
+  }
 };
 
 template <typename Backend>
@@ -52,6 +71,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
     for (int r = 0; r < p; ++r) ins.push_back(input_of(r, n));
     std::vector<T> want = reduce_oracle(ins, rop);
     Buffer<Backend, T> in(n), out(n);
+    RegGuard<Backend, T> reg_in(c.reg, in, comm), reg_out(c.reg, out, comm);
     in.upload(ins[(size_t)me], comm);
     out.upload(std::vector<T>(n, fill), comm);
     const bool is_ar = c.op == "allreduce";
@@ -86,6 +106,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
       mine.emplace_back(ins[(size_t)r].begin() + (long)displs[(size_t)me], ins[(size_t)r].begin() + (long)(displs[(size_t)me] + counts[(size_t)me]));
     std::vector<T> want = reduce_oracle(mine, rop);
     Buffer<Backend, T> in(total), out(counts[(size_t)me]);
+    RegGuard<Backend, T> reg_in(c.reg, in, comm), reg_out(c.reg, out, comm);
     in.upload(ins[(size_t)me], comm);
     out.upload(std::vector<T>(counts[(size_t)me], fill), comm);
     if (!v) {
@@ -162,6 +183,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
     std::vector<T> want(root_data.begin() + (long)displs[(size_t)me], root_data.begin() + (long)(displs[(size_t)me] + counts[(size_t)me]));
     const bool root = me == c.root;
     Buffer<Backend, T> in(root ? total : (ip ? counts[(size_t)me] : 0)), out(ip ? 0 : counts[(size_t)me]);
+    RegGuard<Backend, T> reg_in(c.reg, in, comm), reg_out(c.reg, out, comm);
     if (root) in.upload(root_data, comm);
     else if (ip) in.upload(std::vector<T>(counts[(size_t)me], fill), comm);
     if (!ip) out.upload(std::vector<T>(counts[(size_t)me], fill), comm);
@@ -200,6 +222,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
                 want.begin() + (long)displs[(size_t)r]);
     }
     Buffer<Backend, T> in(total), out(ip ? 0 : total);
+    RegGuard<Backend, T> reg_in(c.reg, in, comm), reg_out(c.reg, out, comm);
     in.upload(mine, comm);
     if (!ip) out.upload(std::vector<T>(total, fill), comm);
     if (!v) {
@@ -220,6 +243,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
   if (c.op == "bcast") {
     std::vector<T> want = input_of(c.root, n);
     Buffer<Backend, T> buf(n);
+    RegGuard<Backend, T> reg_buf(c.reg, buf, comm);
     buf.upload(me == c.root ? want : std::vector<T>(n, fill), comm);
     if (nb) Al::NonblockingBcast<Backend>(buf.data(), n, c.root, comm, req);
     else Al::Bcast<Backend>(buf.data(), n, c.root, comm);
@@ -258,6 +282,7 @@ bool run_case(const Case& c, typename Backend::comm_type& comm) {
   if (c.op == "sendrecv") {
     const int dest = (me + 1) % p, src = (me - 1 + p) % p;
     Buffer<Backend, T> in(n), out(ip ? 0 : n);
+    RegGuard<Backend, T> reg_in(c.reg, in, comm), reg_out(c.reg, out, comm);
     in.upload(input_of(me, n), comm);
     if (!ip) out.upload(std::vector<T>(n, fill), comm);
     if (ip && nb) Al::NonblockingSendRecv<Backend>(in.data(), n, dest, src, comm, req);
@@ -385,6 +410,7 @@ int run_all(const Args& a) {
   c.nonblocking = a.has("nonblocking");
   c.redop = parse_redop(a.str("reduction-op", "sum"));
   c.root = (int)a.num("root", 0) % comm.size();
+  c.reg = a.has("register");
   std::vector<size_t> sizes;
   if (a.has("size")) sizes.push_back((size_t)a.num("size", 1));
   else sizes = sweep_sizes((size_t)a.num("min-size", 1), (size_t)a.num("max-size", 1 << 16), a.has("odd-sizes"), a.has("zero"));

@@ -444,8 +444,26 @@ static void test_arrival_counters() {
   CHECK(single_counter_failures > 0);  // the schedules really do exercise the hazard
 }
 
+static void test_progress_thread_placement() {
+  using Al::internal::choose_pe_core;
+  using Al::internal::parse_cpulist;
+  CHECK((parse_cpulist("0-3,8,10-11\n") == std::vector<int>{0, 1, 2, 3, 8, 10, 11}));
+  CHECK(parse_cpulist("").empty() && (parse_cpulist("5") == std::vector<int>{5}));
+  std::vector<int> allowed;
+  for (int c = 0; c < 64; ++c) allowed.push_back(c);
+  // a GPU on the second socket (cores 32-63): its ranks poll from there, stepping down from the top
+  const std::vector<int> near = parse_cpulist("32-63");
+  CHECK(choose_pe_core(allowed, near, 0) == 63 && choose_pe_core(allowed, near, 3) == 60);
+  // a GPU on the first socket never gets a core of the second one
+  CHECK(choose_pe_core(allowed, parse_cpulist("0-31"), 1) == 30);
+  // cores outside the affinity mask are not used; unknown locality falls back to the allowed cores
+  CHECK(choose_pe_core({0, 1, 2, 3}, near, 0) == 3 && choose_pe_core({4, 5, 40, 41}, near, 1) == 40);
+  CHECK(choose_pe_core(allowed, {}, 2) == 61 && choose_pe_core({7}, near, 0) == -1);
+}
+
 int main() {
   test_meta();
+  test_progress_thread_placement();
   test_arrival_counters();
   test_spsc();
   test_mpsc();

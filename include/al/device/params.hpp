@@ -50,7 +50,10 @@ struct FlagLayout {
   static constexpr size_t off_arrive = off_halo + 4 * stride;              // [2][4] CTA arrival counters (A, B, C, spare) per round parity
   static constexpr size_t off_status = off_arrive + 8 * stride;            // device-local copy of the status code
   static constexpr size_t off_p2p_arrive = off_status + stride;            // [2][16] per-item CTA arrival counters per piece parity
-  static constexpr size_t words = off_p2p_arrive + 32 * stride;
+  static constexpr size_t off_p2p_ready = off_p2p_arrive + 32 * stride;    // [kMaxRanks], written by the receiver into the SENDER's area:
+                                                                            //   word 0 = number of the message's first piece + 1, word 1 = descriptor of its buffer
+  static constexpr size_t off_p2p_posted = off_p2p_ready + kMaxRanks * stride;  // [16] plain words, local: last piece each item of the running launch posted
+  static constexpr size_t words = off_p2p_posted + 16;
   static constexpr size_t bytes = (words * 8 + 4095) / 4096 * 4096;
 };
 
@@ -130,6 +133,7 @@ struct Workspace {
                                  ///< %globaltimer at entry / data sent / data seen / exit (latency breakdowns)
   size_t half_bytes;             ///< size of one staging half
   size_t mbox_slot_bytes;        ///< size of one mailbox slot
+  int mbox_slots;                ///< slots per (source, destination) ring
   int p;                         ///< communicator size
 };
 
@@ -172,6 +176,8 @@ struct CollParams {
   int pipelined;                 ///< 1: half of the CTAs publish while the other half consumes (large uniform ops)
   size_t slot_elems;             ///< elements moved per slot and chunk (0 = the slot's capacity)
   int n_pub;                     ///< bulk-copy pipeline: number of publishing CTAs (0 = half of the grid)
+  int own_direct;                ///< one-shot allreduce: a rank reads its own contribution from its send buffer instead of
+                                 ///< pushing it into its own slot (same in / wire type, 16-byte aligned send buffer)
 };
 
 /**
@@ -253,6 +259,10 @@ struct P2PParams {
   int is_send[kMaxItems];
   int owner[kMaxItems];          ///< rank executing this item (emulation: several ranks per launch)
   uint64_t base[kMaxItems];      ///< pieces already moved between this pair in this direction (host-tracked)
+  uint64_t rdesc[kMaxItems];     ///< receives: descriptor of the receive buffer when it is registered, else 0
+  const WindowTable* windows;    ///< device memory of the launching process
+  size_t rendezvous_bytes;       ///< messages of at least this size wait for the receiver and go straight into a registered buffer
+  uint64_t launch;               ///< number of this launch on the communicator (tags the local "posted" words)
   int ctas_per_item;
   int nitems;
   uint64_t timeout_ns;

@@ -19,6 +19,8 @@
  * the process' affinity mask minus the local rank (no hwloc dependency).
  */
 #pragma once
+#include <string>
+#include <vector>
 #include <atomic>
 #include <condition_variable>
 #include <functional>
@@ -33,6 +35,15 @@
 
 namespace Al {
 namespace internal {
+
+/** "0-3,8,10-11" (the format of sysfs cpulist files) -> the listed core numbers. */
+std::vector<int> parse_cpulist(const std::string& text);
+/**
+ * Core for the progress thread: among the cores the process may use, prefer those local to the GPU
+ * (`near_gpu`, may be empty), take the highest-numbered one and step down by the node-local rank.
+ * -1 = do not bind (fewer than two cores allowed).
+ */
+int choose_pe_core(const std::vector<int>& allowed, const std::vector<int>& near_gpu, long local_rank);
 
 class ProgressEngine {
  public:
@@ -65,6 +76,8 @@ class ProgressEngine {
   size_t in_flight() const { return in_flight_.load(std::memory_order_acquire); }
   /** The core the thread was bound to, or -1. */
   int bound_core() const { return bound_core_; }
+  /** How many cores the kernel reported as local to the GPU (0: unknown, the choice fell back to all allowed cores). */
+  int near_gpu_cores() const { return near_gpu_cores_; }
 
  private:
   struct InputQueue {
@@ -104,6 +117,7 @@ class ProgressEngine {
   std::function<void(const AlState&, double)> hang_cb_;
   int device_ = -1;
   int bound_core_ = -1;
+  int near_gpu_cores_ = 0;
 };
 
 /** The process-wide engine (created by Initialize). */

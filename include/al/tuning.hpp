@@ -18,6 +18,23 @@
 
 namespace Al {
 
+/**
+ * Message sizes at which the device backend changes algorithm.  They depend on the number of ranks, so
+ * the table has a row for communicators of 2, of 3-4 and of 5-8 ranks (tuned on 2, 4 and 8 B200 over
+ * NVLink 5 / NVSwitch; al_info prints it).  Every entry has an environment variable that sets all rows
+ * (AL_LL_MAX, ...) and one per row (AL_LL_MAX_P2, _P4, _P8); al_set_tuning("ll_max_bytes", v) sets all
+ * rows, "ll_max_bytes@4" one.
+ */
+struct Crossovers {
+  size_t ll_max_bytes;             ///< AL_LL_MAX: at most this many bytes per pair of ranks travel as low-latency packets (hard limit 64 KiB; 0 = never)
+  size_t ar_oneshot_max_bytes;     ///< AL_AR_ONESHOT_MAX: staged one-shot allreduce up to this size
+  size_t ar_nvls_min_bytes;        ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on
+  size_t ar_pipeline_min_bytes;    ///< AL_AR_PIPELINE_MIN: two ranks: the one-shot allreduce splits its grid into pushing and reducing CTAs from this size on
+  size_t nvls_pipeline_min_bytes;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is software-pipelined from this size on
+  size_t pipeline_min_bytes;       ///< AL_PIPELINE_MIN: per-rank slice from which staged reduce_scatter / allgather / alltoall split the grid into publishers and consumers
+  size_t window_min_bytes;         ///< AL_WINDOW_MIN: total message size from which registered buffers take the window kernels (below: staging or packets, one flag round less)
+};
+
 struct Tuning {
   // ---- progress engine ------------------------------------------------------
   int pe_num_concurrent_ops = AL_PE_NUM_CONCURRENT_OPS_DEFAULT;  ///< AL_PE_NUM_CONCURRENT_OPS
@@ -37,26 +54,29 @@ struct Tuning {
   bool host_serialize = false;                 ///< AL_HOST_SERIALIZE: blocking host calls also run on the progress thread (the reference's ALUMINUM_MPI_SERIALIZE)
   // ---- device backend ---------------------------------------------------------
   size_t dev_stage_bytes = size_t{64} << 20;   ///< AL_DEV_STAGE_BYTES: one staging half per rank per communicator
-  size_t dev_mailbox_bytes = size_t{4} << 20;  ///< AL_DEV_MAILBOX_BYTES: p2p slot per ordered pair (2 slots each)
+  size_t dev_mailbox_bytes = size_t{4} << 20;  ///< AL_DEV_MAILBOX_BYTES: size of one p2p mailbox slot
+  int dev_mailbox_slots = 4;                   ///< AL_DEV_MAILBOX_SLOTS: slots of the ring every ordered pair of ranks owns (pieces in flight per transfer)
+  size_t p2p_rendezvous_bytes = size_t{1} << 20;  ///< AL_P2P_RENDEZVOUS: from this size on a send first waits for the receiver and, if the receive buffer is registered, stores straight into it (0 = never)
   double dev_wait_timeout_ms = 20000.0;        ///< AL_DEV_WAIT_TIMEOUT_MS: bound of every device-side flag wait
   bool dev_enable_nvls = true;                 ///< AL_DEV_NVLS: bind staging to an NVLink multicast object when supported
-  size_t ar_oneshot_max_bytes = size_t{256} << 10;   ///< AL_AR_ONESHOT_MAX: one-shot allreduce up to this size
-  size_t ar_nvls_min_bytes = 0;                      ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on (measured best at every size on 8 GPUs)
   int max_ctas = 128;                          ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
   int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
   int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
-  size_t pipeline_min_bytes = size_t{32} << 20;  ///< AL_PIPELINE_MIN: per-rank slice from which reduce_scatter / allgather / alltoall split the grid into publishers and consumers
-  size_t ar_pipeline_min_bytes = size_t{8} << 20;  ///< AL_AR_PIPELINE_MIN: on two ranks the one-shot allreduce splits its grid into pushing and reducing CTAs from this size on
-  size_t nvls_pipeline_min_bytes = size_t{128} << 20;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is pipelined from this size on
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
   int p2p_max_ctas = 64;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)
   bool bulk_pipeline = false;                  ///< AL_DEV_BULK_PIPELINE: pipelined reduce_scatter / allgather / alltoall move their data with the bulk copy engine (cp.async.bulk) when every buffer is 16-byte aligned
   int bulk_pub_ctas = 16;                      ///< AL_DEV_BULK_PUB_CTAS: publishing CTAs of that kernel (one issuing thread each)
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
-  size_t ll_max_bytes = size_t{64} << 10;      ///< AL_LL_MAX: uniform allreduce / reduce_scatter / allgather / alltoall of at most this many bytes per pair of ranks travel as low-latency packets (hard limit 64 KiB; 0 = never)
   int ll_max_ctas = 16;                        ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
+  Crossovers cross[3] = {
+      // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min
+      {size_t{64} << 10, size_t{2} << 20, 0, size_t{32} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10},   // 2 ranks
+      {size_t{64} << 10, size_t{256} << 10, 0, size_t{32} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10}, // 3-4 ranks
+      {size_t{64} << 10, size_t{16} << 10, 0, size_t{32} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10},  // 5-8 ranks
+  };
+  /** Row of the table for a communicator of `p` ranks. */
+  const Crossovers& crossovers(int p) const { return cross[p <= 2 ? 0 : (p <= 4 ? 1 : 2)]; }
   bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
-  size_t window_min_bytes = size_t{256} << 10; ///< AL_WINDOW_MIN: ... from this total message size on (smaller ones are faster through staging: one flag round instead of two)
   int window_ctas = 64;                        ///< AL_WINDOW_CTAS: CTA budget of a window kernel
   bool window_multimem = true;                 ///< AL_WINDOW_MULTIMEM: let window kernels use multimem.st / multimem.ld_reduce when all ranks pass the same offset of one multicast-bound window
   // ---- diagnostics ------------------------------------------------------------

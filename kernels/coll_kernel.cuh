@@ -64,8 +64,20 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
         if (!P.two_phase) {  // every rank gets every rank's whole chunk
           const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
           split_range(len, part, nparts, VEC, lo, hi);
-          if (send && hi > lo)
-            cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+          if (send && hi > lo) {
+            if (P.own_direct) {  // the own contribution is read from the send buffer at reduce time: p-1 destinations
+              char* others[kMaxRanks];
+              int n = 0;
+#pragma unroll
+              for (int r = 0; r < kMaxRanks; ++r) {
+                others[r] = nullptr;
+                if (r < p && r != rank) others[n++] = all_stage[r];
+              }
+              cta_publish<Ti, Tw>(others, n, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+            } else {
+              cta_publish<Ti, Tw>(all_stage, p, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
+            }
+          }
         } else {             // rank d gets slice d of every rank's chunk
           const size_t unit = (size_t)p * cap2_e, base = c * unit, len = clamp_len(P.count, base, unit);
           for (int i = 0; i < p; ++i) {
@@ -159,6 +171,9 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
         if (kind == DevColl::reduce && rank != root) break;
         const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
         split_range(len, part, nparts, VEC, lo, hi);
+        if constexpr (std::is_same<Ti, Tw>::value) {
+          if (P.own_direct && kind == DevColl::allreduce) slot[rank] = (char*)(send + base);
+        }
         if (recv && hi > lo) {
           To* out = recv + base + lo;
           cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);

@@ -97,15 +97,43 @@ int al_info(char* buf, size_t buflen) {
 
 #define AL_TUNE_FIELDS(X)                                                                                      \
   X(pe_num_concurrent_ops) X(pe_hang_seconds) X(host_stage_bytes) X(host_mailbox_bytes) X(host_wait_timeout_s) \
-  X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls) X(ar_oneshot_max_bytes)   \
-  X(ar_nvls_min_bytes) X(pipeline_min_bytes) X(nvls_pipeline_min_bytes) X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
+  X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls)   \
+  X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ar_pipeline_min_bytes) X(ll_max_bytes) X(ll_max_ctas) X(window_enable) X(window_min_bytes) X(window_ctas) X(window_multimem)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(window_enable) X(window_ctas) X(window_multimem)
+
+namespace {
+/** "ll_max_bytes" or "ll_max_bytes@4" -> member pointer and row (-1 = all rows); nullptr if not a crossover. */
+size_t Crossovers::*crossover_field(const std::string& full, int* row) {
+  std::string n = full;
+  *row = -1;
+  const size_t at = n.find('@');
+  if (at != std::string::npos) {
+    const int p = atoi(n.c_str() + at + 1);
+    *row = p <= 2 ? 0 : (p <= 4 ? 1 : 2);
+    n = n.substr(0, at);
+  }
+  if (n == "ll_max_bytes") return &Crossovers::ll_max_bytes;
+  if (n == "ar_oneshot_max_bytes") return &Crossovers::ar_oneshot_max_bytes;
+  if (n == "ar_nvls_min_bytes") return &Crossovers::ar_nvls_min_bytes;
+  if (n == "ar_pipeline_min_bytes") return &Crossovers::ar_pipeline_min_bytes;
+  if (n == "nvls_pipeline_min_bytes") return &Crossovers::nvls_pipeline_min_bytes;
+  if (n == "pipeline_min_bytes") return &Crossovers::pipeline_min_bytes;
+  if (n == "window_min_bytes") return &Crossovers::window_min_bytes;
+  return nullptr;
+}
+}  // namespace
 
 int al_set_tuning(const char* name, double value) {
   return guard([&] {
     const std::string n = name;
     Tuning& t = tuning();
+    int row = -1;
+    if (auto f = crossover_field(n, &row)) {
+      for (int r = 0; r < 3; ++r)
+        if (row < 0 || row == r) t.cross[r].*f = (size_t)value;
+      return;
+    }
 #define X(f) if (n == #f) { t.f = (decltype(t.f))value; return; }
     AL_TUNE_FIELDS(X)
 #undef X
@@ -116,6 +144,8 @@ int al_set_tuning(const char* name, double value) {
 double al_get_tuning(const char* name) {
   const std::string n = name;
   const Tuning& t = tuning();
+  int row = -1;
+  if (auto f = crossover_field(n, &row)) return (double)(t.cross[row < 0 ? 2 : row].*f);  // no row given: 5-8 ranks
 #define X(f) if (n == #f) return (double)t.f;
   AL_TUNE_FIELDS(X)
 #undef X

@@ -7,6 +7,9 @@
 #include "al/cuda/events.hpp"
 #include "al/cuda/gpu_status_flag.hpp"
 #include "al/cuda/gpu_wait.hpp"
+#include <cctype>
+#include <string>
+
 #include "al/cuda/helper_kernels.hpp"
 #include "al/cuda/streams.hpp"
 #include "al/cuda/sync_memory.hpp"
@@ -18,6 +21,17 @@ namespace internal {
 
 void pe_make_device_current(int dev) {
   if (dev >= 0) (void)cudaSetDevice(dev);
+}
+
+std::string pe_device_pci_bus_id(int dev) {
+  char id[32] = {0};
+  if (dev < 0 || cudaDeviceGetPCIBusId(id, (int)sizeof(id), dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return std::string();
+  }
+  std::string s(id);
+  for (char& c : s) c = (char)tolower((unsigned char)c);
+  return s;
 }
 
 namespace cuda {

@@ -50,7 +50,8 @@ struct DeviceCommunicator::Impl {
 
   size_t off_stage() const { return FlagLayout::bytes; }
   size_t off_mbox() const { return FlagLayout::bytes + 2 * ws.half_bytes; }
-  size_t off_ll() const { return off_mbox() + (size_t)p * 2 * ws.mbox_slot_bytes; }
+  size_t off_ll() const { return off_mbox() + (size_t)p * (size_t)ws.mbox_slots * ws.mbox_slot_bytes; }
+  uint64_t p2p_launches = 0;
   uint64_t* stamps_dev = nullptr;
 
   void setup(std::unique_ptr<SymmBlock> b, int p_, int rank0_, int nlocal_) {
@@ -92,8 +93,8 @@ struct DeviceCommunicator::Impl {
     if (status_host) AL_WARN_CUDA(cudaFreeHost(status_host));
   }
 
-  static size_t block_bytes(int p, size_t half, size_t slot) {
-    return FlagLayout::bytes + 2 * half + (size_t)p * 2 * slot + kLLAreaBytes;
+  static size_t block_bytes(int p, size_t half, size_t slot, int slots) {
+    return FlagLayout::bytes + 2 * half + (size_t)p * (size_t)slots * slot + kLLAreaBytes;
   }
 
   int free_window() const {
@@ -141,6 +142,7 @@ namespace {
 
 size_t half_bytes_cfg() { return tuning().dev_stage_bytes / 4096 * 4096; }
 size_t slot_bytes_cfg() { return std::max<size_t>(4096, tuning().dev_mailbox_bytes / 4096 * 4096); }
+int slots_cfg() { return std::max(2, std::min(16, tuning().dev_mailbox_slots)); }
 
 void require_device() {
   if (!cuda::device_usable()) throw_al_exception("the device backend needs a CUDA device, none is usable in this process");
@@ -166,9 +168,11 @@ DeviceCommunicator::DeviceCommunicator(const Group& group, cudaStream_t stream)
                            "': split the communicator by node, or use the host-transfer backend across nodes");
   }
   const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
-  auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot), true);
+  const int slots = slots_cfg();
+  auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot, slots), true);
   impl_->ws.half_bytes = half;
   impl_->ws.mbox_slot_bytes = slot;
+  impl_->ws.mbox_slots = slots;
   impl_->setup(std::move(block), group.size(), group.rank(), 1);
 }
 
@@ -179,9 +183,11 @@ DeviceCommunicator DeviceCommunicator::emulated(int p, cudaStream_t stream) {
   require_device();
   auto impl = std::make_shared<Impl>();
   const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
-  auto block = SymmBlock::create_emulated(p, Impl::block_bytes(p, half, slot));
+  const int slots = slots_cfg();
+  auto block = SymmBlock::create_emulated(p, Impl::block_bytes(p, half, slot, slots));
   impl->ws.half_bytes = half;
   impl->ws.mbox_slot_bytes = slot;
+  impl->ws.mbox_slots = slots;
   impl->emulated = true;
   impl->setup(std::move(block), p, 0, p);
   return DeviceCommunicator(std::move(impl), Group(), stream);
@@ -296,6 +302,55 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   if (!reduces && !(in == wire && wire == out) && !collective_supported(in, wire, out, ReductionOperator::sum))
     throw_al_exception("device backend: no kernel for this datatype conversion");
 
+  // Small uniform allreduce / reduce_scatter / allgather / alltoall travel as low-latency packets.  This
+  // is decided first, before anything else is prepared: these calls are all about the time the host spends
+  // here.  Eligibility depends on facts every rank shares (operation, count, type), so the ranks agree.
+  {
+    const bool ll_kind = d.kind == DevColl::allreduce || d.kind == DevColl::reduce_scatter ||
+                         d.kind == DevColl::allgather || d.kind == DevColl::alltoall;
+    const size_t esz_ll = dtype_size(wire);
+    const size_t pair_bytes = d.count * unit * esz_ll;  // what one rank sends to another
+    const bool fits = ll_kind && !d.vector && p > 1 && in == wire && wire == out && d.count > 0 &&
+                      pair_bytes <= kLLPayloadBytes && ll_supported(d.kind, wire, d.op);
+    const bool forced = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::ll : d.path == CollPath::ll;
+    const bool automatic = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::automatic : d.path == CollPath::automatic;
+    if (forced && !fits)
+      throw_al_exception("the low-latency path was requested but the operation does not qualify (uniform allreduce / "
+                         "reduce_scatter / allgather / alltoall of at most ", kLLPayloadBytes, " bytes per pair of ranks)");
+    const Tuning& tn = tuning();
+    if (fits && (forced || (automatic && pair_bytes <= tn.crossovers(p).ll_max_bytes))) {
+      LLParams L;
+      L.ws = I.ws;
+      for (int lr = 0; lr < I.nlocal; ++lr) {
+        L.send[I.rank0 + lr] = ranks[(size_t)lr].send;
+        L.recv[I.rank0 + lr] = ranks[(size_t)lr].recv;
+      }
+      L.count = d.count * unit;
+      L.seq = ++I.seq;
+      L.timeout_ns = I.timeout_ns;
+      L.scale = d.scale;
+      L.int_div = 1;
+      if (d.op == ReductionOperator::avg) {
+        if (dtype_is_float(wire)) L.scale *= 1.0 / p;
+        else L.int_div = p;
+      }
+      L.kind = (int)d.kind;
+      L.op = (int)d.op;
+      L.rank0 = I.rank0;
+      const size_t groups = ceil_div(pair_bytes, (size_t)16);
+      int lctas = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(groups, (size_t)256), (size_t)tn.ll_max_ctas));
+      if (I.nlocal > 1) lctas = std::max(1, std::min(lctas, I.sm_count / I.nlocal));
+      const int lthreads = groups <= 64 ? 64 : (groups <= 128 ? 128 : 256);
+      I.order_after_previous(stream);
+      I.stats.ops++;
+      I.stats.bytes += pair_bytes;
+      I.stats.kernels++;
+      I.stats.ll++;
+      launch_ll(L, wire, lctas, lthreads, I.nlocal, stream);
+      return;
+    }
+  }
+
   CollParams P{};
   P.ws = I.ws;
   P.seq = ++I.seq;
@@ -321,6 +376,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
 
   // ---- algorithm -----------------------------------------------------------------
   const Tuning& tn = tuning();
+  const Crossovers& X = tn.crossovers(p);
   const size_t bytes = P.count * esz;
   AllreduceAlgo algo = d.algo;
   bool zero_copy = false;
@@ -346,63 +402,24 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
                   tail_ok(sb_in, off_in) && tail_ok(sb_out, off_out);
     }
     if (algo == AllreduceAlgo::automatic) {
-      // Measured on 4 and 8 B200: the one-shot push wins for small messages (up to 256 KiB on
-      // <= 4 ranks, 16 KiB on 8), NVLS above, the two-shot push where NVLS does not apply.
-      const size_t one_shot_max = p == 2 ? tn.ar_oneshot_max_bytes * 8
-                                  : (p <= 4 ? tn.ar_oneshot_max_bytes : std::min<size_t>(tn.ar_oneshot_max_bytes, 16384));
-      if (bytes <= one_shot_max || p == 1) algo = AllreduceAlgo::one_shot;
+      // The one-shot push wins for small messages, NVLS above, the two-shot push where NVLS does not
+      // apply; the sizes come from the per-rank-count table of the tuning (al_info prints it).
+      if (bytes <= X.ar_oneshot_max_bytes || p == 1) algo = AllreduceAlgo::one_shot;
       // Two ranks: neither the switch nor a two-shot saves traffic (every algorithm moves S bytes each way), so
       // the one-shot push is used at every size; large messages run it pipelined (below).
       else if (p == 2 && !zero_copy) algo = AllreduceAlgo::one_shot;
-      else if (nvls_ok && (zero_copy || bytes >= tn.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
+      else if (nvls_ok && (zero_copy || bytes >= X.ar_nvls_min_bytes)) algo = AllreduceAlgo::nvls;
       else algo = AllreduceAlgo::two_shot;
     }
     if (algo != AllreduceAlgo::nvls) zero_copy = false;
     P.two_phase = algo == AllreduceAlgo::two_shot ? 1 : 0;
-  }
-
-
-  // Small uniform allreduce / reduce_scatter / allgather / alltoall travel as low-latency packets.
-  // Eligibility depends on facts every rank shares (operation, count, type), so the ranks agree.
-  {
-    const bool ll_kind = d.kind == DevColl::allreduce || d.kind == DevColl::reduce_scatter ||
-                         d.kind == DevColl::allgather || d.kind == DevColl::alltoall;
-    const size_t pair_bytes = P.count * esz;  // what one rank sends to another
-    const bool fits = ll_kind && !d.vector && p > 1 && in == wire && wire == out && P.count > 0 &&
-                      pair_bytes <= kLLPayloadBytes && ll_supported(d.kind, wire, d.op);
-    const bool forced = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::ll : d.path == CollPath::ll;
-    const bool automatic = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::automatic : d.path == CollPath::automatic;
-    if (forced && !fits)
-      throw_al_exception("the low-latency path was requested but the operation does not qualify (uniform allreduce / "
-                         "reduce_scatter / allgather / alltoall of at most ", kLLPayloadBytes, " bytes per pair of ranks)");
-    if (fits && (forced || (automatic && pair_bytes <= tn.ll_max_bytes))) {
-      LLParams L{};
-      L.ws = I.ws;
-      for (int lr = 0; lr < I.nlocal; ++lr) {
-        L.send[I.rank0 + lr] = ranks[(size_t)lr].send;
-        L.recv[I.rank0 + lr] = ranks[(size_t)lr].recv;
-      }
-      L.count = P.count;
-      L.seq = P.seq;
-      L.timeout_ns = P.timeout_ns;
-      L.scale = P.scale;
-      L.int_div = P.int_div;
-      L.kind = P.kind;
-      L.op = P.op;
-      L.rank0 = I.rank0;
-      const size_t groups = ceil_div(pair_bytes, (size_t)16);
-      int lctas = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(groups, (size_t)256), (size_t)tn.ll_max_ctas));
-      if (I.nlocal > 1) lctas = std::max(1, std::min(lctas, I.sm_count / I.nlocal));
-      const int lthreads = groups <= 64 ? 64 : (groups <= 128 ? 128 : 256);
-      I.order_after_previous(stream);
-      I.stats.ops++;
-      I.stats.bytes += bytes ? bytes : pair_bytes;
-      I.stats.kernels++;
-      I.stats.ll++;
-      launch_ll(L, wire, lctas, lthreads, I.nlocal, stream);
-      return;
+    if (algo == AllreduceAlgo::one_shot && in == wire && p > 1) {
+      bool aligned = true;
+      for (const RankArgs& a : ranks) aligned = aligned && a.send && (uintptr_t)a.send % 16 == 0;
+      P.own_direct = aligned ? 1 : 0;
     }
   }
+
 
   // Registered buffers: reduce_scatter (send side) and allgather / alltoall / bcast (receive side) run
   // straight on them.  The decision looks at this rank's buffers only; the kernels compare protocols
@@ -414,7 +431,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
                          d.kind == DevColl::alltoall || d.kind == DevColl::bcast;
     const size_t slice = P.count * esz;                                    // bytes per rank slice (bcast: the vector)
     const size_t total = d.kind == DevColl::bcast ? slice : slice * (size_t)p;
-    const bool wanted = d.path == CollPath::window || (d.path == CollPath::automatic && tn.window_enable && total >= tn.window_min_bytes);
+    const bool wanted = d.path == CollPath::window || (d.path == CollPath::automatic && tn.window_enable && total >= X.window_min_bytes);
     if (d.path == CollPath::window && (!kind_ok || d.vector || !(in == wire && wire == out) || !window_supported(d.kind, wire, d.op)))
       throw_al_exception("the window path serves uniform reduce_scatter (f32 / f16 / bf16: sum, avg, min, max), allgather, alltoall and bcast only");
     if (kind_ok && wanted && !d.vector && p > 1 && in == wire && wire == out && P.count > 0 &&
@@ -464,9 +481,9 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   // other half reduces chunk c, so the link never waits for the reduction.
   size_t slot_e = cap_e;
   const bool ar_pipelined = d.kind == DevColl::allreduce && p == 2 && algo == AllreduceAlgo::one_shot &&
-                            d.algo == AllreduceAlgo::automatic && bytes >= tn.ar_pipeline_min_bytes;
+                            d.algo == AllreduceAlgo::automatic && bytes >= X.ar_pipeline_min_bytes;
   if (((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
-       p > 1 && !use_window && P.count * esz >= tn.pipeline_min_bytes) || ar_pipelined) {
+       p > 1 && !use_window && P.count * esz >= X.pipeline_min_bytes) || ar_pipelined) {
     size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {
@@ -549,7 +566,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     N.recv = ranks[0].recv;
     N.count = P.count;
     N.chunks = P.local_chunks[I.rank0];
-    if (!zero_copy && bytes >= tn.nvls_pipeline_min_bytes) {
+    if (!zero_copy && bytes >= X.nvls_pipeline_min_bytes) {
       // pipelined flavour: chunks of 1/8 of the message (at least 16 MiB, at most a staging half);
       // smaller chunks are dominated by the per-chunk handshakes
       size_t chunk_b = std::max<size_t>(bytes / 8, size_t{16} << 20);
@@ -722,6 +739,10 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
     P2PParams P{};
     P.ws = I.ws;
     P.timeout_ns = I.timeout_ns;
+    P.windows = I.table_dev;
+    P.rendezvous_bytes = tuning().p2p_rendezvous_bytes ? tuning().p2p_rendezvous_bytes : ~size_t{0};
+    P.launch = ++I.p2p_launches;
+    size_t biggest_direct = 0;
     std::vector<uint64_t> used;  // keys taken in this launch
     size_t biggest = 0;
     for (size_t i = 0; i < items.size() && P.nitems < P2PParams::kMaxItems; ++i) {
@@ -740,6 +761,13 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
       P.peer[k] = it.peer;
       P.is_send[k] = it.is_send ? 1 : 0;
       P.owner[k] = owner;
+      if (!it.is_send && it.bytes >= P.rendezvous_bytes) {
+        // a registered receive buffer is announced to the sender, which then stores straight into it
+        size_t off = 0;
+        const int w = find_window(it.rbuf, it.bytes, &off, owner - I.rank0);
+        if (w >= 0) P.rdesc[k] = make_desc(w, off);
+      }
+      if (it.bytes >= P.rendezvous_bytes) biggest_direct = std::max(biggest_direct, it.bytes);
       auto& ctr = it.is_send ? I.p2p_sent : I.p2p_recvd;
       uint64_t& c = ctr[(size_t)(owner - I.rank0) * (size_t)I.p + (size_t)it.peer];
       P.base[k] = c;
@@ -749,7 +777,9 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
       --remaining;
       I.stats.bytes += it.bytes;
     }
-    int per = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(std::min(biggest, slot), (size_t)65536), (size_t)tuning().p2p_max_ctas));
+    // CTAs per transfer: one per 64 KiB of a mailbox piece - or of the whole message where it may go straight
+    // into a registered buffer - up to the tuning's cap.
+    int per = (int)std::max<size_t>(1, std::min<size_t>(ceil_div(std::max(std::min(biggest, slot), biggest_direct), (size_t)65536), (size_t)tuning().p2p_max_ctas));
     if (I.nlocal > 1) per = std::max(1, std::min(per, I.sm_count / P.nitems));
     else per = std::max(1, std::min(per, 2 * I.sm_count / P.nitems));  // waiting CTAs must all be resident
     P.ctas_per_item = per;

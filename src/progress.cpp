@@ -1,6 +1,8 @@
 // The progress engine thread (see al/progress.hpp for the contract).
 #include "al/progress.hpp"
 
+#include <fstream>
+#include <algorithm>
 #include <memory>
 
 #include <pthread.h>
@@ -27,6 +29,41 @@ namespace internal {
 
 // Implemented by the CUDA layer; a weak no-op keeps host-only tools linkable.
 void pe_make_device_current(int dev);
+std::string pe_device_pci_bus_id(int dev);
+
+std::vector<int> parse_cpulist(const std::string& text) {
+  // sysfs format: "0-31,64-95" (ranges and single numbers, comma separated)
+  std::vector<int> out;
+  size_t i = 0;
+  auto number = [&](int& v) {
+    if (i >= text.size() || !isdigit((unsigned char)text[i])) return false;
+    v = 0;
+    while (i < text.size() && isdigit((unsigned char)text[i])) v = v * 10 + (text[i++] - '0');
+    return true;
+  };
+  while (i < text.size()) {
+    int a = 0, b = 0;
+    if (!number(a)) { ++i; continue; }
+    b = a;
+    if (i < text.size() && text[i] == '-') { ++i; if (!number(b)) b = a; }
+    for (int c = a; c <= b && c < CPU_SETSIZE; ++c) out.push_back(c);
+  }
+  return out;
+}
+
+int choose_pe_core(const std::vector<int>& allowed, const std::vector<int>& near_gpu, long local_rank) {
+  if (allowed.size() < 2) return -1;  // nothing to gain, and never steal the only core
+  // Cores that are both allowed and local to the GPU; all allowed cores when that set is empty.
+  std::vector<int> pool;
+  for (int c : near_gpu)
+    if (std::find(allowed.begin(), allowed.end(), c) != allowed.end()) pool.push_back(c);
+  if (pool.empty()) pool = allowed;
+  std::sort(pool.begin(), pool.end());
+  // The highest-numbered cores are the least likely to run the application's main threads; co-located
+  // ranks step down from the top by their node-local rank so that they do not share a core.
+  const size_t idx = pool.size() - 1 - (size_t)(local_rank % (long)pool.size());
+  return pool[idx];
+}
 
 ProgressEngine::ProgressEngine() = default;
 
@@ -134,21 +171,33 @@ std::ostream& ProgressEngine::dump_state(std::ostream& os) {
 
 void ProgressEngine::bind() {
   if (!tuning().pe_bind_thread) return;
-  // Choose the highest-numbered core this process may run on, stepping down by
-  // the node-local rank so that co-located ranks do not pile onto one core.
+  // The thread polls flags that the GPU writes into pinned host memory and answers with stores the GPU
+  // waits for: it belongs on a core of the socket the GPU hangs off (the reference asks hwloc for the
+  // GPU's cpuset, src/progress.cpp:394-495; here the kernel's own answer is read from sysfs:
+  // /sys/bus/pci/devices/<bus id>/local_cpulist).  AL_PE_CORE pins it to a given core instead.
   cpu_set_t mask;
   CPU_ZERO(&mask);
   if (sched_getaffinity(0, sizeof(mask), &mask) != 0) return;
-  std::vector<int> cores;
+  std::vector<int> allowed;
   for (int c = 0; c < CPU_SETSIZE; ++c)
-    if (CPU_ISSET(c, &mask)) cores.push_back(c);
-  if (cores.size() < 2) return;  // nothing to gain, and never steal the only core
-  long local_rank = env_long("AL_LOCAL_RANK", env_long("LOCAL_RANK", 0));
-  size_t idx = cores.size() - 1 - (size_t)(local_rank % (long)cores.size());
+    if (CPU_ISSET(c, &mask)) allowed.push_back(c);
+  int core = (int)env_long("AL_PE_CORE", -1);
+  if (core < 0) {
+    std::vector<int> near_gpu;
+    const std::string bus = device_ >= 0 ? pe_device_pci_bus_id(device_) : std::string();
+    if (!bus.empty()) {
+      std::ifstream f("/sys/bus/pci/devices/" + bus + "/local_cpulist");
+      std::string line;
+      if (f && std::getline(f, line)) near_gpu = parse_cpulist(line);
+    }
+    near_gpu_cores_ = (int)near_gpu.size();
+    core = choose_pe_core(allowed, near_gpu, env_long("AL_LOCAL_RANK", env_long("LOCAL_RANK", 0)));
+  }
+  if (core < 0) return;
   cpu_set_t one;
   CPU_ZERO(&one);
-  CPU_SET(cores[idx], &one);
-  if (pthread_setaffinity_np(pthread_self(), sizeof(one), &one) == 0) bound_core_ = cores[idx];
+  CPU_SET(core, &one);
+  if (pthread_setaffinity_np(pthread_self(), sizeof(one), &one) == 0) bound_core_ = core;
 }
 
 void ProgressEngine::engine() {

@@ -33,10 +33,6 @@ void Tuning::load_from_env() {
   dev_mailbox_bytes = (size_t)env_long("AL_DEV_MAILBOX_BYTES", (long)dev_mailbox_bytes);
   dev_wait_timeout_ms = env_double("AL_DEV_WAIT_TIMEOUT_MS", dev_wait_timeout_ms);
   dev_enable_nvls = env_long("AL_DEV_NVLS", dev_enable_nvls) != 0;
-  ar_oneshot_max_bytes = (size_t)env_long("AL_AR_ONESHOT_MAX", (long)ar_oneshot_max_bytes);
-  ar_nvls_min_bytes = (size_t)env_long("AL_AR_NVLS_MIN", (long)ar_nvls_min_bytes);
-  pipeline_min_bytes = (size_t)env_long("AL_PIPELINE_MIN", (long)pipeline_min_bytes);
-  nvls_pipeline_min_bytes = (size_t)env_long("AL_NVLS_PIPELINE_MIN", (long)nvls_pipeline_min_bytes);
   max_ctas = (int)env_long("AL_MAX_CTAS_PER_OP", max_ctas);
   max_ctas_nvls = (int)env_long("AL_MAX_CTAS_NVLS", max_ctas_nvls);
   max_ctas_zero_copy = (int)env_long("AL_MAX_CTAS_ZERO_COPY", max_ctas_zero_copy);
@@ -45,11 +41,25 @@ void Tuning::load_from_env() {
   bulk_pipeline = env_long("AL_DEV_BULK_PIPELINE", bulk_pipeline) != 0;
   bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
   bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
-  ar_pipeline_min_bytes = (size_t)env_long("AL_AR_PIPELINE_MIN", (long)ar_pipeline_min_bytes);
-  ll_max_bytes = (size_t)env_long("AL_LL_MAX", (long)ll_max_bytes);
   ll_max_ctas = (int)env_long("AL_LL_CTAS", ll_max_ctas);
+  dev_mailbox_slots = (int)env_long("AL_DEV_MAILBOX_SLOTS", dev_mailbox_slots);
+  p2p_rendezvous_bytes = (size_t)env_long("AL_P2P_RENDEZVOUS", (long)p2p_rendezvous_bytes);
+  {
+    struct Entry { const char* env; size_t Crossovers::*field; };
+    static const Entry entries[] = {
+        {"AL_LL_MAX", &Crossovers::ll_max_bytes}, {"AL_AR_ONESHOT_MAX", &Crossovers::ar_oneshot_max_bytes},
+        {"AL_AR_NVLS_MIN", &Crossovers::ar_nvls_min_bytes}, {"AL_AR_PIPELINE_MIN", &Crossovers::ar_pipeline_min_bytes},
+        {"AL_NVLS_PIPELINE_MIN", &Crossovers::nvls_pipeline_min_bytes}, {"AL_PIPELINE_MIN", &Crossovers::pipeline_min_bytes},
+        {"AL_WINDOW_MIN", &Crossovers::window_min_bytes}};
+    static const char* suffix[3] = {"_P2", "_P4", "_P8"};
+    for (const Entry& e : entries)
+      for (int row = 0; row < 3; ++row) {
+        long v = env_long(e.env, -1);
+        v = env_long((std::string(e.env) + suffix[row]).c_str(), v);
+        if (v >= 0) cross[row].*(e.field) = (size_t)v;
+      }
+  }
   window_enable = env_long("AL_WINDOW", window_enable) != 0;
-  window_min_bytes = (size_t)env_long("AL_WINDOW_MIN", (long)window_min_bytes);
   window_ctas = (int)env_long("AL_WINDOW_CTAS", window_ctas);
   window_multimem = env_long("AL_WINDOW_MULTIMEM", window_multimem) != 0;
   trace = env_long("AL_TRACE", trace) != 0;
@@ -102,10 +112,6 @@ std::string Tuning::describe() const {
      << "dev_mailbox_bytes = " << dev_mailbox_bytes << "\n"
      << "dev_wait_timeout_ms = " << dev_wait_timeout_ms << "\n"
      << "dev_enable_nvls = " << dev_enable_nvls << "\n"
-     << "ar_oneshot_max_bytes = " << ar_oneshot_max_bytes << "\n"
-     << "ar_nvls_min_bytes = " << ar_nvls_min_bytes << "\n"
-     << "pipeline_min_bytes = " << pipeline_min_bytes << "\n"
-     << "nvls_pipeline_min_bytes = " << nvls_pipeline_min_bytes << "\n"
      << "max_ctas = " << max_ctas << "\n"
      << "max_ctas_nvls = " << max_ctas_nvls << "\n"
      << "max_ctas_zero_copy = " << max_ctas_zero_copy << "\n"
@@ -114,13 +120,20 @@ std::string Tuning::describe() const {
      << "bulk_pipeline = " << bulk_pipeline << "\n"
      << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
      << "bulk_con_ctas = " << bulk_con_ctas << "\n"
-     << "ar_pipeline_min_bytes = " << ar_pipeline_min_bytes << "\n"
-     << "ll_max_bytes = " << ll_max_bytes << "\n"
      << "ll_max_ctas = " << ll_max_ctas << "\n"
+     << "dev_mailbox_slots = " << dev_mailbox_slots << "\n"
+     << "p2p_rendezvous_bytes = " << p2p_rendezvous_bytes << "\n"
      << "window_enable = " << window_enable << "\n"
-     << "window_min_bytes = " << window_min_bytes << "\n"
      << "window_ctas = " << window_ctas << "\n"
      << "window_multimem = " << window_multimem << "\n"
+     << "crossovers (bytes)      2 ranks      3-4 ranks      5-8 ranks\n"
+     << "  ll_max_bytes            " << cross[0].ll_max_bytes << "  " << cross[1].ll_max_bytes << "  " << cross[2].ll_max_bytes << "\n"
+     << "  ar_oneshot_max_bytes    " << cross[0].ar_oneshot_max_bytes << "  " << cross[1].ar_oneshot_max_bytes << "  " << cross[2].ar_oneshot_max_bytes << "\n"
+     << "  ar_nvls_min_bytes       " << cross[0].ar_nvls_min_bytes << "  " << cross[1].ar_nvls_min_bytes << "  " << cross[2].ar_nvls_min_bytes << "\n"
+     << "  ar_pipeline_min_bytes   " << cross[0].ar_pipeline_min_bytes << "  " << cross[1].ar_pipeline_min_bytes << "  " << cross[2].ar_pipeline_min_bytes << "\n"
+     << "  nvls_pipeline_min_bytes " << cross[0].nvls_pipeline_min_bytes << "  " << cross[1].nvls_pipeline_min_bytes << "  " << cross[2].nvls_pipeline_min_bytes << "\n"
+     << "  pipeline_min_bytes      " << cross[0].pipeline_min_bytes << "  " << cross[1].pipeline_min_bytes << "  " << cross[2].pipeline_min_bytes << "\n"
+     << "  window_min_bytes        " << cross[0].window_min_bytes << "  " << cross[1].window_min_bytes << "  " << cross[2].window_min_bytes << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
      << "signal_handler = " << signal_handler << "\n"

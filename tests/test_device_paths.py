@@ -329,3 +329,38 @@ def test_row_exchange_strided_indexed_and_chunked(al, p):
             assert torch.equal(back[r], shards[r])
         assert comm.stats()["rows"] == before + 2 and comm.status()["code"] == 0
     comm.close()
+
+
+@pytest.mark.parametrize("p", [2, 4])
+def test_p2p_ring_of_slots_and_rendezvous_into_registered_buffers(al, p):
+    """Point-to-point: a message of many pieces through the mailbox ring (more pieces than slots), and large
+    messages that wait for the receiver and go straight into its registered buffer (no mailbox, no copy-out)."""
+    old = al.get_tuning("dev_mailbox_bytes")
+    al.set_tuning("dev_mailbox_bytes", 1 << 20)     # 1 MiB slots: a 9 MiB message is 9 pieces through 4 slots
+    comm = al.DeviceComm(emulate=p)
+    al.set_tuning("dev_mailbox_bytes", old)
+    comm.set_timeout_ms(3000)
+    n = 9 * 256 * 1024 + 17                          # floats: 9 MiB and a ragged tail
+    for registered in (False, True):
+        src = [rand(n, torch.float32, 800 + r) for r in range(p)]
+        dst = [torch.full((n + 4,), -1.0, device="cuda") for _ in range(p)]
+        if registered:
+            assert comm.register(dst) >= 0
+        for it in range(2):
+            items = []
+            for r in range(p):
+                items.append((True, (r + 1) % p, src[r], r))
+                items.append((False, (r - 1) % p, dst[r][:n], r))
+            comm.p2p(items)
+            small = [torch.full((8,), float(r), device="cuda") for r in range(p)]
+            got = [torch.zeros(8, device="cuda") for _ in range(p)]
+            comm.p2p([x for r in range(p) for x in ((True, (r + 1) % p, small[r], r), (False, (r - 1) % p, got[r], r))])
+            torch.cuda.synchronize()
+            assert comm.status()["code"] == 0, comm.status()
+            for r in range(p):
+                assert torch.equal(dst[r][:n], src[(r - 1) % p])
+                assert torch.all(dst[r][n:] == -1.0)
+                assert torch.all(got[r] == float((r - 1) % p))
+        if registered:
+            comm.unregister(dst)
+    comm.close()

@@ -73,7 +73,7 @@ def _declare(lib) -> None:
         "al_dev_time_collective": (i, [vp, i, vp, vp, sz, i, i, i, i, vp, C.POINTER(C.c_float)]),
         "al_dev_p2p": (i, [vp, i, ip, ip, ip, vpp, szp, vp, vpp]),
         "al_dev_test": (i, [vpp, ip]), "al_dev_wait": (i, [vpp]),
-        "al_dev_symm_alloc": (vp, [vp, sz]), "al_dev_symm_free": (i, [vp, vp]),
+        "al_dev_check_guards": (i, [vp]), "al_dev_symm_alloc": (vp, [vp, sz]), "al_dev_symm_free": (i, [vp, vp]),
         "al_dev_symm_peer_ptr": (vp, [vp, vp, i]),
         "al_rma_attach": (vp, [vp, vp, i]), "al_rma_detach": (i, [vp, vp, i]),
         "al_rma_put": (i, [vp, vp, i, vp, sz]), "al_rma_get": (i, [vp, vp, i, vp, sz]), "al_rma_notify": (i, [vp, i]), "al_rma_wait": (i, [vp, i]),

@@ -375,6 +375,11 @@ class DeviceComm:
         self._symm[out[0].data_ptr()] = base
         return out
 
+    def check_guards(self) -> None:
+        """Guard mode (``set_tuning("debug_guard", 1)`` before allocating): raises if anything wrote outside a
+        :meth:`symm_empty` tensor of this rank (4 KiB of a known pattern sit before and after each)."""
+        check(self._lib.al_dev_check_guards(self._h))
+
     def symm_free(self, tensor) -> None:
         t = tensor[0] if isinstance(tensor, (list, tuple)) else tensor
         base = self._symm.pop(t.data_ptr(), None)

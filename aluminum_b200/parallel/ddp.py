@@ -41,7 +41,7 @@ class DataParallel:
 
     def __init__(self, module: nn.Module, comm=None, bucket_bytes: int = 25 * 1024 * 1024, lr: float = 0.1,
                  momentum: float = 0.9, weight_decay: float = 0.0, wire_dtype: Optional[torch.dtype] = None,
-                 symmetric_grads: bool = True):
+                 symmetric_grads: bool = True, timeline: bool = False):
         self.module = module
         self.comm = comm
         self.world = comm.size if comm is not None else 1
@@ -49,6 +49,12 @@ class DataParallel:
         self.wire_dtype = wire_dtype
         self.steps = 0
         self.launches = 0  # kernels of this library launched so far (allreduces + optimizer steps)
+        # Optional per-step timeline (CUDA events on the compute stream): when each bucket became ready, when
+        # backward ended, when each bucket's averaged gradients were available to the optimizer.
+        self.timeline = timeline
+        self._tl_ready, self._tl_avail = {}, {}
+        self._tl_bwd_end = self._tl_done = self._tl_start = None
+        self.timeline_log: List[dict] = []
 
         params = [p for p in module.parameters() if p.requires_grad]
         assert all(p.dtype == torch.float32 and p.is_cuda for p in params), "fp32 CUDA parameters expected"
@@ -125,6 +131,10 @@ class DataParallel:
         b = self._bucket_of[p]
         b.pending -= 1
         if b.pending == 0:
+            if self.timeline:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                self._tl_ready[id(b)] = ev
             # Bucket complete: average it across ranks in the background.
             b.req = self.comm.allreduce(b.view, op="sum", scale=1.0 / self.world, nonblocking=True,
                                         wire_dtype=self.wire_dtype)
@@ -135,10 +145,17 @@ class DataParallel:
 
     def finish_gradients(self) -> None:
         """Join every outstanding bucket allreduce on the compute stream (host does not block)."""
+        if self.timeline:
+            self._tl_bwd_end = torch.cuda.Event(enable_timing=True)
+            self._tl_bwd_end.record()
         for b in self.buckets:
             if b.req is not None:
                 b.req.wait()
                 b.req = None
+                if self.timeline:
+                    ev = torch.cuda.Event(enable_timing=True)
+                    ev.record()
+                    self._tl_avail[id(b)] = ev
             b.pending = b.total
 
     def step(self) -> None:
@@ -148,6 +165,36 @@ class DataParallel:
                           1.0, first_step=(self.steps == 0), zero_grad=True)
         self.launches += 1
         self.steps += 1
+
+    def mark_step_start(self) -> None:
+        """Timeline mode: call at the start of a step (before forward)."""
+        if self.timeline:
+            self._tl_start = torch.cuda.Event(enable_timing=True)
+            self._tl_start.record()
+
+    def collect_timeline(self) -> Optional[dict]:
+        """Timeline mode: synchronise and return this step's record (milliseconds relative to the end of backward):
+        when each bucket was handed to the allreduce, when its result was available, and the exposed tail."""
+        if not self.timeline or self._tl_bwd_end is None:
+            return None
+        torch.cuda.synchronize()
+        end = self._tl_bwd_end
+        rec = {"buckets": []}
+        if self._tl_start is not None:
+            rec["step_start_ms"] = -self._tl_start.elapsed_time(end)
+        last = 0.0
+        for i, b in enumerate(self.buckets):
+            r, a = self._tl_ready.get(id(b)), self._tl_avail.get(id(b))
+            if r is None or a is None:
+                continue
+            avail = end.elapsed_time(a)
+            rec["buckets"].append({"bucket": i, "mbytes": (b.hi - b.lo) * 4 / 1e6, "ready_ms": -r.elapsed_time(end),
+                                   "available_ms": avail})
+            last = max(last, avail)
+        rec["exposed_tail_ms"] = last
+        self._tl_ready.clear(); self._tl_avail.clear()
+        self.timeline_log.append(rec)
+        return rec
 
     def state_dict(self) -> dict:
         return {"model": self.module.state_dict(), "momentum": self.flat_mom.clone(), "steps": self.steps}

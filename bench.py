@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-collectives", action="store_true")
     ap.add_argument("--coll-max-bytes", type=int, default=1 << 30, help="largest vector of the collective sweep")
+    ap.add_argument("--timeline", type=str, default="", help="(ours) after the timed runs, write a per-bucket timeline of a "
+                    "few extra steps to this file: when each gradient bucket was ready, when its average was available")
     return ap.parse_args()
 
 
@@ -378,6 +380,23 @@ def main():
         torch.cuda.synchronize()
         collectives = collectives_block(lambda k, s, w, i: arm.time_collective(bufs, k, s, w, i), world,
                                         arm.max_over_ranks, a.coll_max_bytes)
+
+    if a.timeline and a.impl == "ours" and world > 1:
+        dp = arm.dp
+        dp.timeline = True
+        xd2, yd2 = xh.cuda(non_blocking=True), yh.cuda(non_blocking=True)
+        recs = []
+        for i in range(6):
+            dp.mark_step_start()
+            arm.device_step(xd2, yd2)
+            r = dp.collect_timeline()
+            if i >= 2 and r is not None:
+                recs.append(r)
+        dp.timeline = False
+        tails = [arm.max_over_ranks(r["exposed_tail_ms"]) for r in recs]
+        if rank == 0:
+            with open(a.timeline, "w") as f:
+                json.dump({"n_gpus": world, "exposed_tail_ms_max_over_ranks": tails, "rank0_steps": recs}, f, indent=1)
 
     if rank == 0:
         out = {"metric": "ResNet-50 data-parallel training throughput", "value": value, "unit": "images/s",

@@ -429,10 +429,19 @@ int run_all(const Args& a) {
     // threads never share a communicator (test/test_ops.cpp:373-391 of the reference).
     std::vector<typename Backend::comm_type> comms;
     for (int t = 0; t < nthreads; ++t) comms.push_back(make_thread_comm<Backend>(comm));
+    int thread_device = -1;
+#ifdef AL_HAS_CUDA
+    if (Al::internal::cuda::device_usable()) (void)cudaGetDevice(&thread_device);
+#endif
     std::vector<int> rc((size_t)nthreads, 0);
     std::vector<std::thread> th;
     for (int t = 0; t < nthreads; ++t)
-      th.emplace_back([&, t] { rc[(size_t)t] = sweep<Backend, T>(comms[(size_t)t], c, sizes, trials, dog); });
+      th.emplace_back([&, t] {
+#ifdef AL_HAS_CUDA
+        if (thread_device >= 0) (void)cudaSetDevice(thread_device);  // the test's own copies need it; the library sets it itself
+#endif
+        rc[(size_t)t] = sweep<Backend, T>(comms[(size_t)t], c, sizes, trials, dog);
+      });
     for (auto& x : th) x.join();
     for (int r : rc) failed += r;
     for (auto& cm : comms) release_thread_comm<Backend>(cm);

@@ -153,6 +153,8 @@ int al_dev_test(void** req, int* done);
 int al_dev_wait(void** req);
 void* al_dev_symm_alloc(void* comm, size_t bytes);
 int al_dev_symm_free(void* comm, void* ptr);
+/** Guard mode (tuning entry debug_guard): fails if anything wrote outside a symm_alloc buffer of this rank. */
+int al_dev_check_guards(void* comm);
 /** Address of rank `peer`'s copy of the symmetric allocation that contains `local_ptr`. */
 void* al_dev_symm_peer_ptr(void* comm, void* local_ptr, int peer);
 

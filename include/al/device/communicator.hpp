@@ -98,6 +98,29 @@ struct CommStats {
 }  // namespace device
 }  // namespace internal
 
+/**
+ * Makes a communicator's device current for the calling thread for the duration of a call and restores the
+ * previous one.  A thread that was never told which device to use (cudaSetDevice is per thread) would
+ * otherwise launch on device 0 into streams of another device.
+ */
+class ScopedDevice {
+ public:
+  explicit ScopedDevice(int device) {
+    if (cudaGetDevice(&prev_) == cudaSuccess && prev_ != device && device >= 0) {
+      switched_ = cudaSetDevice(device) == cudaSuccess;
+    }
+  }
+  ~ScopedDevice() {
+    if (switched_) (void)cudaSetDevice(prev_);
+  }
+  ScopedDevice(const ScopedDevice&) = delete;
+  ScopedDevice& operator=(const ScopedDevice&) = delete;
+
+ private:
+  int prev_ = -1;
+  bool switched_ = false;
+};
+
 class DeviceCommunicator {
  public:
   /** World communicator on the default stream (collective). */
@@ -124,6 +147,8 @@ class DeviceCommunicator {
   cudaStream_t get_stream() const { return stream_; }
   const internal::Group& group() const { return group_; }
   bool is_emulated() const;
+  /** The CUDA device the communicator was created on (its workspace, streams and kernels live there). */
+  int device() const;
   bool has_multicast() const;
   const char* memory_backing() const;
 
@@ -161,6 +186,12 @@ class DeviceCommunicator {
   int register_buffers_emulated(const std::vector<void*>& ptrs, size_t bytes);
   /** Window containing [ptr, ptr+bytes) of local rank `local_rank`, or -1; *offset = distance from its start. */
   int find_window(const void* ptr, size_t bytes, size_t* offset, int local_rank = 0) const;
+  /**
+   * Guard mode (tuning().debug_guard / AL_DEBUG_GUARD=1): every symm_alloc block carries a 4 KiB region of a
+   * known pattern before and after the user's bytes.  Synchronises the device and throws al_exception if any
+   * guard of this rank's blocks was overwritten (naming block, side and distance).  symm_free runs it too.
+   */
+  void check_guards() const;
   /** The symmetric block containing `ptr`, or nullptr. */
   const internal::device::SymmBlock* find_symm(const void* ptr, size_t bytes, size_t* offset) const;
 

@@ -117,7 +117,7 @@ struct DeviceStatus {
  * between the data and a flag (the role of NCCL's LL protocol, which the reference gets from ncclAllReduce
  * & co. at these sizes).  One slot per (parity of the operation number, source rank).
  */
-constexpr size_t kLLPayloadBytes = 65536;
+constexpr size_t kLLPayloadBytes = 262144;
 constexpr size_t kLLSlotBytes = 2 * kLLPayloadBytes;
 constexpr size_t kLLAreaBytes = 2 * (size_t)kMaxRanks * kLLSlotBytes;
 
@@ -200,7 +200,7 @@ struct WinParams {
   int op;
   int root;
   int rank0;
-  int allow_multimem;            ///< 0: plain peer loads / stores only (tuning, tests of rank failure)
+  int allow_multimem;            ///< bit 0: multimem for reduce_scatter / bcast, bit 1: for allgather; 0: plain peer loads / stores only
 };
 
 /** Arguments of one launch of the low-latency kernel (kernels/ll.cu).  Indexed by rank like CollParams. */

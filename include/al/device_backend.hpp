@@ -102,6 +102,7 @@ class DeviceBackend {
   static void run(internal::Resolved&& r, comm_type& comm, req_type* req, int path = 0,
                   DeviceAllreduceAlgo algo = DeviceAllreduceAlgo::automatic) {
     using namespace internal::device;
+    ScopedDevice on_device(comm.device());
     CollDesc d;
     d.kind = (DevColl)(int)r.kind;
     d.in = d.wire = d.out = r.dt;
@@ -131,6 +132,7 @@ class DeviceBackend {
   }
   static void run_p2p(std::vector<internal::device::P2PDesc>&& items, comm_type& comm, req_type* req, const char*) {
     using namespace internal::device;
+    ScopedDevice on_device(comm.device());
     if (req) {
       cudaStream_t s = begin_nonblocking(comm);
       comm.p2p(items, s);

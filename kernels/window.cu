@@ -95,6 +95,40 @@ __device__ __forceinline__ void multicast_copy(char* mc_dst, const char* src, si
   for (; v < nvec; v += stride) mm_st(mc_dst + (v << 4), s[v]);
 }
 
+/**
+ * Copy [0, n) of `src` to every destination.  When source and destinations are 16-byte aligned the vectors
+ * are stored to all destinations in turn (every link and the local memory stay busy at the same time);
+ * otherwise one destination after the other with whatever width the alignment allows.
+ */
+__device__ __forceinline__ void fan_copy(char* const* dsts, int ndst, const char* src, size_t n) {
+  if (n == 0 || ndst == 0) return;
+  uintptr_t mis = (uintptr_t)src | (uintptr_t)n;
+  for (int d = 0; d < ndst; ++d) mis |= (uintptr_t)dsts[d];
+  if ((mis & 15) == 0) {
+    const uint4* s = (const uint4*)src;
+    const size_t nv = n >> 4, stride = blockDim.x;
+    size_t i = threadIdx.x;
+    for (; i + 3 * stride < nv; i += 4 * stride) {
+      const uint4 a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
+#pragma unroll
+      for (int d = 0; d < kMaxRanks; ++d) {
+        if (d < ndst) {
+          uint4* o = (uint4*)dsts[d];
+          o[i] = a; o[i + stride] = b; o[i + 2 * stride] = c; o[i + 3 * stride] = e;
+        }
+      }
+    }
+    for (; i < nv; i += stride) {
+      const uint4 a = s[i];
+#pragma unroll
+      for (int d = 0; d < kMaxRanks; ++d)
+        if (d < ndst) ((uint4*)dsts[d])[i] = a;
+    }
+    return;
+  }
+  for (int d = 0; d < ndst; ++d) cta_copy(dsts[d], src, n, false);
+}
+
 // ---------------------------------------------------------------------------------------------
 // allgather / alltoall / bcast: byte movement into registered receive buffers
 // ---------------------------------------------------------------------------------------------
@@ -123,18 +157,26 @@ __global__ void __launch_bounds__(512) window_move_kernel(const __grid_constant_
 
   if (kind == DevColl::allgather) {
     if (send && count) {
-      if (vec_ok) {
+      // A multicast store also comes back to its sender: p slices enter every GPU instead of p-1.  The host
+      // allows it for allgather (bit 1) only where saving p-2 store instructions per vector is worth that.
+      if (vec_ok && (P.allow_multimem & 2)) {
         // the switch delivers the slice to every rank, this one included
         multicast_copy(mc + (size_t)rank * count, send, count >> 4, cta, nct);
       } else {
         size_t lo, hi;
         split_range(count, cta, nct, 16, lo, hi);
-        for (int i = 0; i < p && hi > lo; ++i) {
-          const int d = (rank + 1 + i) % p;  // rotated: at any moment the ranks write to distinct peers
-          char* dst = window_addr(W, sh.recv[d], d, rank, recv) + (size_t)rank * count;
-          if (d == rank && dst == send) continue;  // in place: the contribution already sits there
-          cta_copy(dst + lo, send + lo, hi - lo, false);
+        char* dsts[kMaxRanks];
+        int n = 0;
+#pragma unroll
+        for (int i = 0; i < kMaxRanks; ++i) {
+          dsts[i] = nullptr;
+          if (i < p) {
+            const int d = (rank + 1 + i) % p;  // rotated: the ranks start on distinct peers
+            char* dst = window_addr(W, sh.recv[d], d, rank, recv) + (size_t)rank * count;
+            if (!(d == rank && dst == send)) dsts[n++] = dst + lo;  // in place: the contribution already sits there
+          }
         }
+        if (hi > lo) fan_copy(dsts, n, send + lo, hi - lo);
       }
     }
   } else if (kind == DevColl::alltoall) {
@@ -154,10 +196,14 @@ __global__ void __launch_bounds__(512) window_move_kernel(const __grid_constant_
       } else {
         size_t lo, hi;
         split_range(count, cta, nct, 16, lo, hi);
-        for (int i = 0; i < p - 1 && hi > lo; ++i) {
-          const int d = (rank + 1 + i) % p;
-          cta_copy(window_addr(W, sh.recv[d], d, rank, recv) + lo, send + lo, hi - lo, false);
+        char* dsts[kMaxRanks];
+        int n = 0;
+#pragma unroll
+        for (int i = 0; i < kMaxRanks; ++i) {
+          dsts[i] = nullptr;
+          if (i < p - 1) dsts[n++] = window_addr(W, sh.recv[(rank + 1 + i) % p], (rank + 1 + i) % p, rank, recv) + lo;
         }
+        if (hi > lo) fan_copy(dsts, n, send + lo, hi - lo);
       }
     }
   }

@@ -98,9 +98,9 @@ int al_info(char* buf, size_t buflen) {
 #define AL_TUNE_FIELDS(X)                                                                                      \
   X(pe_num_concurrent_ops) X(pe_hang_seconds) X(host_stage_bytes) X(host_mailbox_bytes) X(host_wait_timeout_s) \
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls)   \
-  X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(stream_pool_size)    \
+  X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(debug_guard) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(window_enable) X(window_ctas) X(window_multimem)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(window_enable) X(window_ctas) X(window_multimem) X(window_multimem_ag_ranks) X(window_rs_min_ranks)
 
 namespace {
 /** "ll_max_bytes" or "ll_max_bytes@4" -> member pointer and row (-1 = all rows); nullptr if not a crossover. */
@@ -320,6 +320,7 @@ int al_dev_collective(void* comm, int kind, int nlocal, const void* const* send,
                       void** req_out) {
   return guard([&] {
     DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    ScopedDevice on_device(c.device());
     const int p = c.size();
     const int expect = c.is_emulated() ? p : 1;
     if (nlocal != expect) throw_al_exception("expected ", expect, " local rank(s), got ", nlocal);
@@ -415,6 +416,7 @@ int al_dev_exchange_rows(void* comm, int nlocal, const void* const* send, void* 
                          void** req_out) {
   return guard([&] {
     DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    ScopedDevice on_device(c.device());
     const size_t p = (size_t)c.size();
     std::vector<device::RowArgs> ra((size_t)nlocal);
     for (int lr = 0; lr < nlocal; ++lr) {
@@ -489,6 +491,7 @@ int al_dev_p2p(void* comm, int n, const int* is_send, const int* peer, const int
                const size_t* bytes, void* stream, void** req_out) {
   return guard([&] {
     DeviceCommunicator& c = *(DeviceCommunicator*)comm;
+    ScopedDevice on_device(c.device());
     std::vector<device::P2PDesc> items((size_t)n);
     for (int i = 0; i < n; ++i) {
       items[(size_t)i].is_send = is_send[i] != 0;
@@ -533,6 +536,7 @@ void* al_dev_symm_alloc(void* comm, size_t bytes) {
   guard([&] { r = ((DeviceCommunicator*)comm)->symm_alloc(bytes); });
   return r;
 }
+int al_dev_check_guards(void* comm) { return guard([&] { ((DeviceCommunicator*)comm)->check_guards(); }); }
 int al_dev_symm_free(void* comm, void* ptr) { return guard([&] { ((DeviceCommunicator*)comm)->symm_free(ptr); }); }
 void* al_dev_symm_peer_ptr(void* comm, void* local_ptr, int peer) {
   void* r = nullptr;

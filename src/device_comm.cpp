@@ -33,6 +33,12 @@ struct DeviceCommunicator::Impl {
   cudaEvent_t chain_event = nullptr;
   std::vector<uint64_t> p2p_sent, p2p_recvd;  // [nlocal][p]
   std::vector<std::unique_ptr<SymmBlock>> user_blocks;
+  std::vector<size_t> user_guard;  // bytes of guard region before and after the user's part of each block (0: none)
+  size_t guard_of(const SymmBlock* b) const {
+    for (size_t i = 0; i < user_blocks.size(); ++i)
+      if (user_blocks[i].get() == b) return user_guard[i];
+    return 0;
+  }
   // Registered buffers.  Slot w describes window w on every rank; the device copy is what kernels read.
   struct Window {
     bool used = false;
@@ -214,6 +220,7 @@ DeviceCommunicator DeviceCommunicator::split(int color, int key, cudaStream_t st
 int DeviceCommunicator::rank() const { return impl_->emulated ? 0 : impl_->rank0; }
 int DeviceCommunicator::size() const { return impl_->p; }
 bool DeviceCommunicator::is_emulated() const { return impl_->emulated; }
+int DeviceCommunicator::device() const { return impl_->device; }
 bool DeviceCommunicator::has_multicast() const { return impl_->ws.mc_stage != nullptr; }
 const char* DeviceCommunicator::memory_backing() const { return impl_->block->backing(); }
 const Workspace& DeviceCommunicator::workspace() const { return impl_->ws; }
@@ -396,7 +403,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       // acceptable where the last vector ends in the block's own padding (symm_alloc pads to 16):
       // anywhere else the tail vector would overwrite the caller's elements after `count`.
       auto tail_ok = [&](const SymmBlock* b, size_t off) {
-        return bytes % 16 == 0 || round_up(off + bytes, 16) == b->bytes();
+        return bytes % 16 == 0 || round_up(off + bytes, 16) == b->bytes() - I.guard_of(b);
       };
       zero_copy = sb_in && sb_out && sb_in->mc() && sb_out->mc() && (off_in % 16 == 0) && (off_out % 16 == 0) &&
                   tail_ok(sb_in, off_in) && tail_ok(sb_out, off_out);
@@ -450,6 +457,11 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
           case DevColl::reduce_scatter:
             // in place (the result overwrites the start of the input other ranks still read) stays staged
             ok = sb && rb && !(rb < sb + total && sb < rb + slice) && (w = find_window(sb, total, &off, lr)) >= 0;
+            // Pulling slices with peer loads is slower than pushing them through staging (loads over NVLink stall
+            // their threads); left to itself the library takes the window path for reduce_scatter only where
+            // the switch does the reduction (multicast-bound window) and there are enough ranks for that to pay.
+            if (ok && d.path == CollPath::automatic)
+              ok = tn.window_multimem && I.table_host.mc[w] != nullptr && p >= tn.window_rs_min_ranks;
             if (ok) Wp.send_desc[r] = make_desc(w, off);
             break;
           case DevColl::allgather: {
@@ -604,7 +616,8 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     Wp.op = P.op;
     Wp.root = P.root;
     Wp.rank0 = I.rank0;
-    Wp.allow_multimem = tn.window_multimem ? 1 : 0;
+    // bit 0: multimem for reduce_scatter / bcast, bit 1: for allgather (only from window_multimem_ag_ranks ranks on)
+    Wp.allow_multimem = tn.window_multimem ? (1 | (p >= tn.window_multimem_ag_ranks ? 2 : 0)) : 0;
     const size_t moved = P.count * esz * (d.kind == DevColl::alltoall ? (size_t)p : 1);
     int wctas = d.ctas > 0 ? d.ctas : (int)std::max<size_t>(1, std::min<size_t>(ceil_div(moved, (size_t)32768), (size_t)tn.window_ctas));
     if (I.nlocal > 1) wctas = std::max(1, std::min(wctas, I.sm_count / I.nlocal));
@@ -793,28 +806,90 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
 // ---------------------------------------------------------------------------
 // symmetric user memory
 // ---------------------------------------------------------------------------
+namespace {
+constexpr size_t kGuardBytes = 4096;
+constexpr int kGuardByte = 0xA5;
+}  // namespace
+
 void* DeviceCommunicator::symm_alloc(size_t bytes) {
   Impl& I = *impl_;
   std::unique_ptr<SymmBlock> b;
   const size_t padded = round_up(std::max<size_t>(bytes, 16), 16);
-  if (I.emulated) b = SymmBlock::create_emulated(I.p, padded);
-  else b = SymmBlock::create(group_, padded, true);
-  void* ptr = b->peer(I.emulated ? 0 : I.rank0);
+  // Guard mode (AL_DEBUG_GUARD=1): a region of a known byte pattern before and after the user's part of
+  // every symmetric block; check_guards() (also run by symm_free) reports a kernel - of this library or of
+  // the caller - that wrote outside the buffer.  The stand-in for a memory checker on the device.
+  const size_t guard = tuning().debug_guard ? kGuardBytes : 0;
+  if (I.emulated) b = SymmBlock::create_emulated(I.p, padded + 2 * guard);
+  else b = SymmBlock::create(group_, padded + 2 * guard, true);
+  if (guard) {
+    for (int lr = 0; lr < I.nlocal; ++lr) {
+      char* base = (char*)b->peer(I.rank0 + lr);
+      AL_CHECK_CUDA(cudaMemset(base, kGuardByte, guard));
+      AL_CHECK_CUDA(cudaMemset(base + guard + padded, kGuardByte, guard));
+    }
+    AL_CHECK_CUDA(cudaDeviceSynchronize());
+    if (!I.emulated) group_.barrier();  // nobody uses the block before every rank's guards are in place
+  }
+  void* ptr = (char*)b->peer(I.emulated ? 0 : I.rank0) + guard;
   std::lock_guard<std::mutex> lock(I.mu);
   I.add_block_window(b.get());
   I.user_blocks.push_back(std::move(b));
+  I.user_guard.push_back(guard);
   return ptr;
+}
+
+void DeviceCommunicator::check_guards() const {
+  const Impl& I = *impl_;
+  AL_CHECK_CUDA(cudaDeviceSynchronize());
+  std::vector<unsigned char> h(kGuardBytes);
+  for (size_t i = 0; i < I.user_blocks.size(); ++i) {
+    const size_t guard = I.user_guard[i];
+    if (!guard) continue;
+    const SymmBlock* b = I.user_blocks[i].get();
+    for (int lr = 0; lr < I.nlocal; ++lr) {
+      const char* base = (const char*)b->peer(I.rank0 + lr);
+      for (int side = 0; side < 2; ++side) {
+        const char* g = side == 0 ? base : base + b->bytes() - guard;
+        AL_CHECK_CUDA(cudaMemcpy(h.data(), g, guard, cudaMemcpyDeviceToHost));
+        for (size_t k = 0; k < guard; ++k) {
+          if (h[k] == (unsigned char)kGuardByte) continue;
+          const long dist = side == 0 ? (long)k - (long)guard : (long)k;
+          throw_al_exception("guard region of symmetric block ", i, " (rank ", I.rank0 + lr, ") was overwritten: byte at ",
+                             side == 0 ? "offset " : "offset end+", dist, side == 0 ? " before the buffer" : " after the buffer",
+                             " holds ", (int)h[k]);
+        }
+      }
+    }
+  }
 }
 
 void DeviceCommunicator::symm_free(void* ptr) {
   Impl& I = *impl_;
   std::unique_ptr<SymmBlock> victim;
+  bool guarded = false;
   {
     std::lock_guard<std::mutex> lock(I.mu);
-    for (auto it = I.user_blocks.begin(); it != I.user_blocks.end(); ++it) {
-      if ((*it)->peer(I.emulated ? 0 : I.rank0) == ptr) {
-        victim = std::move(*it);
-        I.user_blocks.erase(it);
+    for (size_t i = 0; i < I.user_blocks.size(); ++i) {
+      if ((char*)I.user_blocks[i]->peer(I.emulated ? 0 : I.rank0) + I.user_guard[i] == ptr) {
+        if (I.user_guard[i]) {
+          guarded = true;
+          break;
+        }
+        victim = std::move(I.user_blocks[i]);
+        I.user_blocks.erase(I.user_blocks.begin() + (long)i);
+        I.user_guard.erase(I.user_guard.begin() + (long)i);
+        break;
+      }
+    }
+  }
+  if (guarded) {
+    check_guards();  // throws if anything wrote outside a guarded buffer; the block is then kept for inspection
+    std::lock_guard<std::mutex> lock(I.mu);
+    for (size_t i = 0; i < I.user_blocks.size(); ++i) {
+      if ((char*)I.user_blocks[i]->peer(I.emulated ? 0 : I.rank0) + I.user_guard[i] == ptr) {
+        victim = std::move(I.user_blocks[i]);
+        I.user_blocks.erase(I.user_blocks.begin() + (long)i);
+        I.user_guard.erase(I.user_guard.begin() + (long)i);
         break;
       }
     }

@@ -62,8 +62,17 @@ void Tuning::load_from_env() {
   window_enable = env_long("AL_WINDOW", window_enable) != 0;
   window_ctas = (int)env_long("AL_WINDOW_CTAS", window_ctas);
   window_multimem = env_long("AL_WINDOW_MULTIMEM", window_multimem) != 0;
+  window_multimem_ag_ranks = (int)env_long("AL_WINDOW_MULTIMEM_AG_RANKS", window_multimem_ag_ranks);
+  window_rs_min_ranks = (int)env_long("AL_WINDOW_RS_MIN_RANKS", window_rs_min_ranks);
   trace = env_long("AL_TRACE", trace) != 0;
+#ifdef AL_DEBUG_DEFAULT
+  debug_checks = true;   // built with ALUMINUM_ENABLE_DEBUG: checks are on unless AL_DEBUG=0
+#endif
+#ifdef AL_TRACE_DEFAULT
+  trace = true;          // built with ALUMINUM_ENABLE_TRACE
+#endif
   debug_checks = env_long("AL_DEBUG", debug_checks) != 0;
+  debug_guard = env_long("AL_DEBUG_GUARD", debug_guard) != 0;
   signal_handler = env_long("AL_DISABLE_SIGNAL_HANDLER", 0) == 0;
   fault_rank = (int)env_long("AL_FAULT_RANK", fault_rank);
   fault_op = env_long("AL_FAULT_OP", fault_op);
@@ -126,6 +135,8 @@ std::string Tuning::describe() const {
      << "window_enable = " << window_enable << "\n"
      << "window_ctas = " << window_ctas << "\n"
      << "window_multimem = " << window_multimem << "\n"
+     << "window_multimem_ag_ranks = " << window_multimem_ag_ranks << "\n"
+     << "window_rs_min_ranks = " << window_rs_min_ranks << "\n"
      << "crossovers (bytes)      2 ranks      3-4 ranks      5-8 ranks\n"
      << "  ll_max_bytes            " << cross[0].ll_max_bytes << "  " << cross[1].ll_max_bytes << "  " << cross[2].ll_max_bytes << "\n"
      << "  ar_oneshot_max_bytes    " << cross[0].ar_oneshot_max_bytes << "  " << cross[1].ar_oneshot_max_bytes << "  " << cross[2].ar_oneshot_max_bytes << "\n"
@@ -136,6 +147,7 @@ std::string Tuning::describe() const {
      << "  window_min_bytes        " << cross[0].window_min_bytes << "  " << cross[1].window_min_bytes << "  " << cross[2].window_min_bytes << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
+     << "debug_guard = " << debug_guard << "\n"
      << "signal_handler = " << signal_handler << "\n"
      << "fault_rank = " << fault_rank << "\n"
      << "fault_op = " << fault_op << "\n"

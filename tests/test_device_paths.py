@@ -20,7 +20,7 @@ def al():
         pytest.skip("no CUDA device")
     al.init()
     old = al.get_tuning("ll_max_bytes")
-    al.set_tuning("ll_max_bytes", 65536)   # the largest message the packet slots hold
+    al.set_tuning("ll_max_bytes", 262144)  # the largest message the packet slots hold
     yield al
     al.set_tuning("ll_max_bytes", old)
 
@@ -47,7 +47,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
     esz = torch.empty((), dtype=dtype).element_size()
-    sizes = [1, 3, 4, 5, 33, 1000, 65536 // esz]
+    sizes = [1, 3, 4, 5, 33, 1000, 262144 // esz]
     before = comm.stats()["ll"]
     calls = 0
     for it, n in enumerate(sizes):
@@ -66,7 +66,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
                 assert torch.equal(ys[r], outs[r][:n])                          # both forms, and every rank, bit-identical
             assert all(torch.equal(outs[0], o) for o in outs)
         # reduce_scatter: n elements per rank
-        if n * esz <= 65536:
+        if n * esz <= 262144:
             xs = [rand(n * p, dtype, 50 + 10 * it + r) for r in range(p)]
             want = ref_reduce(xs, "sum")
             outs = [torch.zeros(n, dtype=dtype, device="cuda") for _ in range(p)]
@@ -87,7 +87,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
 def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
-    for it, n in enumerate([1, 2, 5, 64, 1023, 16384]):
+    for it, n in enumerate([1, 2, 5, 64, 1023, 65536]):
         for dtype in (torch.float32, torch.uint8 if n % 4 == 0 else torch.int16):
             ss = [rand(n, torch.float32, 100 + r + it).to(dtype) for r in range(p)]
             outs = [torch.zeros(n * p, dtype=dtype, device="cuda") for _ in range(p)]
@@ -117,7 +117,7 @@ def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     torch.testing.assert_close(xs[0], st.mean(0))
     torch.testing.assert_close(ys[p - 1], st.sum(0) * 0.25)
     # a message that does not fit is refused when the path is forced, and staged when it is not
-    big = [rand(20000, torch.float32, 1) for _ in range(p)]
+    big = [rand(70000, torch.float32, 1) for _ in range(p)]
     with pytest.raises(al.AlError):
         comm.allreduce(big, algo="ll")
     before = comm.stats()["ll"]
@@ -364,3 +364,35 @@ def test_p2p_ring_of_slots_and_rendezvous_into_registered_buffers(al, p):
         if registered:
             comm.unregister(dst)
     comm.close()
+
+
+def test_guard_regions_catch_a_write_past_the_end(al):
+    """Guard mode: 4 KiB of a known pattern before and after every symmetric buffer.  Library operations leave them
+    intact; a stray 4-byte store just behind a buffer (made here with the library's fill kernel, inside the block's
+    own allocation) is reported by check_guards() with its position."""
+    import ctypes as C
+    from aluminum_b200 import _lib
+    al.set_tuning("debug_guard", 1)
+    try:
+        p = 4
+        comm = al.DeviceComm(emulate=p)
+        comm.set_timeout_ms(2000)
+        n = 100 * p
+        ts = comm.symm_empty((n,), torch.float32)
+        for r in range(p):
+            ts[r].fill_(float(r))
+        comm.allreduce(ts)
+        outs = comm.symm_empty((n * p,), torch.float32)
+        comm.allgather(ts, outs, algo="window")
+        comm.reduce_scatter(outs, [t[:n] for t in ts], algo="window")
+        torch.cuda.synchronize()
+        comm.check_guards()                                   # nothing wrote outside
+        comm.symm_free(outs)                                  # (checks again)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert _lib.load().al_fill_u32(C.c_void_p(ts[2].data_ptr() + n * 4), 1, 0xDEADBEEF, stream) == 0
+        torch.cuda.synchronize()
+        with pytest.raises(al.AlError, match="after the buffer"):
+            comm.check_guards()
+        comm.close()
+    finally:
+        al.set_tuning("debug_guard", 0)

@@ -30,7 +30,7 @@ OPS = {"sum": 0, "prod": 1, "min": 2, "max": 3, "lor": 4, "land": 5, "lxor": 6, 
 KINDS = {"allreduce": 0, "reduce": 1, "reduce_scatter": 2, "allgather": 3, "alltoall": 4, "bcast": 5, "gather": 6,
          "scatter": 7, "barrier": 8}
 ALGOS = {"auto": 0, "one_shot": 1, "two_shot": 2, "nvls": 3, "ll": 4}
-PATHS = {"auto": 0, "staged": 1, "window": 2, "ll": 3}  # data path of every collective but allreduce
+PATHS = {"auto": 0, "staged": 1, "window": 2, "ll": 3, "nvls": 4}  # data path of every collective but allreduce
 COMM_STREAM = C.c_void_p(-1 & (2 ** 64 - 1))
 
 

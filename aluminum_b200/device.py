@@ -83,10 +83,10 @@ class DeviceComm:
         check(self._lib.al_dev_comm_abort(self._h, why.encode()))
 
     def stats(self) -> dict:
-        out = (C.c_uint64 * 12)()
+        out = (C.c_uint64 * 16)()
         check(self._lib.al_dev_comm_stats(self._h, out))
         names = ["ops", "bytes", "kernels", "timeouts", "one_shot", "two_shot", "nvls", "nvls_zero_copy", "bulk_pipeline",
-                 "window", "ll", "rows"]
+                 "window", "ll", "rows", "rs_nvls"]
         return dict(zip(names, [int(v) for v in out]))
 
     def status(self) -> dict:

@@ -1,7 +1,10 @@
 """Small single-GPU cases of the library's kernels, sized for profiler captures
 (inputs larger than the 126 MB L2, a few GB on the device at most, a handful of launches).
 
-    python benchmark/profile_kernels.py --case sgd|cast|allreduce|alltoall|halo [--iters 3]
+    python benchmark/profile_kernels.py --case sgd|cast|allreduce|alltoall|halo|ll|window_ag|window_rs|rows|p2p|rs_pipelined [--iters 3]
+
+The multi-rank cases run all ranks of an emulated communicator in one launch on one GPU: "remote" traffic
+lands in local HBM, so the figures show the kernels' memory behaviour, not NVLink.
 
 Prints the CUDA-event time of the case and the achieved fraction of the measured copy bandwidth.
 """
@@ -54,6 +57,56 @@ def main():
         else:
             fn = lambda: comm.alltoall(xs, outs)
             nbytes = pr * n * 4 * 4
+    elif a.case == "ll":
+        pr = 8
+        comm = al.DeviceComm(emulate=pr)
+        n = 16 << 10  # 64 KiB per rank: the packet path's upper range
+        xs = [torch.randn(n, device="cuda") for _ in range(pr)]
+        outs = [torch.empty(n, device="cuda") for _ in range(pr)]
+        fn = lambda: comm.allreduce(xs, outs, algo="ll")
+        nbytes = pr * n * 4 * (1 + 2 * (pr - 1) * 2 + 1)  # read in; packets written and read at 2x payload; write out
+    elif a.case in ("window_ag", "window_rs"):
+        pr = 8
+        comm = al.DeviceComm(emulate=pr)
+        n = 4 << 20  # 16 MiB per rank slice, 128 MiB per rank buffer
+        full = [torch.randn(n * pr, device="cuda") for _ in range(pr)]
+        assert comm.register(full) >= 0
+        part = [torch.randn(n, device="cuda") for _ in range(pr)]
+        if a.case == "window_ag":
+            fn = lambda: comm.allgather(part, full, algo="window")
+            nbytes = pr * n * 4 * (1 + pr)          # read own slice, write it into p buffers
+        else:
+            fn = lambda: comm.reduce_scatter(full, part, algo="window")
+            nbytes = pr * n * 4 * (pr + 1)          # read p slices, write one
+    elif a.case == "rows":
+        pr = 8
+        comm = al.DeviceComm(emulate=pr)
+        from aluminum_b200.parallel import ulysses
+        s_, h_, d_ = 2048, 32, 128                  # per rank: 2048 x 32 x 128 bf16 = 16 MiB
+        shards = [torch.randn(s_, h_, d_, device="cuda", dtype=torch.bfloat16) for _ in range(pr)]
+        fn = lambda: ulysses.seq_to_head(comm, shards)
+        nbytes = pr * s_ * h_ * d_ * 2 * 4          # read, write slot, read slot, write
+    elif a.case == "p2p":
+        pr = 2
+        comm = al.DeviceComm(emulate=pr)
+        n = 32 << 20                                # 128 MiB each way
+        src = [torch.randn(n, device="cuda") for _ in range(pr)]
+        dst = [torch.empty(n, device="cuda") for _ in range(pr)]
+        assert comm.register(dst) >= 0
+        items = []
+        for r in range(pr):
+            items.append((True, (r + 1) % pr, src[r], r))
+            items.append((False, (r - 1) % pr, dst[r], r))
+        fn = lambda: comm.p2p(items)
+        nbytes = pr * n * 4 * 2                     # rendezvous into registered buffers: read once, write once
+    elif a.case == "rs_pipelined":
+        pr = 8
+        comm = al.DeviceComm(emulate=pr)
+        n = 8 << 20                                 # 32 MiB per rank slice, 256 MiB per rank: publisher / consumer CTAs
+        full = [torch.randn(n * pr, device="cuda") for _ in range(pr)]
+        part = [torch.empty(n, device="cuda") for _ in range(pr)]
+        fn = lambda: comm.reduce_scatter(full, part)
+        nbytes = pr * n * 4 * (pr + pr + pr + 1)    # read p slices, write p slots, read p slots, write one
     elif a.case == "halo":
         pr = 4
         comm = al.DeviceComm(emulate=pr)

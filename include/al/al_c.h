@@ -94,7 +94,7 @@ const char* al_dev_comm_backing(void* comm);
 int al_dev_comm_set_timeout_ms(void* comm, double ms);
 /** Every later call on the communicator fails (why may be NULL). */
 int al_dev_comm_abort(void* comm, const char* why);
-/** Fills out[0..11]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, window, ll, rows. */
+/** Fills out[0..12]: ops, bytes, kernels, timeouts, one_shot, two_shot, nvls, nvls_zero_copy, bulk_pipeline, window, ll, rows, rs_nvls. */
 int al_dev_comm_stats(void* comm, uint64_t* out);
 /** Status record: out[0]=code, [1]=rank, [2]=peer, [3]=where, [4]=epoch, [5]=seen. Never fails. */
 int al_dev_comm_status(void* comm, uint64_t* out);

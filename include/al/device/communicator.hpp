@@ -42,10 +42,14 @@ enum class AllreduceAlgo : int { automatic = 0, one_shot, two_shot, nvls, ll };
  *              (RegisterMemory or symm_alloc); an error if this rank's buffer is not registered.
  *   ll         small reduce_scatter / allgather / alltoall as low-latency packets (kernels/ll.cu);
  *              an error if the message does not fit (kLLPayloadBytes from one rank to another).
+ *   nvls       reduce_scatter of private buffers reduced by the switch: copy into the multicast-bound staging,
+ *              multimem.ld_reduce of the own slice straight into the receive buffer (kernels/nvls.cu); an error
+ *              without multicast, on two ranks, or for types / operators the switch does not reduce.
  * `automatic` takes packets up to tuning().ll_max_bytes, the window path for registered buffers from
- * tuning().window_min_bytes on, staging otherwise.  AllreduceAlgo::ll is the same for allreduce.
+ * tuning().window_min_bytes on, the switch for large reduce_scatters (rs_nvls_min_bytes), staging otherwise.
+ * AllreduceAlgo::ll is the same for allreduce.
  */
-enum class CollPath : int { automatic = 0, staged, window, ll };
+enum class CollPath : int { automatic = 0, staged, window, ll, nvls };
 
 /** Arguments of one collective for one local rank. */
 struct RankArgs {
@@ -91,6 +95,7 @@ struct CommStats {
   uint64_t ar_one_shot = 0, ar_two_shot = 0, ar_nvls = 0, ar_nvls_zero_copy = 0;
   uint64_t bulk_pipeline = 0;   ///< operations run by the bulk-copy pipeline kernel
   uint64_t window = 0;          ///< operations that ran straight on registered buffers (window kernels)
+  uint64_t rs_nvls = 0;         ///< reduce_scatters of private buffers that the switch reduced (staged NVLS)
   uint64_t ll = 0;              ///< operations that ran as low-latency packets
   uint64_t rows = 0;            ///< row exchanges (alltoall with fused pack / unpack)
 };

@@ -82,6 +82,10 @@ struct NvlsParams {
 bool nvls_allreduce_supported(DType dt, ReductionOperator op);
 void launch_nvls_allreduce(const NvlsParams& P, DType dt, ReductionOperator op, int ctas, int threads,
                            cudaStream_t stream);
+/** Staged NVLS reduce_scatter of private buffers (same types / operators): `count` = elements per slice,
+ *  `chunk_elems` = elements of a slice per chunk (at most a p-th of a staging half), `chunks` accordingly. */
+void launch_nvls_reduce_scatter(const NvlsParams& P, DType dt, ReductionOperator op, int ctas, int threads,
+                                cudaStream_t stream);
 
 // ---- point-to-point mailbox transfers (kernels/p2p.cu) ----------------------------
 void launch_p2p(const P2PParams& P, int threads, int local_ranks_cooperative, cudaStream_t stream);

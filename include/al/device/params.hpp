@@ -117,16 +117,24 @@ struct DeviceStatus {
  * between the data and a flag (the role of NCCL's LL protocol, which the reference gets from ncclAllReduce
  * & co. at these sizes).  One slot per (parity of the operation number, source rank).
  */
-constexpr size_t kLLPayloadBytes = 262144;
+constexpr size_t kLLPayloadBytes = 1048576;
 constexpr size_t kLLSlotBytes = 2 * kLLPayloadBytes;
 constexpr size_t kLLAreaBytes = 2 * (size_t)kMaxRanks * kLLSlotBytes;
+/**
+ * Point-to-point messages of up to kP2PLLPayloadBytes travel as the same kind of packets: a ring of packet
+ * slots per ordered pair of ranks, [source][piece number % mbox_slots], placed behind the collectives'
+ * packet area (at ll[r] + kLLAreaBytes).  The packets' epoch is the pair's piece number + 1.
+ */
+constexpr size_t kP2PLLPayloadBytes = 262144;
+constexpr size_t kP2PLLSlotBytes = 2 * kP2PLLPayloadBytes;
 
 /** Workspace of one communicator as seen from the launching process. */
 struct Workspace {
   char* stage[kMaxRanks];        ///< staging base (two halves, contiguous) of every rank
   uint64_t* flags[kMaxRanks];    ///< flag area of every rank
   char* mbox[kMaxRanks];         ///< p2p mailbox area of every rank: [src][2 slots]
-  char* ll[kMaxRanks];           ///< low-latency packet area of every rank: [parity][src][kLLSlotBytes]
+  char* ll[kMaxRanks];           ///< low-latency packet area of every rank: [parity][src][kLLSlotBytes], then the
+                                 ///< point-to-point packet slots [src][mbox_slots][kP2PLLSlotBytes]
   char* mc_stage;                ///< NVLink-multicast alias of the staging area, or nullptr
   DeviceStatus* status;          ///< pinned host record (device-visible address)
   uint64_t* stamps;              ///< nullptr, or 4 words of this GPU's memory that the small-message kernels fill with
@@ -262,6 +270,7 @@ struct P2PParams {
   uint64_t rdesc[kMaxItems];     ///< receives: descriptor of the receive buffer when it is registered, else 0
   const WindowTable* windows;    ///< device memory of the launching process
   size_t rendezvous_bytes;       ///< messages of at least this size wait for the receiver and go straight into a registered buffer
+  size_t ll_bytes;               ///< messages of at most this size (> 0) travel as packets (at most kP2PLLPayloadBytes)
   uint64_t launch;               ///< number of this launch on the communicator (tags the local "posted" words)
   int ctas_per_item;
   int nitems;

@@ -26,13 +26,14 @@ namespace Al {
  * rows, "ll_max_bytes@4" one.
  */
 struct Crossovers {
-  size_t ll_max_bytes;             ///< AL_LL_MAX: at most this many bytes per pair of ranks travel as low-latency packets (hard limit 256 KiB; 0 = never)
+  size_t ll_max_bytes;             ///< AL_LL_MAX: at most this many bytes per pair of ranks travel as low-latency packets (hard limit 1 MiB; 0 = never)
   size_t ar_oneshot_max_bytes;     ///< AL_AR_ONESHOT_MAX: staged one-shot allreduce up to this size
   size_t ar_nvls_min_bytes;        ///< AL_AR_NVLS_MIN: NVLS allreduce from this size on
   size_t ar_pipeline_min_bytes;    ///< AL_AR_PIPELINE_MIN: two ranks: the one-shot allreduce splits its grid into pushing and reducing CTAs from this size on
   size_t nvls_pipeline_min_bytes;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is software-pipelined from this size on
   size_t pipeline_min_bytes;       ///< AL_PIPELINE_MIN: per-rank slice from which staged reduce_scatter / allgather / alltoall split the grid into publishers and consumers
   size_t window_min_bytes;         ///< AL_WINDOW_MIN: total message size from which registered buffers take the window kernels (below: staging or packets, one flag round less)
+  size_t rs_nvls_min_bytes;        ///< AL_RS_NVLS_MIN: total message size from which reduce_scatter of private buffers reduces in the switch (staged NVLS; needs multicast and more than two ranks)
 };
 
 struct Tuning {
@@ -56,6 +57,7 @@ struct Tuning {
   size_t dev_stage_bytes = size_t{64} << 20;   ///< AL_DEV_STAGE_BYTES: one staging half per rank per communicator
   size_t dev_mailbox_bytes = size_t{8} << 20;  ///< AL_DEV_MAILBOX_BYTES: size of one p2p mailbox slot (larger pieces amortise the per-piece flag round: 4 MiB moved 315 GB/s, 16 MiB 536 GB/s between two B200)
   int dev_mailbox_slots = 2;                   ///< AL_DEV_MAILBOX_SLOTS: slots of the ring every ordered pair of ranks owns (pieces in flight per transfer)
+  size_t p2p_ll_max_bytes = size_t{256} << 10;     ///< AL_P2P_LL_MAX: point-to-point messages up to this size travel as low-latency packets (data and piece number in one 16-byte store; hard limit 256 KiB; 0 = never)
   size_t p2p_rendezvous_bytes = size_t{1} << 20;  ///< AL_P2P_RENDEZVOUS: from this size on a send first waits for the receiver and, if the receive buffer is registered, stores straight into it (0 = never)
   double dev_wait_timeout_ms = 20000.0;        ///< AL_DEV_WAIT_TIMEOUT_MS: bound of every device-side flag wait
   bool dev_enable_nvls = true;                 ///< AL_DEV_NVLS: bind staging to an NVLink multicast object when supported
@@ -69,10 +71,10 @@ struct Tuning {
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
   int ll_max_ctas = 64;                        ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
   Crossovers cross[3] = {
-      // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min
-      {size_t{256} << 10, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10},   // 2 ranks
-      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10}, // 3-4 ranks
-      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10},  // 5-8 ranks
+      // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min  rs nvls min
+      {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, ~size_t{0}},             // 2 ranks
+      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{128} << 20}, // 3-4 ranks
+      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{128} << 20},  // 5-8 ranks
   };
   /** Row of the table for a communicator of `p` ranks. */
   const Crossovers& crossovers(int p) const { return cross[p <= 2 ? 0 : (p <= 4 ? 1 : 2)]; }

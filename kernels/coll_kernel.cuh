@@ -11,7 +11,10 @@
 // the user's receive buffer with local loads.  One template serves all nine
 // collectives; Ti/Tw/To are the user-input, wire (staging) and user-output
 // element types and Red the reduction functor.  Pure data-movement collectives
-// instantiate it once with byte elements.
+// instantiate it once with byte elements.  FAM says which operations an
+// instantiation serves, so that the reducing instantiations (one per element
+// type and operator) do not carry the code and registers of the data-movement
+// operations and the byte instantiation none of the reductions.
 #pragma once
 #include "datamove.cuh"
 
@@ -19,8 +22,19 @@ namespace Al {
 namespace internal {
 namespace device {
 
-template <typename Ti, typename Tw, typename To, typename Red>
+constexpr int kFamAll = 0;     // every operation (mixed element types)
+constexpr int kFamReduce = 1;  // allreduce, reduce, reduce_scatter (+ barrier)
+constexpr int kFamMove = 2;    // allgather, alltoall, bcast, gather, scatter (+ barrier)
+
+/** Whether an instantiation of family `fam` serves operation `kind`. */
+inline bool family_serves(int fam, DevColl kind) {
+  const bool reduces = kind == DevColl::allreduce || kind == DevColl::reduce || kind == DevColl::reduce_scatter;
+  return fam == kFamAll || kind == DevColl::barrier || (fam == kFamReduce) == reduces;
+}
+
+template <typename Ti, typename Tw, typename To, typename Red, int FAM = kFamAll>
 __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollParams P, Red red) {
+  constexpr bool kReduces = FAM != kFamMove, kMoves = FAM != kFamReduce;
   const Workspace& ws = P.ws;
   const int p = ws.p;
   const int rank = P.rank0 + (int)blockIdx.y;
@@ -60,7 +74,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
     for (int r = 0; r < kMaxRanks; ++r) all_stage[r] = r < p ? ws.stage[r] + (size_t)par * half : nullptr;
     size_t lo, hi;
     switch (kind) {
-      case DevColl::allreduce: {
+      case DevColl::allreduce: if constexpr (kReduces) {
         if (!P.two_phase) {  // every rank gets every rank's whole chunk
           const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
           split_range(len, part, nparts, VEC, lo, hi);
@@ -90,23 +104,23 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           }
         }
         break;
-      }
-      case DevColl::reduce: {
+      } break;
+      case DevColl::reduce: if constexpr (kReduces) {
         const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
         split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo)
           cta_publish<Ti, Tw>(&all_stage[root], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
-      }
-      case DevColl::bcast: {
+      } break;
+      case DevColl::bcast: if constexpr (kMoves) {
         if (rank != root) break;
         const size_t base = c * full_e, len = clamp_len(P.count, base, full_e);
         split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo) cta_publish<Ti, Tw>(all_stage, p, lo * sizeof(Tw), send + base + lo, hi - lo);
         break;
-      }
+      } break;
       case DevColl::allgather:
-      case DevColl::gather: {
+      case DevColl::gather: if constexpr (kMoves) {
         const size_t base = c * cap_e, len = clamp_len(T.send_counts[rank], base, cap_e);
         split_range(len, part, nparts, VEC, lo, hi);
         if (send && hi > lo) {
@@ -116,10 +130,12 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
             cta_publish<Ti, Tw>(&all_stage[root], 1, (size_t)rank * cap_b + lo * sizeof(Tw), send + base + lo, hi - lo);
         }
         break;
-      }
+      } break;
       case DevColl::reduce_scatter:
       case DevColl::alltoall:
       case DevColl::scatter: {
+        if constexpr (!kMoves) { if (kind != DevColl::reduce_scatter) break; }
+        if constexpr (!kReduces) { if (kind == DevColl::reduce_scatter) break; }
         if (kind == DevColl::scatter && rank != root) break;
         const bool sc = kind == DevColl::scatter;
         const size_t unit = sc ? full_e : cap_e, base = c * unit;
@@ -167,7 +183,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
     size_t lo, hi;
     switch (kind) {
       case DevColl::allreduce:
-      case DevColl::reduce: {
+      case DevColl::reduce: if constexpr (kReduces) {
         if (kind == DevColl::reduce && rank != root) break;
         const size_t base = c * cap_e, len = clamp_len(P.count, base, cap_e);
         split_range(len, part, nparts, VEC, lo, hi);
@@ -179,8 +195,8 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
         }
         break;
-      }
-      case DevColl::reduce_scatter: {
+      } break;
+      case DevColl::reduce_scatter: if constexpr (kReduces) {
         const size_t base = c * cap_e, len = clamp_len(T.recv_counts[rank], base, cap_e);
         split_range(len, part, nparts, VEC, lo, hi);
         if (recv && hi > lo) {
@@ -188,10 +204,10 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           cta_reduce<Tw, To, Red>(&out, 1, slot, lo * sizeof(Tw), p, hi - lo, red, P.scale, P.int_div);
         }
         break;
-      }
+      } break;
       case DevColl::allgather:
       case DevColl::gather:
-      case DevColl::alltoall: {
+      case DevColl::alltoall: if constexpr (kMoves) {
         if (kind == DevColl::gather && rank != root) break;
         const size_t base = c * cap_e;
         if constexpr (std::is_same<Tw, To>::value) {
@@ -218,9 +234,9 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
           }
         }
         break;
-      }
+      } break;
       case DevColl::bcast:
-      case DevColl::scatter: {
+      case DevColl::scatter: if constexpr (kMoves) {
         if (kind == DevColl::bcast && rank == root) break;
         const size_t cnt = kind == DevColl::bcast ? P.count : T.recv_counts[rank];
         const size_t base = c * full_e, len = clamp_len(cnt, base, full_e);
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
             cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(Tw), (hi - lo) * sizeof(Tw), true);
         }
         break;
-      }
+      } break;
       case DevColl::barrier: break;
     }
   };
@@ -287,10 +303,11 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
       __syncthreads();
       G = s_chunks;
     }
-    if (!(kind == DevColl::allreduce && P.two_phase)) {
+    if (!kReduces || !(kind == DevColl::allreduce && P.two_phase)) {
       consume(c, cta, nct);
       continue;
     }
+    if constexpr (kReduces) {
     // ---- two-phase allreduce ---------------------------------------------------
     const int par = (int)((P.seq + c) & 1);
     char* mystage = ws.stage[rank] + (size_t)par * half;
@@ -323,6 +340,7 @@ __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollP
         }
       }
     }
+    }  // kReduces
   }
 
   stamp(ws, 3);

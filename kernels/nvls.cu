@@ -19,6 +19,7 @@
 #include "al/device/kernels.hpp"
 #include "datamove.cuh"
 #include "multimem.cuh"
+#include "packets.cuh"
 
 namespace Al {
 namespace internal {
@@ -193,6 +194,86 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
   (void)wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, G), P.timeout_ns);
 }
 
+/**
+ * Staged NVLS reduce_scatter for large private buffers: the switch reduces, two groups of CTAs pipeline.
+ *   IN   copies chunk c of all p slices of the user's input into the multicast-bound staging half,
+ *        slice d at slot d (HBM traffic only), and posts A(c) to everyone;
+ *   RED  waits for everyone's A(c), pulls this rank's slot through multimem.ld_reduce - one reduced stream
+ *        arrives instead of p-1 pushed ones, and nothing is read back from staging - applies the scale,
+ *        writes the user's output and posts C(c) to everyone.
+ * A staging half is reused every second chunk: IN waits for everyone's C(c-2) first, because every rank's RED
+ * group reads every rank's staging.  `count` is the length of one slice, `chunk_elems` the part of a slice
+ * that travels per chunk.  (Role of ncclReduceScatter's NVLS kernels behind the reference,
+ * include/aluminum/nccl_impl.hpp:1306.)
+ */
+template <typename T, NvOp OP>
+__global__ void __launch_bounds__(512) nvls_reduce_scatter_kernel(const __grid_constant__ NvlsParams P) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const Workspace& ws = P.ws;
+  const int p = ws.p, rank = P.rank;
+  if (poisoned(ws, rank)) return;
+  const float scale = (float)P.scale;
+  const size_t half = ws.half_bytes;
+  const size_t cap_b = (half / (size_t)p) / 256 * 256;  // one slot per slice
+  const size_t chunk_e = P.chunk_elems;
+  const uint64_t G = P.chunks;
+  const T* send = (const T*)P.send;
+  T* recv = (T*)P.recv;
+  const unsigned n = gridDim.x, b = blockIdx.x;
+  const unsigned n_red = n / 2 < 1 ? 1 : n / 2, n_in = n - n_red;
+  const uint64_t my_proto = proto_word(kProtoNvlsStaged, (int)DevColl::reduce_scatter, 1);
+  // Ranks that took the window path wait for this flag before they touch anything: tell them what runs here.
+  if (b == 0) post_entered(ws, rank, P.seq, my_proto, 0, 0);
+
+  if (b < n_in) {
+    for (uint64_t c = 0; c < G; ++c) {
+      if (c >= 2 && !wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, c - 1), P.timeout_ns)) return;
+      char* mystage = ws.stage[rank] + (size_t)((P.seq + c) & 1) * half;
+      const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
+      size_t lo, hi;
+      split_range(len, b, n_in, (size_t)VEC, lo, hi);
+      if (hi > lo)
+        for (int i = 0; i < p; ++i) {
+          const int d = (rank + i) % p;
+          cta_copy(mystage + (size_t)d * cap_b + lo * sizeof(T), (const char*)(send + (size_t)d * P.count + base + lo),
+                   (hi - lo) * sizeof(T), false);
+        }
+      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
+    }
+  } else {
+    const unsigned part = b - n_in;
+    for (uint64_t c = 0; c < G; ++c) {
+      if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
+      const char* mc = ws.mc_stage + (size_t)((P.seq + c) & 1) * half + (size_t)rank * cap_b;
+      const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
+      const size_t nvec = (len + VEC - 1) / VEC;  // the tail vector reads stale staging bytes; store_group drops them
+      T* out = recv + base;
+      constexpr int U = 4;
+      const size_t stride = (size_t)blockDim.x * n_red;
+      size_t v = (size_t)part * blockDim.x + threadIdx.x;
+      for (; v + (U - 1) * stride < nvec; v += U * stride) {
+        uint4 a[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) a[u] = MM<T, OP>::ld(mc + ((v + u * stride) << 4));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (scale != 1.f) a[u] = scale_pack<T>(a[u], scale);
+          store_group(out, (v + u * stride) * VEC, len, a[u]);
+        }
+      }
+      for (; v < nvec; v += stride) {
+        uint4 a = MM<T, OP>::ld(mc + (v << 4));
+        if (scale != 1.f) a = scale_pack<T>(a, scale);
+        store_group(out, v * VEC, len, a);
+      }
+      arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_red, make_epoch(P.seq, c + 1), false, 0, 0);
+    }
+  }
+  // Closing barrier: every rank has pulled its last chunk, both halves are free for the next launch.
+  (void)wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, G), P.timeout_ns);
+}
+
 template <typename T, NvOp OP>
 void launch(const NvlsParams& P, int ctas, int threads, cudaStream_t s) {
   if (P.chunk_elems && !P.mc_in && ctas >= 8) {
@@ -227,6 +308,28 @@ void launch_nvls_allreduce(const NvlsParams& P, DType dt, ReductionOperator op, 
   if (add) return launch<__half, NvOp::add>(P, ctas, threads, s);
   if (op == ReductionOperator::min) return launch<__half, NvOp::min>(P, ctas, threads, s);
   return launch<__half, NvOp::max>(P, ctas, threads, s);
+}
+
+template <typename T, NvOp OP>
+static void launch_rs(const NvlsParams& P, int ctas, int threads, cudaStream_t s) {
+  nvls_reduce_scatter_kernel<T, OP><<<ctas, threads, 0, s>>>(P);
+  AL_CHECK_CUDA(cudaGetLastError());
+}
+
+void launch_nvls_reduce_scatter(const NvlsParams& P, DType dt, ReductionOperator op, int ctas, int threads,
+                                cudaStream_t s) {
+  if (!nvls_allreduce_supported(dt, op)) throw_al_exception("NVLS reduce_scatter does not support this type/operator");
+  if (ctas < 2) ctas = 2;
+  const bool add = op == ReductionOperator::sum || op == ReductionOperator::avg;
+  if (dt == DType::f32) return launch_rs<float, NvOp::add>(P, ctas, threads, s);
+  if (dt == DType::bf16) {
+    if (add) return launch_rs<__nv_bfloat16, NvOp::add>(P, ctas, threads, s);
+    if (op == ReductionOperator::min) return launch_rs<__nv_bfloat16, NvOp::min>(P, ctas, threads, s);
+    return launch_rs<__nv_bfloat16, NvOp::max>(P, ctas, threads, s);
+  }
+  if (add) return launch_rs<__half, NvOp::add>(P, ctas, threads, s);
+  if (op == ReductionOperator::min) return launch_rs<__half, NvOp::min>(P, ctas, threads, s);
+  return launch_rs<__half, NvOp::max>(P, ctas, threads, s);
 }
 
 }  // namespace device

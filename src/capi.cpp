@@ -100,7 +100,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls)   \
   X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(debug_guard) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(window_enable) X(window_ctas) X(window_multimem) X(window_multimem_ag_ranks) X(window_rs_min_ranks)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(p2p_ll_max_bytes) X(window_enable) X(window_ctas) X(window_multimem) X(window_multimem_ag_ranks) X(window_rs_min_ranks)
 
 namespace {
 /** "ll_max_bytes" or "ll_max_bytes@4" -> member pointer and row (-1 = all rows); nullptr if not a crossover. */
@@ -120,6 +120,7 @@ size_t Crossovers::*crossover_field(const std::string& full, int* row) {
   if (n == "nvls_pipeline_min_bytes") return &Crossovers::nvls_pipeline_min_bytes;
   if (n == "pipeline_min_bytes") return &Crossovers::pipeline_min_bytes;
   if (n == "window_min_bytes") return &Crossovers::window_min_bytes;
+  if (n == "rs_nvls_min_bytes") return &Crossovers::rs_nvls_min_bytes;
   return nullptr;
 }
 }  // namespace
@@ -305,7 +306,7 @@ int al_dev_comm_stats(void* comm, uint64_t* out) {
     device::CommStats s = ((DeviceCommunicator*)comm)->stats();
     out[0] = s.ops; out[1] = s.bytes; out[2] = s.kernels; out[3] = s.timeouts;
     out[4] = s.ar_one_shot; out[5] = s.ar_two_shot; out[6] = s.ar_nvls; out[7] = s.ar_nvls_zero_copy;
-    out[8] = s.bulk_pipeline; out[9] = s.window; out[10] = s.ll; out[11] = s.rows;
+    out[8] = s.bulk_pipeline; out[9] = s.window; out[10] = s.ll; out[11] = s.rows; out[12] = s.rs_nvls;
   });
 }
 int al_dev_comm_status(void* comm, uint64_t* out) {

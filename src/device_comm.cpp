@@ -100,7 +100,8 @@ struct DeviceCommunicator::Impl {
   }
 
   static size_t block_bytes(int p, size_t half, size_t slot, int slots) {
-    return FlagLayout::bytes + 2 * half + (size_t)p * (size_t)slots * slot + kLLAreaBytes;
+    return FlagLayout::bytes + 2 * half + (size_t)p * (size_t)slots * slot + kLLAreaBytes +
+           (size_t)p * (size_t)slots * kP2PLLSlotBytes;
   }
 
   int free_window() const {
@@ -487,6 +488,46 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       throw_al_exception("the window path was requested but this rank's buffer is not registered (or the buffers overlap)");
   }
 
+  // Large reduce_scatters of private buffers let the switch reduce: copy into the multicast-bound staging,
+  // multimem.ld_reduce the own slice straight into the receive buffer.  Each GPU then receives one reduced
+  // stream instead of p-1 pushed ones and reads nothing back from staging.  Eligibility depends on facts all
+  // ranks share (and the kernels compare protocols anyway).
+  if (d.kind == DevColl::reduce_scatter && !use_window) {
+    const bool ok = !d.vector && !I.emulated && p > 2 && I.ws.mc_stage != nullptr && in == wire && wire == out &&
+                    P.count > 0 && nvls_allreduce_supported(wire, d.op);
+    if (d.path == CollPath::nvls && !ok)
+      throw_al_exception("NVLS reduce_scatter requested but unavailable (no multicast, two ranks, vector form, or type/operator unsupported)");
+    if (ok && (d.path == CollPath::nvls || (d.path == CollPath::automatic && P.count * esz * (size_t)p >= X.rs_nvls_min_bytes))) {
+      NvlsParams N{};
+      N.ws = I.ws;
+      N.send = ranks[0].send;
+      N.recv = ranks[0].recv;
+      N.count = P.count;
+      const size_t vec = 16 / esz;
+      const size_t slot_cap_e = (half / (size_t)p) / 256 * 256 / esz;               // elements of a slice a staging half holds
+      size_t chunk_e = std::max<size_t>(ceil_div(P.count, (size_t)8), (size_t{1} << 20) / esz);  // an eighth of the slice, 1 MiB at least
+      chunk_e = std::min(round_up(chunk_e, vec), slot_cap_e);
+      N.chunk_elems = chunk_e;
+      N.chunks = ceil_div(P.count, chunk_e);
+      if (N.chunks >= (1u << 24) - 2) throw_al_exception("message too large for the configured staging size");
+      N.seq = P.seq;
+      N.timeout_ns = P.timeout_ns;
+      N.scale = P.scale;
+      N.rank = I.rank0;
+      const size_t work = std::min(P.count, chunk_e) * esz * (size_t)p;
+      int nctas = (int)std::max<size_t>(2, std::min<size_t>((size_t)std::min(tn.max_ctas_nvls, 128), ceil_div(work, (size_t)65536)));
+      I.order_after_previous(stream);
+      I.stats.ops++;
+      I.stats.bytes += P.count * esz * (size_t)p;
+      I.stats.kernels++;
+      I.stats.rs_nvls++;
+      launch_nvls_reduce_scatter(N, wire, d.op, nctas, std::min(512, tn.threads_per_cta), stream);
+      return;
+    }
+  } else if (d.path == CollPath::nvls) {
+    throw_al_exception("the nvls path serves reduce_scatter (for allreduce use AllreduceAlgo::nvls)");
+  }
+
   // Large uniform reduce_scatter / allgather / alltoall run pipelined: smaller chunks, half of the
   // grid publishing while the other half consumes.
   // The one-shot allreduce of two ranks joins them: half of the grid pushes chunk c+1 to the peer while the
@@ -754,6 +795,7 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
     P.timeout_ns = I.timeout_ns;
     P.windows = I.table_dev;
     P.rendezvous_bytes = tuning().p2p_rendezvous_bytes ? tuning().p2p_rendezvous_bytes : ~size_t{0};
+    P.ll_bytes = std::min(tuning().p2p_ll_max_bytes, std::min(kP2PLLPayloadBytes, P.rendezvous_bytes - 1));
     P.launch = ++I.p2p_launches;
     size_t biggest_direct = 0;
     std::vector<uint64_t> used;  // keys taken in this launch

@@ -44,13 +44,14 @@ void Tuning::load_from_env() {
   ll_max_ctas = (int)env_long("AL_LL_CTAS", ll_max_ctas);
   dev_mailbox_slots = (int)env_long("AL_DEV_MAILBOX_SLOTS", dev_mailbox_slots);
   p2p_rendezvous_bytes = (size_t)env_long("AL_P2P_RENDEZVOUS", (long)p2p_rendezvous_bytes);
+  p2p_ll_max_bytes = (size_t)env_long("AL_P2P_LL_MAX", (long)p2p_ll_max_bytes);
   {
     struct Entry { const char* env; size_t Crossovers::*field; };
     static const Entry entries[] = {
         {"AL_LL_MAX", &Crossovers::ll_max_bytes}, {"AL_AR_ONESHOT_MAX", &Crossovers::ar_oneshot_max_bytes},
         {"AL_AR_NVLS_MIN", &Crossovers::ar_nvls_min_bytes}, {"AL_AR_PIPELINE_MIN", &Crossovers::ar_pipeline_min_bytes},
         {"AL_NVLS_PIPELINE_MIN", &Crossovers::nvls_pipeline_min_bytes}, {"AL_PIPELINE_MIN", &Crossovers::pipeline_min_bytes},
-        {"AL_WINDOW_MIN", &Crossovers::window_min_bytes}};
+        {"AL_WINDOW_MIN", &Crossovers::window_min_bytes}, {"AL_RS_NVLS_MIN", &Crossovers::rs_nvls_min_bytes}};
     static const char* suffix[3] = {"_P2", "_P4", "_P8"};
     for (const Entry& e : entries)
       for (int row = 0; row < 3; ++row) {
@@ -132,6 +133,7 @@ std::string Tuning::describe() const {
      << "ll_max_ctas = " << ll_max_ctas << "\n"
      << "dev_mailbox_slots = " << dev_mailbox_slots << "\n"
      << "p2p_rendezvous_bytes = " << p2p_rendezvous_bytes << "\n"
+     << "p2p_ll_max_bytes = " << p2p_ll_max_bytes << "\n"
      << "window_enable = " << window_enable << "\n"
      << "window_ctas = " << window_ctas << "\n"
      << "window_multimem = " << window_multimem << "\n"
@@ -145,6 +147,7 @@ std::string Tuning::describe() const {
      << "  nvls_pipeline_min_bytes " << cross[0].nvls_pipeline_min_bytes << "  " << cross[1].nvls_pipeline_min_bytes << "  " << cross[2].nvls_pipeline_min_bytes << "\n"
      << "  pipeline_min_bytes      " << cross[0].pipeline_min_bytes << "  " << cross[1].pipeline_min_bytes << "  " << cross[2].pipeline_min_bytes << "\n"
      << "  window_min_bytes        " << cross[0].window_min_bytes << "  " << cross[1].window_min_bytes << "  " << cross[2].window_min_bytes << "\n"
+     << "  rs_nvls_min_bytes       " << cross[0].rs_nvls_min_bytes << "  " << cross[1].rs_nvls_min_bytes << "  " << cross[2].rs_nvls_min_bytes << "\n"
      << "trace = " << trace << "\n"
      << "debug_checks = " << debug_checks << "\n"
      << "debug_guard = " << debug_guard << "\n"

@@ -20,7 +20,7 @@ def al():
         pytest.skip("no CUDA device")
     al.init()
     old = al.get_tuning("ll_max_bytes")
-    al.set_tuning("ll_max_bytes", 262144)  # the largest message the packet slots hold
+    al.set_tuning("ll_max_bytes", 1 << 20)  # the largest message the packet slots hold
     yield al
     al.set_tuning("ll_max_bytes", old)
 
@@ -47,7 +47,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(2000)
     esz = torch.empty((), dtype=dtype).element_size()
-    sizes = [1, 3, 4, 5, 33, 1000, 262144 // esz]
+    sizes = [1, 3, 4, 5, 33, 1000, 262144 // esz, (1 << 20) // esz]
     before = comm.stats()["ll"]
     calls = 0
     for it, n in enumerate(sizes):
@@ -66,7 +66,7 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
                 assert torch.equal(ys[r], outs[r][:n])                          # both forms, and every rank, bit-identical
             assert all(torch.equal(outs[0], o) for o in outs)
         # reduce_scatter: n elements per rank
-        if n * esz <= 262144:
+        if n * esz <= (1 << 20):
             xs = [rand(n * p, dtype, 50 + 10 * it + r) for r in range(p)]
             want = ref_reduce(xs, "sum")
             outs = [torch.zeros(n, dtype=dtype, device="cuda") for _ in range(p)]
@@ -117,7 +117,7 @@ def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     torch.testing.assert_close(xs[0], st.mean(0))
     torch.testing.assert_close(ys[p - 1], st.sum(0) * 0.25)
     # a message that does not fit is refused when the path is forced, and staged when it is not
-    big = [rand(70000, torch.float32, 1) for _ in range(p)]
+    big = [rand(270000, torch.float32, 1) for _ in range(p)]
     with pytest.raises(al.AlError):
         comm.allreduce(big, algo="ll")
     before = comm.stats()["ll"]
@@ -363,6 +363,37 @@ def test_p2p_ring_of_slots_and_rendezvous_into_registered_buffers(al, p):
                 assert torch.all(got[r] == float((r - 1) % p))
         if registered:
             comm.unregister(dst)
+    comm.close()
+
+
+@pytest.mark.parametrize("p", [2, 3])
+def test_p2p_small_messages_travel_as_packets(al, p):
+    """Messages up to p2p_ll_max_bytes use the packet slots: odd sizes, unaligned buffers, more messages in a
+    row than the ring has slots, mixed with mailbox-sized messages between the same pair of ranks."""
+    comm = al.DeviceComm(emulate=p)
+    comm.set_timeout_ms(3000)
+    seq = [1, 7, 16, 100, 4099, 300_000, 65_539, 262_144, 5, 262_145, 33]     # bytes; 300 000 and 262 145 go through the mailbox
+    for it, nbytes in enumerate(seq):
+        src = [torch.randint(0, 256, (nbytes + 3,), dtype=torch.uint8, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7 * it + r)) for r in range(p)]
+        dst = [torch.full((nbytes + 5,), 0xEE, dtype=torch.uint8, device="cuda") for _ in range(p)]
+        items = []
+        for r in range(p):
+            items.append((True, (r + 1) % p, src[r][3:], r))                      # source starts 3 bytes into its allocation
+            items.append((False, (r - 1) % p, dst[r][1:1 + nbytes], r))           # destination 1 byte in
+        comm.p2p(items)
+        torch.cuda.synchronize()
+        assert comm.status()["code"] == 0, comm.status()
+        for r in range(p):
+            assert torch.equal(dst[r][1:1 + nbytes], src[(r - 1) % p][3:]), (nbytes, r)
+            assert dst[r][0] == 0xEE and torch.all(dst[r][1 + nbytes:] == 0xEE)
+    # one-directional stream of small sends, received later: the sender runs ahead by at most the ring's depth
+    if p == 2:
+        msgs = [torch.full((64,), float(i), device="cuda") for i in range(6)]
+        got = [torch.zeros(64, device="cuda") for _ in range(6)]
+        for i in range(6):
+            comm.p2p([(True, 1, msgs[i], 0), (False, 0, got[i], 1)])
+        torch.cuda.synchronize()
+        assert all(torch.equal(got[i], msgs[i]) for i in range(6))
     comm.close()
 
 

@@ -6,6 +6,8 @@
   ordinary torch tensors registered through CUDA IPC, at equal and at different offsets;
 * the zero-copy NVLS allreduce on a sub-range of a symmetric tensor whose length is not a multiple of 16 bytes
   (must not touch the elements behind it);
+* reduce_scatter of private buffers reduced by the switch (staged NVLS; more than two ranks): odd lengths,
+  several chunks, unaligned and in-place outputs, avg and max, against the locally computed expectation;
 * large messages: pipelined staged NVLS allreduce (private, 160 MiB), zero-copy allreduce (symmetric),
   pipelined reduce_scatter / allgather / alltoall (64 MiB per rank) - only with AL_TEST_LARGE=1;
 * a rank that passes a private buffer where the others pass a symmetric one: every rank must get a clear
@@ -138,6 +140,27 @@ if comm.has_multicast:
         assert torch.all(t[:count] == p * (p + 1) / 2), f"rank {me}: nvls allreduce of {count} wrong"
         assert torch.all(t[count:] == float(me + 1)), f"rank {me}: nvls allreduce of {count} touched the elements behind it"
         comm.symm_free(t)
+
+# ---- 2b. staged NVLS reduce_scatter of private buffers (the switch reduces) ----------------------------------
+if comm.has_multicast and p > 2:
+    before = comm.stats()["rs_nvls"]
+    calls = 0
+    for dt, ops in ((torch.float32, ("sum", "avg")), (torch.bfloat16, ("sum", "max"))):
+        for n in (5, 1000, 262_147, 3_000_001):
+            src = [data(r, n * p, 40 + n % 7, dt) for r in range(p)]
+            st = torch.stack([t.float() for t in src])
+            for op in ops:
+                want = {"sum": st.sum(0), "avg": st.mean(0), "max": st.max(0).values}[op][me * n:(me + 1) * n]
+                out = torch.full((n + 3,), -7.0, dtype=dt, device="cuda")
+                comm.reduce_scatter(src[me], out[1:1 + n], op=op, algo="nvls")       # output one element into its allocation
+                check(f"nvls reduce_scatter {dt} {op} {n}", out[1:1 + n].float(), want, exact=False)
+                assert out[0] == -7.0 and torch.all(out[1 + n:] == -7.0), "nvls reduce_scatter wrote outside its output"
+                calls += 1
+            buf = src[me].clone()
+            comm.reduce_scatter(buf, op="sum", algo="nvls")                            # in place: result at the start
+            check(f"nvls reduce_scatter in place {dt} {n}", buf[:n].float(), st.sum(0)[me * n:(me + 1) * n], exact=False)
+            calls += 1
+    assert comm.stats()["rs_nvls"] == before + calls, comm.stats()
 
 # ---- 3. large messages ----------------------------------------------------------------------------------------
 if LARGE:

@@ -39,8 +39,10 @@ static bool ring(Al::DeviceCommunicator& comm, size_t n) {
   auto got_r = from_right.download_on(comm.get_stream());
   got_l.resize(n); got_r.resize(n);
   const bool ok = check_vector(got_l, want_l, "ring from left", me) && check_vector(got_r, want_r, "ring from right", me);
-  Al::ext::Sync(right, comm);
-  if (left != right) Al::ext::Sync(left, comm);
+  // Both neighbours at once (all notifies, then all waits): one Sync per neighbour in ring order would make
+  // every rank wait for its right neighbour before it signals its left one - a cycle from four ranks on.
+  const int both[2] = {right, left};
+  Al::ext::Sync(both, left != right ? 2 : 1, comm);
   Al::ext::DetachRemoteBuffer(r_right, right, comm);
   Al::ext::DetachRemoteBuffer(r_left, left, comm);
   // The buffers are released on return: every importer must have closed its mapping first.

@@ -73,6 +73,7 @@ struct NvlsParams {
   char* mc_out;         ///< zero-copy flavour: multicast alias of the symmetric output
   size_t count;
   size_t chunk_elems;   ///< non-zero: pipelined staged flavour with chunks of this many elements
+  int ring_depth;       ///< pipelined allreduce: chunks in flight (slots of chunk_elems laid over both staging halves)
   uint64_t chunks;
   uint64_t seq;
   uint64_t timeout_ns;

@@ -53,9 +53,15 @@ struct FlagLayout {
   static constexpr size_t off_p2p_ready = off_p2p_arrive + 32 * stride;    // [kMaxRanks], written by the receiver into the SENDER's area:
                                                                             //   word 0 = number of the message's first piece + 1, word 1 = descriptor of its buffer
   static constexpr size_t off_p2p_posted = off_p2p_ready + kMaxRanks * stride;  // [16] plain words, local: last piece each item of the running launch posted
-  static constexpr size_t words = off_p2p_posted + 16;
+  static constexpr size_t off_ring_arrive = off_p2p_posted + 16;           // [3][kRingDepth] plain words, local: CTA arrival counters of the
+                                                                            //   ring-pipelined kernels, per CTA group and ring slot
+  static constexpr size_t words = off_ring_arrive + 3 * 8;
   static constexpr size_t bytes = (words * 8 + 4095) / 4096 * 4096;
 };
+
+/** Most chunks a ring-pipelined kernel keeps in flight in the staging area (FlagLayout::off_ring_arrive). */
+constexpr int kRingDepth = 8;
+static_assert(FlagLayout::bytes == 4096, "the flag area is one page (the allocation-free entry point's scratch layout depends on it)");
 
 /** Why a kernel gave up. */
 enum StatusCode : uint32_t {
@@ -224,6 +230,8 @@ struct LLParams {
   int kind;                      ///< DevColl: allreduce, reduce_scatter, allgather or alltoall
   int op;
   int rank0;
+  int two_phase;                 ///< allreduce only: reduce-scatter the vector in packets, then allgather the reduced slices in
+                                 ///< packets (second half of every slot); a slice then holds at most kLLPayloadBytes / 2
 };
 
 /**

@@ -138,16 +138,15 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* slot, uint64_t epoch, 
  * arrivals of at most two neighbouring rounds are ever in flight and a fast CTA's arrival
  * for round k+1 can never complete the count of round k.
  */
-__device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, size_t off, int counter_idx,
-                                                unsigned group, uint64_t epoch, bool with_meta, int meta_par,
-                                                uint64_t meta_value, uint64_t meta_proto = 0) {
+__device__ __forceinline__ void arrive_and_post_ctr(const Workspace& ws, int rank, size_t off, unsigned* ctr,
+                                                    unsigned group, uint64_t epoch, bool with_meta, int meta_par,
+                                                    uint64_t meta_value, uint64_t meta_proto = 0) {
   __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     int last = 1;
     if (group > 1) {
       __threadfence();  // this CTA's writes before the arrival count
-      unsigned* ctr = (unsigned*)flag_slot(ws.flags[rank], FlagLayout::off_arrive, counter_idx + 4 * (int)(epoch & 1));
       last = atomicInc(ctr, group - 1) == group - 1;
       if (last) __threadfence();  // other CTAs' writes before the flag stores
     }
@@ -163,6 +162,25 @@ __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, s
     }
     st_release_sys(flag_slot(ws.flags[dst], off, rank), epoch);
   }
+}
+
+__device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, size_t off, int counter_idx,
+                                                unsigned group, uint64_t epoch, bool with_meta, int meta_par,
+                                                uint64_t meta_value, uint64_t meta_proto = 0) {
+  unsigned* ctr = (unsigned*)flag_slot(ws.flags[rank], FlagLayout::off_arrive, counter_idx + 4 * (int)(epoch & 1));
+  arrive_and_post_ctr(ws, rank, off, ctr, group, epoch, with_meta, meta_par, meta_value, meta_proto);
+}
+
+/**
+ * The same for kernels that keep up to `depth` (<= kRingDepth) rounds in flight: one counter per CTA group
+ * (0..2) and ring slot.  Valid while no CTA can be `depth` rounds ahead of the slowest CTA of its group,
+ * which the ring-pipelined kernels guarantee by gating round c on the completion of round c - depth.
+ */
+__device__ __forceinline__ void arrive_and_post_ring(const Workspace& ws, int rank, size_t off, int group_id, uint64_t round,
+                                                     int depth, unsigned group, uint64_t epoch, bool with_meta, int meta_par,
+                                                     uint64_t meta_value, uint64_t meta_proto = 0) {
+  unsigned* ctr = (unsigned*)(ws.flags[rank] + FlagLayout::off_ring_arrive + (size_t)group_id * kRingDepth + (size_t)(round % (uint64_t)depth));
+  arrive_and_post_ctr(ws, rank, off, ctr, group, epoch, with_meta, meta_par, meta_value, meta_proto);
 }
 
 /** Every CTA waits until all ranks posted `epoch` in this rank's array `off`.

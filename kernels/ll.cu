@@ -50,6 +50,59 @@ __global__ void __launch_bounds__(256) ll_kernel(const __grid_constant__ LLParam
   char* my_slots = ws.ll[rank] + par_off;               // [source rank]
   const size_t to_me = par_off + (size_t)rank * kLLSlotBytes;  // my slot inside a peer's area
 
+  if (P.two_phase) {
+    // ---------------- two-phase allreduce ---------------------------------------------------------
+    // Slice r (groups [r*per, (r+1)*per)) is reduced by rank r.  Phase 1: every rank sends its groups of slice d
+    // to rank d (first half of the slot).  The owner folds the p contributions in rank order, keeps the result
+    // and sends it to every peer (phase 2, second half of the owner's slot in every peer's area), which
+    // copies it out.  Traffic per rank 2(p-1)/p of the vector instead of p-1 times the vector; a second
+    // NVLink trip, but still no flag round and no fence.  Group g is handled by the same thread in every
+    // loop, so an in-place call only overwrites elements its own thread has already sent.
+    const size_t per = (groups + (size_t)p - 1) / (size_t)p;
+    const size_t half_slot = kLLSlotBytes / 2;
+    for (size_t g = tid; g < groups; g += nthr) {
+      const int d = (int)(g / per);
+      if (d != rank) send_group(ws.ll[d] + to_me, g - (size_t)d * per, load_group(send, g * VEC, n), flag);
+    }
+    stamp(ws, 1);
+    const uint64_t epoch = make_epoch(P.seq, 1);
+    bool first = true;
+    const size_t mine_lo = (size_t)rank * per, mine_hi = mine_lo + per < groups ? mine_lo + per : groups;
+    for (size_t g = tid; g < groups; g += nthr) {
+      if (g < mine_lo || g >= mine_hi) continue;
+      A acc[VEC];
+      for (int r = 0; r < p; ++r) {
+        union { uint4 u; T e[VEC]; } x;
+        if (r == rank) x.u = load_group(send, g * VEC, n);
+        else if (!recv_group(my_slots + (size_t)r * kLLSlotBytes, g - mine_lo, flag, x.u, ws, rank, r, epoch, P.timeout_ns)) return;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const A a = Elem<T>::up(x.e[k]);
+          acc[k] = r == 0 ? a : red(acc[k], a);
+        }
+      }
+      if (first) { stamp(ws, 2); first = false; }
+      union { uint4 u; T e[VEC]; } o;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) o.e[k] = Elem<T>::down(finish_acc(acc[k], P.scale, P.int_div));
+      for (int i = 1; i < p; ++i) {
+        const int d = (rank + i) % p;
+        send_group(ws.ll[d] + to_me + half_slot, g - mine_lo, o.u, flag);
+      }
+      store_group(recv, g * VEC, n, o.u);
+    }
+    const uint64_t epoch2 = make_epoch(P.seq, 2);
+    for (size_t g = tid; g < groups; g += nthr) {
+      const int owner = (int)(g / per);
+      if (owner == rank) continue;
+      uint4 v;
+      if (!recv_group(my_slots + (size_t)owner * kLLSlotBytes + half_slot, g - (size_t)owner * per, flag, v, ws, rank, owner, epoch2, P.timeout_ns)) return;
+      store_group(recv, g * VEC, n, v);
+    }
+    stamp(ws, 3);
+    return;
+  }
+
   // ---------------- send ----------------------------------------------------------------------
   for (size_t g = tid; g < groups; g += nthr) {
     if (kind == DevColl::allreduce || kind == DevColl::allgather) {

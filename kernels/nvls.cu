@@ -124,7 +124,9 @@ __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_consta
  *   IN   copies chunk c of the user's input into the multicast-bound staging half (HBM),
  *   RED  switch-reduces this rank's slice of chunk c in place (NVLink),
  *   OUT  copies the finished chunk to the user's output (HBM),
- * so that the copies of neighbouring chunks hide behind the NVLink phase.  Flags:
+ * so that the copies of neighbouring chunks hide behind the NVLink phase.  The chunks travel through a
+ * ring of D slots laid over both staging halves (D = 2 * half / chunk, at most kRingDepth), so IN may run
+ * D-1 chunks ahead of OUT and a late copy never stalls the switch phase.  Flags:
  * A(c) "my copy-in of chunk c is done" (to everyone), B(c) "my slice of chunk c is
  * reduced and replicated" (to everyone), C(c) "I copied chunk c out" (to everyone;
  * IN only looks at its own, the closing wait looks at all).
@@ -135,8 +137,9 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
   const int p = ws.p, rank = P.rank;
   if (poisoned(ws, rank)) return;
   const float scale = (float)P.scale;
-  const size_t half = ws.half_bytes;
   const size_t chunk_e = P.chunk_elems;
+  const size_t chunk_b = chunk_e * sizeof(T);   // a multiple of 4096; ring slot c % D starts at (c % D) * chunk_b
+  const int D = P.ring_depth;                   // slots in the staging area (both halves, contiguous)
   const uint64_t G = P.chunks;
   const T* send = (const T*)P.send;
   T* recv = (T*)P.recv;
@@ -149,48 +152,48 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
 
   if (b < n_in) {
     for (uint64_t c = 0; c < G; ++c) {
-      if (c >= 2) {  // the half is free once my own OUT group copied chunk c-2 out
+      if (c >= (uint64_t)D) {  // the slot is free once my own OUT group copied chunk c-D out (which follows every rank's RED of it)
         __shared__ int s_ok;
         if (threadIdx.x == 0) {
           uint64_t seen = 0;
-          s_ok = wait_flag(flag_slot(ws.flags[rank], FlagLayout::off_C, rank), make_epoch(P.seq, c - 1), P.timeout_ns, &seen);
-          if (!s_ok) report_timeout(ws, rank, rank, 2, make_epoch(P.seq, c - 1), seen);
+          s_ok = wait_flag(flag_slot(ws.flags[rank], FlagLayout::off_C, rank), make_epoch(P.seq, c - D + 1), P.timeout_ns, &seen);
+          if (!s_ok) report_timeout(ws, rank, rank, 2, make_epoch(P.seq, c - D + 1), seen);
         }
         __syncthreads();
         if (!s_ok) return;
       }
-      char* mystage = ws.stage[rank] + (size_t)((P.seq + c) & 1) * half;
+      char* mystage = ws.stage[rank] + (size_t)(c % D) * chunk_b;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       size_t lo, hi;
       split_range(len, b, n_in, 16 / sizeof(T), lo, hi);
       if (hi > lo) cta_copy(mystage + lo * sizeof(T), (const char*)(send + base + lo), (hi - lo) * sizeof(T), false);
-      arrive_and_post(ws, rank, FlagLayout::off_A, 0, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
+      arrive_and_post_ring(ws, rank, FlagLayout::off_A, 0, c, D, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
     }
   } else if (b < n_in + n_red) {
     for (uint64_t c = 0; c < G; ++c) {
       if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
       if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
-      char* mc = ws.mc_stage + (size_t)((P.seq + c) & 1) * half;
+      char* mc = ws.mc_stage + (size_t)(c % D) * chunk_b;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       const size_t nvec = (len * sizeof(T) + 15) >> 4;
       size_t s_lo, s_hi;
       split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
       reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale, b - n_in, n_red);
       __threadfence_system();
-      arrive_and_post(ws, rank, FlagLayout::off_B, 1, n_red, make_epoch(P.seq, c + 1), false, 0, 0);
+      arrive_and_post_ring(ws, rank, FlagLayout::off_B, 1, c, D, n_red, make_epoch(P.seq, c + 1), false, 0, 0);
     }
   } else {
     for (uint64_t c = 0; c < G; ++c) {
       if (!wait_all(ws, rank, FlagLayout::off_B, 1, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
-      char* mystage = ws.stage[rank] + (size_t)((P.seq + c) & 1) * half;
+      char* mystage = ws.stage[rank] + (size_t)(c % D) * chunk_b;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       size_t lo, hi;
       split_range(len, b - n_in - n_red, n_out, 16 / sizeof(T), lo, hi);
       if (hi > lo) cta_copy((char*)(recv + base + lo), mystage + lo * sizeof(T), (hi - lo) * sizeof(T), true);
-      arrive_and_post(ws, rank, FlagLayout::off_C, 2, n_out, make_epoch(P.seq, c + 1), false, 0, 0);
+      arrive_and_post_ring(ws, rank, FlagLayout::off_C, 2, c, D, n_out, make_epoch(P.seq, c + 1), false, 0, 0);
     }
   }
-  // Closing barrier: every rank has copied its last chunk out; both halves are free for the next launch.
+  // Closing barrier: every rank has copied its last chunk out; the whole staging area is free for the next launch.
   (void)wait_all(ws, rank, FlagLayout::off_C, 2, make_epoch(P.seq, G), P.timeout_ns);
 }
 

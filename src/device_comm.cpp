@@ -318,16 +318,24 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
                          d.kind == DevColl::allgather || d.kind == DevColl::alltoall;
     const size_t esz_ll = dtype_size(wire);
     const size_t pair_bytes = d.count * unit * esz_ll;  // what one rank sends to another
-    const bool fits = ll_kind && !d.vector && p > 1 && in == wire && wire == out && d.count > 0 &&
-                      pair_bytes <= kLLPayloadBytes && ll_supported(d.kind, wire, d.op);
+    const bool eligible = ll_kind && !d.vector && p > 1 && in == wire && wire == out && d.count > 0 &&
+                          ll_supported(d.kind, wire, d.op);
+    const bool fits = eligible && pair_bytes <= kLLPayloadBytes;
+    // Allreduce beyond that: reduce-scatter and allgather in packets inside one kernel (two NVLink trips, 2(p-1)/p
+    // of the vector per rank instead of p-1 times the vector); a slice must fit half a slot.
+    const size_t slice_groups = ceil_div(ceil_div(pair_bytes, (size_t)16), (size_t)p);
+    const bool fits2 = eligible && d.kind == DevColl::allreduce && p > 2 && slice_groups * 32 <= kLLSlotBytes / 2;
     const bool forced = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::ll : d.path == CollPath::ll;
     const bool automatic = d.kind == DevColl::allreduce ? d.algo == AllreduceAlgo::automatic : d.path == CollPath::automatic;
-    if (forced && !fits)
+    if (forced && !fits && !fits2)
       throw_al_exception("the low-latency path was requested but the operation does not qualify (uniform allreduce / "
                          "reduce_scatter / allgather / alltoall of at most ", kLLPayloadBytes, " bytes per pair of ranks)");
     const Tuning& tn = tuning();
-    if (fits && (forced || (automatic && pair_bytes <= tn.crossovers(p).ll_max_bytes))) {
+    const bool one_phase = fits && (forced || (automatic && pair_bytes <= tn.crossovers(p).ll_max_bytes));
+    const bool two_phase = !one_phase && fits2 && (forced || (automatic && pair_bytes <= tn.crossovers(p).ar_ll2_max_bytes));
+    if (one_phase || two_phase) {
       LLParams L;
+      L.two_phase = two_phase ? 1 : 0;
       L.ws = I.ws;
       for (int lr = 0; lr < I.nlocal; ++lr) {
         L.send[I.rank0 + lr] = ranks[(size_t)lr].send;
@@ -620,12 +628,13 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     N.count = P.count;
     N.chunks = P.local_chunks[I.rank0];
     if (!zero_copy && bytes >= X.nvls_pipeline_min_bytes) {
-      // pipelined flavour: chunks of 1/8 of the message (at least 16 MiB, at most a staging half);
-      // smaller chunks are dominated by the per-chunk handshakes
-      size_t chunk_b = std::max<size_t>(bytes / 8, size_t{16} << 20);
+      // pipelined flavour: chunks of 1/16 of the message (at least 8 MiB, at most a staging half) in a ring of
+      // slots laid over both halves; smaller chunks are dominated by the per-chunk handshakes
+      size_t chunk_b = std::max<size_t>(bytes / 16, size_t{8} << 20);
       chunk_b = std::min(chunk_b / 4096 * 4096, half);
       N.chunk_elems = chunk_b / esz;
       N.chunks = ceil_div(P.count, N.chunk_elems);
+      N.ring_depth = (int)std::max<size_t>(2, std::min<size_t>((size_t)kRingDepth, 2 * half / chunk_b));
       ctas = std::max(8, std::min(tn.max_ctas_nvls, 128));
     }
     N.seq = P.seq;

@@ -83,6 +83,49 @@ def test_ll_allreduce_and_reduce_scatter(al, p, dtype):
     comm.close()
 
 
+@pytest.mark.parametrize("p", [3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_ll_two_phase_allreduce(al, p, dtype):
+    """Allreduce beyond the one-phase packet limit: reduce-scatter and allgather in packets inside one kernel.
+    Odd lengths, unaligned views, in place and out of place, every rank bit-identical."""
+    old1, old2 = al.get_tuning("ll_max_bytes"), al.get_tuning("ar_ll2_max_bytes")
+    al.set_tuning("ll_max_bytes", 64)            # everything above 64 bytes takes the two-phase form
+    al.set_tuning("ar_ll2_max_bytes", 4 << 20)
+    comm = al.DeviceComm(emulate=p)
+    comm.set_timeout_ms(3000)
+    try:
+        before = comm.stats()["ll"]
+        calls = 0
+        for it, n in enumerate((17, 100, 1000, 70_001, 300_000)):
+            for op in ("sum", "max"):
+                base = [rand(n + 3, dtype, 900 + 10 * it + r) for r in range(p)]
+                xs = [b[1:1 + n] for b in base]                                    # views one element into their allocations
+                want = ref_reduce(xs, op)
+                outs = [torch.zeros(n + 2, dtype=dtype, device="cuda") for _ in range(p)]
+                comm.allreduce(xs, [o[:n] for o in outs], op=op)
+                ys = [x.clone() for x in xs]
+                comm.allreduce(ys, op=op)                                          # in place
+                calls += 2
+                torch.cuda.synchronize()
+                assert comm.status()["code"] == 0, comm.status()
+                for r in range(p):
+                    torch.testing.assert_close(outs[r][:n].double(), want, rtol=2e-2, atol=2e-2)
+                    assert torch.all(outs[r][n:] == 0)
+                    assert torch.equal(ys[r], outs[r][:n])
+                assert all(torch.equal(outs[0], o) for o in outs)
+        assert comm.stats()["ll"] == before + calls
+        # one-phase and two-phase operations alternate on the same slots
+        for n in (8, 5000, 12, 90_000):
+            xs = [rand(n, torch.float32, n + r) for r in range(p)]
+            comm.allreduce(xs)
+            torch.cuda.synchronize()
+            assert all(torch.equal(xs[0], x) for x in xs)
+    finally:
+        comm.close()
+        al.set_tuning("ll_max_bytes", old1)
+        al.set_tuning("ar_ll2_max_bytes", old2)
+
+
 @pytest.mark.parametrize("p", [2, 4, 8])
 def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     comm = al.DeviceComm(emulate=p)

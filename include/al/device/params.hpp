@@ -127,12 +127,12 @@ constexpr size_t kLLPayloadBytes = 1048576;
 constexpr size_t kLLSlotBytes = 2 * kLLPayloadBytes;
 constexpr size_t kLLAreaBytes = 2 * (size_t)kMaxRanks * kLLSlotBytes;
 /**
- * Point-to-point messages of up to kP2PLLPayloadBytes travel as the same kind of packets: a ring of packet
- * slots per ordered pair of ranks, [source][piece number % mbox_slots], placed behind the collectives'
- * packet area (at ll[r] + kLLAreaBytes).  The packets' epoch is the pair's piece number + 1.
+ * Small point-to-point messages travel as the same kind of packets: a ring of packet slots per ordered pair
+ * of ranks, [source][piece number % mbox_slots] of Workspace::p2p_ll_slot_bytes each (twice the largest
+ * payload, fixed when the communicator is created), placed behind the collectives' packet area (at
+ * ll[r] + kLLAreaBytes).  The packets' epoch is the pair's piece number + 1.
  */
-constexpr size_t kP2PLLPayloadBytes = 262144;
-constexpr size_t kP2PLLSlotBytes = 2 * kP2PLLPayloadBytes;
+constexpr size_t kP2PLLMaxPayloadBytes = size_t{8} << 20;  ///< upper bound of the tunable payload limit
 
 /** Workspace of one communicator as seen from the launching process. */
 struct Workspace {
@@ -140,13 +140,14 @@ struct Workspace {
   uint64_t* flags[kMaxRanks];    ///< flag area of every rank
   char* mbox[kMaxRanks];         ///< p2p mailbox area of every rank: [src][2 slots]
   char* ll[kMaxRanks];           ///< low-latency packet area of every rank: [parity][src][kLLSlotBytes], then the
-                                 ///< point-to-point packet slots [src][mbox_slots][kP2PLLSlotBytes]
+                                 ///< point-to-point packet slots [src][mbox_slots][p2p_ll_slot_bytes]
   char* mc_stage;                ///< NVLink-multicast alias of the staging area, or nullptr
   DeviceStatus* status;          ///< pinned host record (device-visible address)
   uint64_t* stamps;              ///< nullptr, or 4 words of this GPU's memory that the small-message kernels fill with
                                  ///< %globaltimer at entry / data sent / data seen / exit (latency breakdowns)
   size_t half_bytes;             ///< size of one staging half
   size_t mbox_slot_bytes;        ///< size of one mailbox slot
+  size_t p2p_ll_slot_bytes;      ///< size of one point-to-point packet slot (0: no packet slots)
   int mbox_slots;                ///< slots per (source, destination) ring
   int p;                         ///< communicator size
 };
@@ -278,7 +279,7 @@ struct P2PParams {
   uint64_t rdesc[kMaxItems];     ///< receives: descriptor of the receive buffer when it is registered, else 0
   const WindowTable* windows;    ///< device memory of the launching process
   size_t rendezvous_bytes;       ///< messages of at least this size wait for the receiver and go straight into a registered buffer
-  size_t ll_bytes;               ///< messages of at most this size (> 0) travel as packets (at most kP2PLLPayloadBytes)
+  size_t ll_bytes;               ///< messages of at most this size (> 0) travel as packets (at most half a packet slot)
   uint64_t launch;               ///< number of this launch on the communicator (tags the local "posted" words)
   int ctas_per_item;
   int nitems;

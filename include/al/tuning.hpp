@@ -58,12 +58,14 @@ struct Tuning {
   size_t dev_stage_bytes = size_t{64} << 20;   ///< AL_DEV_STAGE_BYTES: one staging half per rank per communicator
   size_t dev_mailbox_bytes = size_t{8} << 20;  ///< AL_DEV_MAILBOX_BYTES: size of one p2p mailbox slot (larger pieces amortise the per-piece flag round: 4 MiB moved 315 GB/s, 16 MiB 536 GB/s between two B200)
   int dev_mailbox_slots = 2;                   ///< AL_DEV_MAILBOX_SLOTS: slots of the ring every ordered pair of ranks owns (pieces in flight per transfer)
-  size_t p2p_ll_max_bytes = size_t{256} << 10;     ///< AL_P2P_LL_MAX: point-to-point messages up to this size travel as low-latency packets (data and piece number in one 16-byte store; hard limit 256 KiB; 0 = never)
+  size_t p2p_ll_max_bytes = size_t{2} << 20;       ///< AL_P2P_LL_MAX: point-to-point messages up to this size travel as low-latency packets (data and piece number in one 16-byte store).  A communicator sizes its packet slots (ranks x ring depth x twice this) when it is created; lowering the value later takes effect at once, raising it applies to new communicators.  At most 8 MiB; 0 = never
   size_t p2p_rendezvous_bytes = size_t{1} << 20;  ///< AL_P2P_RENDEZVOUS: from this size on a send first waits for the receiver and, if the receive buffer is registered, stores straight into it (0 = never)
   double dev_wait_timeout_ms = 20000.0;        ///< AL_DEV_WAIT_TIMEOUT_MS: bound of every device-side flag wait
   bool dev_enable_nvls = true;                 ///< AL_DEV_NVLS: bind staging to an NVLink multicast object when supported
   int max_ctas = 128;                          ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
+  int max_ctas_pipelined = 128;                ///< AL_MAX_CTAS_PIPELINED: grid of the pipelined reduce_scatter / allgather / alltoall (half publishes, half consumes; at most one CTA per SM)
   int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
+  size_t nvls_chunk_bytes = size_t{8} << 20;   ///< AL_NVLS_CHUNK_BYTES: smallest chunk of the pipelined staged NVLS allreduce (a chunk is 1/16 of the message, at least this, at most a staging half)
   int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
   int p2p_max_ctas = 64;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)

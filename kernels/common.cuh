@@ -140,7 +140,7 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* slot, uint64_t epoch, 
  */
 __device__ __forceinline__ void arrive_and_post_ctr(const Workspace& ws, int rank, size_t off, unsigned* ctr,
                                                     unsigned group, uint64_t epoch, bool with_meta, int meta_par,
-                                                    uint64_t meta_value, uint64_t meta_proto = 0) {
+                                                    uint64_t meta_value, uint64_t meta_proto = 0, int word = 0) {
   __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -160,7 +160,7 @@ __device__ __forceinline__ void arrive_and_post_ctr(const Workspace& ws, int ran
       st_relaxed_sys(m + kMetaChunks, meta_value);
       if (meta_proto) st_relaxed_sys(m + kMetaProto, meta_proto);
     }
-    st_release_sys(flag_slot(ws.flags[dst], off, rank), epoch);
+    st_release_sys(flag_slot(ws.flags[dst], off, rank) + word, epoch);
   }
 }
 
@@ -178,21 +178,21 @@ __device__ __forceinline__ void arrive_and_post(const Workspace& ws, int rank, s
  */
 __device__ __forceinline__ void arrive_and_post_ring(const Workspace& ws, int rank, size_t off, int group_id, uint64_t round,
                                                      int depth, unsigned group, uint64_t epoch, bool with_meta, int meta_par,
-                                                     uint64_t meta_value, uint64_t meta_proto = 0) {
+                                                     uint64_t meta_value, uint64_t meta_proto = 0, int word = 0) {
   unsigned* ctr = (unsigned*)(ws.flags[rank] + FlagLayout::off_ring_arrive + (size_t)group_id * kRingDepth + (size_t)(round % (uint64_t)depth));
-  arrive_and_post_ctr(ws, rank, off, ctr, group, epoch, with_meta, meta_par, meta_value, meta_proto);
+  arrive_and_post_ctr(ws, rank, off, ctr, group, epoch, with_meta, meta_par, meta_value, meta_proto, word);
 }
 
 /** Every CTA waits until all ranks posted `epoch` in this rank's array `off`.
  *  Returns false (block-uniform) after a time-out, which has been reported. */
 __device__ __forceinline__ bool wait_all(const Workspace& ws, int rank, size_t off, uint32_t where,
-                                         uint64_t epoch, uint64_t timeout_ns) {
+                                         uint64_t epoch, uint64_t timeout_ns, int word = 0) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if (threadIdx.x < ws.p) {
     uint64_t seen = 0;
-    if (!wait_flag(flag_slot(ws.flags[rank], off, threadIdx.x), epoch, timeout_ns, &seen)) {
+    if (!wait_flag(flag_slot(ws.flags[rank], off, threadIdx.x) + word, epoch, timeout_ns, &seen)) {
       report_timeout(ws, rank, threadIdx.x, where, epoch, seen);
       s_ok = 0;
     }
@@ -253,6 +253,7 @@ __device__ __forceinline__ bool protocols_agree(const Workspace& ws, int rank, u
     const uint64_t last = make_epoch(seq, 0xFFFFFE);
     st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_A, rank), last);
     st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_B, rank), last);
+    st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_B, rank) + 1, last);  // odd chunks of the pipelined NVLS allreduce
     st_release_sys(flag_slot(ws.flags[threadIdx.x], FlagLayout::off_C, rank), last);
   }
   __syncthreads();

@@ -170,21 +170,28 @@ __global__ void __launch_bounds__(512) nvls_allreduce_pipelined_kernel(const __g
       arrive_and_post_ring(ws, rank, FlagLayout::off_A, 0, c, D, n_in, make_epoch(P.seq, c + 1), c == 0, (int)(P.seq & 1), G, my_proto);
     }
   } else if (b < n_in + n_red) {
-    for (uint64_t c = 0; c < G; ++c) {
+    // Two sub-groups take the even and the odd chunks: while one of them waits for its stores to be
+    // acknowledged and posts its flags, the other one keeps the links busy.  Each parity has its own B word
+    // (word 0 / word 1 of the flag's sector), so that every word only ever grows.
+    const unsigned rb = b - n_in;
+    const unsigned nsub = n_red >= 8 && D >= 4 ? 2 : 1;
+    const unsigned sub = rb % nsub, part = rb / nsub;
+    const unsigned ns = n_red / nsub + (sub < n_red % nsub ? 1 : 0);
+    for (uint64_t c = sub; c < G; c += nsub) {
       if (!wait_all(ws, rank, FlagLayout::off_A, 0, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
-      if (c == 0 && !protocols_agree(ws, rank, P.seq, my_proto)) return;
+      if (c == sub && !protocols_agree(ws, rank, P.seq, my_proto)) return;
       char* mc = ws.mc_stage + (size_t)(c % D) * chunk_b;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       const size_t nvec = (len * sizeof(T) + 15) >> 4;
       size_t s_lo, s_hi;
       split_range(nvec, (unsigned)rank, (unsigned)p, 1, s_lo, s_hi);
-      reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale, b - n_in, n_red);
+      reduce_vectors<T, OP>(mc, mc, s_lo, s_hi, scale, part, ns);
       __threadfence_system();
-      arrive_and_post_ring(ws, rank, FlagLayout::off_B, 1, c, D, n_red, make_epoch(P.seq, c + 1), false, 0, 0);
+      arrive_and_post_ring(ws, rank, FlagLayout::off_B, 1, c, D, ns, make_epoch(P.seq, c + 1), false, 0, 0, 0, (int)(c & 1));
     }
   } else {
     for (uint64_t c = 0; c < G; ++c) {
-      if (!wait_all(ws, rank, FlagLayout::off_B, 1, make_epoch(P.seq, c + 1), P.timeout_ns)) return;
+      if (!wait_all(ws, rank, FlagLayout::off_B, 1, make_epoch(P.seq, c + 1), P.timeout_ns, (int)(c & 1))) return;
       char* mystage = ws.stage[rank] + (size_t)(c % D) * chunk_b;
       const size_t base = c * chunk_e, len = clamp_len(P.count, base, chunk_e);
       size_t lo, hi;

@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(512) p2p_kernel(const __grid_constant__ P2PPar
     const char* src = (const char*)P.sbuf[item];
     if (packets) {
       if (base >= S && !cta_wait_word(acked, base - S + 1, P.timeout_ns, ws, me, peer, 3)) return;
-      char* dst = ws.ll[peer] + kLLAreaBytes + ((size_t)me * S + (base % S)) * kP2PLLSlotBytes;
+      char* dst = ws.ll[peer] + kLLAreaBytes + ((size_t)me * S + (base % S)) * ws.p2p_ll_slot_bytes;
       for (size_t g = ptid; g < pgroups; g += pthreads)
         send_group(dst, g, load_group((const uint8_t*)src, g * 16, bytes), pflag);
       return;
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(512) p2p_kernel(const __grid_constant__ P2PPar
     uint64_t* acked_remote = flag_slot(ws.flags[peer], FlagLayout::off_p2p_acked, me);
     char* dstbuf = (char*)P.rbuf[item];
     if (packets) {
-      const char* slot_in = ws.ll[me] + kLLAreaBytes + ((size_t)peer * S + (base % S)) * kP2PLLSlotBytes;
+      const char* slot_in = ws.ll[me] + kLLAreaBytes + ((size_t)peer * S + (base % S)) * ws.p2p_ll_slot_bytes;
       int bad = 0;
       for (size_t g = ptid; g < pgroups && !bad; g += pthreads) {
         uint4 v;

@@ -99,9 +99,9 @@ struct DeviceCommunicator::Impl {
     if (status_host) AL_WARN_CUDA(cudaFreeHost(status_host));
   }
 
-  static size_t block_bytes(int p, size_t half, size_t slot, int slots) {
+  static size_t block_bytes(int p, size_t half, size_t slot, int slots, size_t ll_slot) {
     return FlagLayout::bytes + 2 * half + (size_t)p * (size_t)slots * slot + kLLAreaBytes +
-           (size_t)p * (size_t)slots * kP2PLLSlotBytes;
+           (size_t)p * (size_t)slots * ll_slot;
   }
 
   int free_window() const {
@@ -150,6 +150,8 @@ namespace {
 size_t half_bytes_cfg() { return tuning().dev_stage_bytes / 4096 * 4096; }
 size_t slot_bytes_cfg() { return std::max<size_t>(4096, tuning().dev_mailbox_bytes / 4096 * 4096); }
 int slots_cfg() { return std::max(2, std::min(16, tuning().dev_mailbox_slots)); }
+/** Packet slot of the point-to-point path: twice the largest payload (every 8 bytes carry 4 of payload). */
+size_t p2p_ll_slot_cfg() { return 2 * round_up(std::min(tuning().p2p_ll_max_bytes, kP2PLLMaxPayloadBytes), (size_t)4096); }
 
 void require_device() {
   if (!cuda::device_usable()) throw_al_exception("the device backend needs a CUDA device, none is usable in this process");
@@ -176,10 +178,12 @@ DeviceCommunicator::DeviceCommunicator(const Group& group, cudaStream_t stream)
   }
   const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
   const int slots = slots_cfg();
-  auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot, slots), true);
+  const size_t ll_slot = p2p_ll_slot_cfg();
+  auto block = SymmBlock::create(group, Impl::block_bytes(group.size(), half, slot, slots, ll_slot), true);
   impl_->ws.half_bytes = half;
   impl_->ws.mbox_slot_bytes = slot;
   impl_->ws.mbox_slots = slots;
+  impl_->ws.p2p_ll_slot_bytes = ll_slot;
   impl_->setup(std::move(block), group.size(), group.rank(), 1);
 }
 
@@ -191,10 +195,12 @@ DeviceCommunicator DeviceCommunicator::emulated(int p, cudaStream_t stream) {
   auto impl = std::make_shared<Impl>();
   const size_t half = half_bytes_cfg(), slot = slot_bytes_cfg();
   const int slots = slots_cfg();
-  auto block = SymmBlock::create_emulated(p, Impl::block_bytes(p, half, slot, slots));
+  const size_t ll_slot = p2p_ll_slot_cfg();
+  auto block = SymmBlock::create_emulated(p, Impl::block_bytes(p, half, slot, slots, ll_slot));
   impl->ws.half_bytes = half;
   impl->ws.mbox_slot_bytes = slot;
   impl->ws.mbox_slots = slots;
+  impl->ws.p2p_ll_slot_bytes = ll_slot;
   impl->emulated = true;
   impl->setup(std::move(block), p, 0, p);
   return DeviceCommunicator(std::move(impl), Group(), stream);
@@ -610,7 +616,8 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   if (I.nlocal > 1) cap = std::min(cap, std::max(1, I.sm_count / I.nlocal));  // cooperative launch must be co-resident
   ctas = std::max(1, std::min(ctas, cap));
   if (P.pipelined) {
-    ctas = std::max(2, std::min(cap, 128));   // the whole budget: half publishes, half consumes
+    // the whole budget: half publishes, half consumes; one CTA per SM at most (they wait for each other)
+    ctas = std::max(2, std::min(tn.max_ctas_pipelined, I.sm_count - 4));
     if (I.nlocal > 1) ctas = std::max(2, std::min(ctas, I.sm_count / I.nlocal));
   }
   if (max_work_bytes <= 4096) threads = std::min(threads, 256);
@@ -630,7 +637,7 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
     if (!zero_copy && bytes >= X.nvls_pipeline_min_bytes) {
       // pipelined flavour: chunks of 1/16 of the message (at least 8 MiB, at most a staging half) in a ring of
       // slots laid over both halves; smaller chunks are dominated by the per-chunk handshakes
-      size_t chunk_b = std::max<size_t>(bytes / 16, size_t{8} << 20);
+      size_t chunk_b = std::max<size_t>(bytes / 16, std::max<size_t>(tn.nvls_chunk_bytes, 65536));
       chunk_b = std::min(chunk_b / 4096 * 4096, half);
       N.chunk_elems = chunk_b / esz;
       N.chunks = ceil_div(P.count, N.chunk_elems);
@@ -804,7 +811,7 @@ void DeviceCommunicator::p2p(const std::vector<P2PDesc>& items_in, cudaStream_t 
     P.timeout_ns = I.timeout_ns;
     P.windows = I.table_dev;
     P.rendezvous_bytes = tuning().p2p_rendezvous_bytes ? tuning().p2p_rendezvous_bytes : ~size_t{0};
-    P.ll_bytes = std::min(tuning().p2p_ll_max_bytes, std::min(kP2PLLPayloadBytes, P.rendezvous_bytes - 1));
+    P.ll_bytes = std::min(tuning().p2p_ll_max_bytes, I.ws.p2p_ll_slot_bytes / 2);
     P.launch = ++I.p2p_launches;
     size_t biggest_direct = 0;
     std::vector<uint64_t> used;  // keys taken in this launch

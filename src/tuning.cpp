@@ -42,6 +42,8 @@ void Tuning::load_from_env() {
   bulk_pub_ctas = (int)env_long("AL_DEV_BULK_PUB_CTAS", bulk_pub_ctas);
   bulk_con_ctas = (int)env_long("AL_DEV_BULK_CON_CTAS", bulk_con_ctas);
   ll_max_ctas = (int)env_long("AL_LL_CTAS", ll_max_ctas);
+  max_ctas_pipelined = (int)env_long("AL_MAX_CTAS_PIPELINED", max_ctas_pipelined);
+  nvls_chunk_bytes = (size_t)env_long("AL_NVLS_CHUNK_BYTES", (long)nvls_chunk_bytes);
   dev_mailbox_slots = (int)env_long("AL_DEV_MAILBOX_SLOTS", dev_mailbox_slots);
   p2p_rendezvous_bytes = (size_t)env_long("AL_P2P_RENDEZVOUS", (long)p2p_rendezvous_bytes);
   p2p_ll_max_bytes = (size_t)env_long("AL_P2P_LL_MAX", (long)p2p_ll_max_bytes);
@@ -132,6 +134,8 @@ std::string Tuning::describe() const {
      << "bulk_pub_ctas = " << bulk_pub_ctas << "\n"
      << "bulk_con_ctas = " << bulk_con_ctas << "\n"
      << "ll_max_ctas = " << ll_max_ctas << "\n"
+     << "max_ctas_pipelined = " << max_ctas_pipelined << "\n"
+     << "nvls_chunk_bytes = " << nvls_chunk_bytes << "\n"
      << "dev_mailbox_slots = " << dev_mailbox_slots << "\n"
      << "p2p_rendezvous_bytes = " << p2p_rendezvous_bytes << "\n"
      << "p2p_ll_max_bytes = " << p2p_ll_max_bytes << "\n"

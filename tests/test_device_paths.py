@@ -160,7 +160,7 @@ def test_ll_allgather_alltoall_with_scale_and_explicit_paths(al, p):
     torch.testing.assert_close(xs[0], st.mean(0))
     torch.testing.assert_close(ys[p - 1], st.sum(0) * 0.25)
     # a message that does not fit is refused when the path is forced, and staged when it is not
-    big = [rand(270000, torch.float32, 1) for _ in range(p)]
+    big = [rand(1_200_000, torch.float32, 1) for _ in range(p)]   # beyond one slot, and beyond p half-slots (two-phase form)
     with pytest.raises(al.AlError):
         comm.allreduce(big, algo="ll")
     before = comm.stats()["ll"]
@@ -415,7 +415,7 @@ def test_p2p_small_messages_travel_as_packets(al, p):
     row than the ring has slots, mixed with mailbox-sized messages between the same pair of ranks."""
     comm = al.DeviceComm(emulate=p)
     comm.set_timeout_ms(3000)
-    seq = [1, 7, 16, 100, 4099, 300_000, 65_539, 262_144, 5, 262_145, 33]     # bytes; 300 000 and 262 145 go through the mailbox
+    seq = [1, 7, 16, 100, 4099, 3_000_000, 65_539, 2_097_152, 5, 2_097_153, 33]     # bytes; 3 000 000 and 2 097 153 go through the mailbox
     for it, nbytes in enumerate(seq):
         src = [torch.randint(0, 256, (nbytes + 3,), dtype=torch.uint8, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7 * it + r)) for r in range(p)]
         dst = [torch.full((nbytes + 5,), 0xEE, dtype=torch.uint8, device="cuda") for _ in range(p)]

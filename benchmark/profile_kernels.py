@@ -33,6 +33,9 @@ def main():
         pass
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     comm = None
+    if a.case != "p2p":   # keep the emulated communicators' workspaces small: these cases do not use the mailboxes
+        al.set_tuning("dev_mailbox_bytes", 1 << 20)
+        al.set_tuning("p2p_ll_max_bytes", 65536)
     if a.case == "sgd":
         n = 64 << 20
         p, m, g = (torch.randn(n, device="cuda") for _ in range(3))
@@ -101,8 +104,9 @@ def main():
         nbytes = pr * n * 4 * 2                     # rendezvous into registered buffers: read once, write once
     elif a.case == "rs_pipelined":
         pr = 8
+        al.set_tuning("pipeline_min_bytes", 8 << 20)
         comm = al.DeviceComm(emulate=pr)
-        n = 8 << 20                                 # 32 MiB per rank slice, 256 MiB per rank: publisher / consumer CTAs
+        n = 4 << 20                                 # 16 MiB per rank slice, 128 MiB per rank: publisher / consumer CTAs
         full = [torch.randn(n * pr, device="cuda") for _ in range(pr)]
         part = [torch.empty(n, device="cuda") for _ in range(pr)]
         fn = lambda: comm.reduce_scatter(full, part)

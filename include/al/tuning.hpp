@@ -65,7 +65,7 @@ struct Tuning {
   int max_ctas = 128;                          ///< AL_MAX_CTAS_PER_OP: CTA budget of a bandwidth kernel
   int max_ctas_pipelined = 128;                ///< AL_MAX_CTAS_PIPELINED: grid of the pipelined reduce_scatter / allgather / alltoall (half publishes, half consumes; at most one CTA per SM)
   int max_ctas_nvls = 128;                     ///< AL_MAX_CTAS_NVLS: staged NVLS allreduce (its copies need many CTAs)
-  size_t nvls_chunk_bytes = size_t{8} << 20;   ///< AL_NVLS_CHUNK_BYTES: smallest chunk of the pipelined staged NVLS allreduce (a chunk is 1/16 of the message, at least this, at most a staging half)
+  size_t nvls_chunk_bytes = size_t{16} << 20;  ///< AL_NVLS_CHUNK_BYTES: smallest chunk of the pipelined staged NVLS allreduce (a chunk is 1/16 of the message, at least this, at most a staging half)
   int max_ctas_zero_copy = 32;                 ///< AL_MAX_CTAS_ZERO_COPY: NVLS allreduce on symmetric buffers (no copies)
   int threads_per_cta = 512;                   ///< AL_THREADS_PER_CTA
   int p2p_max_ctas = 64;                       ///< AL_DEV_P2P_CTAS: most CTAs one send or receive of a point-to-point launch gets (one per 64 KiB of a mailbox piece)
@@ -76,14 +76,14 @@ struct Tuning {
   Crossovers cross[3] = {
       // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min  two-phase packets max  rs nvls min
       {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, 0, ~size_t{0}},                      // 2 ranks
-      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},   // 3-4 ranks
-      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},    // 5-8 ranks
+      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},    // 3-4 ranks
+      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},     // 5-8 ranks
   };
   /** Row of the table for a communicator of `p` ranks. */
   const Crossovers& crossovers(int p) const { return cross[p <= 2 ? 0 : (p <= 4 ? 1 : 2)]; }
   bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
-  int window_ctas = 64;                        ///< AL_WINDOW_CTAS: CTA budget of a window kernel
-  int window_multimem_ag_ranks = 4;            ///< AL_WINDOW_MULTIMEM_AG_RANKS: allgather uses multimem.st from this many ranks on (a multicast store returns to its sender too, which costs 1/(p-1) extra ingress)
+  int window_ctas = 128;                       ///< AL_WINDOW_CTAS: CTA budget of a window kernel
+  int window_multimem_ag_ranks = 8;           ///< AL_WINDOW_MULTIMEM_AG_RANKS: allgather uses multimem.st from this many ranks on (a multicast store returns to its sender too, which costs 1/(p-1) extra ingress)
   int window_rs_min_ranks = 4;                 ///< AL_WINDOW_RS_MIN_RANKS: automatic reduce_scatter takes the window path (switch reduction) from this many ranks on
   bool window_multimem = true;                 ///< AL_WINDOW_MULTIMEM: let window kernels use multimem.st / multimem.ld_reduce when all ranks pass the same offset of one multicast-bound window
   // ---- diagnostics ------------------------------------------------------------

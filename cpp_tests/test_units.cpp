@@ -444,6 +444,75 @@ static void test_arrival_counters() {
   CHECK(single_counter_failures > 0);  // the schedules really do exercise the hazard
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The ring-pipelined NVLS allreduce (kernels/nvls.cu): IN, RED and OUT groups of CTAs, chunks in a ring of D
+// staging slots, the RED group split into two sub-groups that take the even and the odd chunks and post
+// into a flag word per parity.  Model one rank (the ranks are symmetric): CTAs advance in random order,
+// each group counts arrivals in the counter of ring slot c % D.  Checked: every chunk's A, B and C flag is
+// posted exactly once and only after all CTAs of the responsible (sub-)group arrived for it; flag words
+// only ever grow; a slot is never written by IN before OUT has emptied it.
+// ---------------------------------------------------------------------------------------------------
+static void test_ring_pipeline_schedule() {
+  std::mt19937 rng(99);
+  for (int trial = 0; trial < 300; ++trial) {
+    const int D = 2 + (int)(rng() % 7);                  // 2..8 slots
+    const int G = 1 + (int)(rng() % 20);                 // chunks
+    const int n_in = 1 + (int)(rng() % 4), n_out = 1 + (int)(rng() % 4);
+    const int n_red = 2 + (int)(rng() % 10);
+    const int nsub = (n_red >= 8 && D >= 4) ? 2 : 1;
+    struct Cta { int group, sub, next; };               // group 0 IN, 1 RED, 2 OUT; next = chunk it arrives for next
+    std::vector<Cta> ctas;
+    for (int i = 0; i < n_in; ++i) ctas.push_back({0, 0, 0});
+    for (int i = 0; i < n_red; ++i) ctas.push_back({1, i % nsub, i % nsub});
+    for (int i = 0; i < n_out; ++i) ctas.push_back({2, 0, 0});
+    auto group_size = [&](const Cta& c) {
+      if (c.group == 0) return n_in;
+      if (c.group == 2) return n_out;
+      return n_red / nsub + (c.sub < n_red % nsub ? 1 : 0);
+    };
+    std::vector<int> A((size_t)G, 0), B((size_t)G, 0), C((size_t)G, 0), arrivals((size_t)(3 * G), 0);
+    unsigned ctr[3][8] = {};
+    long wordB[2] = {0, 0}, wordA = 0, wordC = 0;
+    bool ok = true;
+    size_t finished = 0;
+    for (const Cta& c : ctas) finished += c.next >= G;   // the odd sub-group has nothing to do when there is one chunk
+    while (finished < ctas.size() && ok) {
+      std::vector<size_t> ready;
+      for (size_t i = 0; i < ctas.size(); ++i) {
+        const Cta& c = ctas[i];
+        if (c.next >= G) continue;
+        bool can = true;
+        if (c.group == 0) can = c.next < D || C[(size_t)(c.next - D)];   // slot emptied by OUT
+        if (c.group == 1) can = A[(size_t)c.next] != 0;                   // chunk copied in
+        if (c.group == 2) can = B[(size_t)c.next] != 0;                   // chunk reduced
+        if (can) ready.push_back(i);
+      }
+      if (ready.empty()) { ok = false; break; }
+      Cta& c = ctas[ready[(rng() % 3) ? 0 : rng() % ready.size()]];
+      const int k = c.next;
+      if (c.group == 0 && k >= D && !C[(size_t)(k - D)]) ok = false;       // would overwrite a slot still in use
+      arrivals[(size_t)(c.group * G + k)]++;
+      unsigned& n = ctr[c.group][k % D];
+      const unsigned g = (unsigned)group_size(c);
+      const bool last = n == g - 1;
+      n = last ? 0 : n + 1;
+      if (last) {
+        if (arrivals[(size_t)(c.group * G + k)] != (int)g) ok = false;     // posted before everybody arrived
+        std::vector<int>& flag = c.group == 0 ? A : (c.group == 1 ? B : C);
+        if (flag[(size_t)k]) ok = false;                                    // posted twice
+        flag[(size_t)k] = 1;
+        long& word = c.group == 0 ? wordA : (c.group == 1 ? wordB[k & 1] : wordC);
+        if (word >= k + 1) ok = false;                                      // a flag word must only grow
+        word = k + 1;
+      }
+      c.next += c.group == 1 ? nsub : 1;
+      if (c.next >= G) ++finished;
+    }
+    for (int k = 0; k < G; ++k) ok = ok && A[(size_t)k] && B[(size_t)k] && C[(size_t)k];
+    CHECK(ok);
+  }
+}
+
 static void test_progress_thread_placement() {
   using Al::internal::choose_pe_core;
   using Al::internal::parse_cpulist;
@@ -465,6 +534,7 @@ int main() {
   test_meta();
   test_progress_thread_placement();
   test_arrival_counters();
+  test_ring_pipeline_schedule();
   test_spsc();
   test_mpsc();
   test_allocator();

@@ -33,6 +33,7 @@ struct Crossovers {
   size_t nvls_pipeline_min_bytes;  ///< AL_NVLS_PIPELINE_MIN: staged NVLS allreduce is software-pipelined from this size on
   size_t pipeline_min_bytes;       ///< AL_PIPELINE_MIN: per-rank slice from which staged reduce_scatter / allgather / alltoall split the grid into publishers and consumers
   size_t window_min_bytes;         ///< AL_WINDOW_MIN: total message size from which registered buffers take the window kernels (below: staging or packets, one flag round less)
+  size_t ar_ll_max_bytes;          ///< AL_AR_LL_MAX: allreduce travels as one-phase packets (every rank sends its whole vector to every rank) up to this size; at most ll_max_bytes
   size_t ar_ll2_max_bytes;         ///< AL_AR_LL2_MAX: allreduce up to this size (beyond ll_max_bytes) runs as packets in two phases (reduce-scatter, then allgather; more than two ranks; hard limit p x 512 KiB)
   size_t rs_nvls_min_bytes;        ///< AL_RS_NVLS_MIN: total message size from which reduce_scatter of private buffers reduces in the switch (staged NVLS; needs multicast and more than two ranks)
 };
@@ -74,16 +75,16 @@ struct Tuning {
   int bulk_con_ctas = 16;                      ///< AL_DEV_BULK_CON_CTAS: its consuming CTAs for allgather / alltoall (reduce_scatter reduces with SM loads and takes max_ctas/2)
   int ll_max_ctas = 64;                        ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
   Crossovers cross[3] = {
-      // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min  two-phase packets max  rs nvls min
-      {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, 0, ~size_t{0}},                      // 2 ranks
-      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},    // 3-4 ranks
-      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},     // 5-8 ranks
+      // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min  one-phase / two-phase packet allreduce max  rs nvls min
+      {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{1} << 20, 0, ~size_t{0}},                      // 2 ranks
+      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},  // 3-4 ranks
+      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{64} << 10, size_t{2} << 20, ~size_t{0}},    // 5-8 ranks
   };
   /** Row of the table for a communicator of `p` ranks. */
   const Crossovers& crossovers(int p) const { return cross[p <= 2 ? 0 : (p <= 4 ? 1 : 2)]; }
   bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
   int window_ctas = 128;                       ///< AL_WINDOW_CTAS: CTA budget of a window kernel
-  int window_multimem_ag_ranks = 8;           ///< AL_WINDOW_MULTIMEM_AG_RANKS: allgather uses multimem.st from this many ranks on (a multicast store returns to its sender too, which costs 1/(p-1) extra ingress)
+  int window_multimem_ag_ranks = 16;          ///< AL_WINDOW_MULTIMEM_AG_RANKS: allgather uses multimem.st from this many ranks on (a multicast store returns to its sender too, which costs 1/(p-1) extra ingress)
   int window_rs_min_ranks = 4;                 ///< AL_WINDOW_RS_MIN_RANKS: automatic reduce_scatter takes the window path (switch reduction) from this many ranks on
   bool window_multimem = true;                 ///< AL_WINDOW_MULTIMEM: let window kernels use multimem.st / multimem.ld_reduce when all ranks pass the same offset of one multicast-bound window
   // ---- diagnostics ------------------------------------------------------------

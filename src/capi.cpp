@@ -122,6 +122,7 @@ size_t Crossovers::*crossover_field(const std::string& full, int* row) {
   if (n == "window_min_bytes") return &Crossovers::window_min_bytes;
   if (n == "rs_nvls_min_bytes") return &Crossovers::rs_nvls_min_bytes;
   if (n == "ar_ll2_max_bytes") return &Crossovers::ar_ll2_max_bytes;
+  if (n == "ar_ll_max_bytes") return &Crossovers::ar_ll_max_bytes;
   return nullptr;
 }
 }  // namespace

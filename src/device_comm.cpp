@@ -337,7 +337,12 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
       throw_al_exception("the low-latency path was requested but the operation does not qualify (uniform allreduce / "
                          "reduce_scatter / allgather / alltoall of at most ", kLLPayloadBytes, " bytes per pair of ranks)");
     const Tuning& tn = tuning();
-    const bool one_phase = fits && (forced || (automatic && pair_bytes <= tn.crossovers(p).ll_max_bytes));
+    // One-phase packets cost an allreduce p-1 times the vector per rank: its limit is lower than that of the
+    // other three operations (whose pair_bytes is one slice) and shrinks with the number of ranks.
+    const size_t one_phase_max = d.kind == DevColl::allreduce
+                                     ? std::min(tn.crossovers(p).ll_max_bytes, tn.crossovers(p).ar_ll_max_bytes)
+                                     : tn.crossovers(p).ll_max_bytes;
+    const bool one_phase = fits && ((forced && !(fits2 && pair_bytes > one_phase_max)) || (automatic && pair_bytes <= one_phase_max));
     const bool two_phase = !one_phase && fits2 && (forced || (automatic && pair_bytes <= tn.crossovers(p).ar_ll2_max_bytes));
     if (one_phase || two_phase) {
       LLParams L;
@@ -549,8 +554,11 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
   size_t slot_e = cap_e;
   const bool ar_pipelined = d.kind == DevColl::allreduce && p == 2 && algo == AllreduceAlgo::one_shot &&
                             d.algo == AllreduceAlgo::automatic && bytes >= X.ar_pipeline_min_bytes;
+  // (Real ranks also pipeline as soon as a slice does not fit one staging slot: the alternative would be
+  // several chunks one after the other, each with its handshakes exposed.)
+  const bool slice_exceeds_slot = !I.emulated && P.count > cap_e;
   if (((d.kind == DevColl::reduce_scatter || d.kind == DevColl::allgather || d.kind == DevColl::alltoall) && !d.vector &&
-       p > 1 && !use_window && P.count * esz >= X.pipeline_min_bytes) || ar_pipelined) {
+       p > 1 && !use_window && (P.count * esz >= X.pipeline_min_bytes || slice_exceeds_slot)) || ar_pipelined) {
     size_t chunk_b = std::max<size_t>(P.count * esz / 8, size_t{4} << 20);
     chunk_b = std::min(chunk_b / 256 * 256, cap_e * esz);
     if (chunk_b >= 256 && chunk_b < P.count * esz) {

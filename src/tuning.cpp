@@ -54,7 +54,7 @@ void Tuning::load_from_env() {
         {"AL_AR_NVLS_MIN", &Crossovers::ar_nvls_min_bytes}, {"AL_AR_PIPELINE_MIN", &Crossovers::ar_pipeline_min_bytes},
         {"AL_NVLS_PIPELINE_MIN", &Crossovers::nvls_pipeline_min_bytes}, {"AL_PIPELINE_MIN", &Crossovers::pipeline_min_bytes},
         {"AL_WINDOW_MIN", &Crossovers::window_min_bytes}, {"AL_RS_NVLS_MIN", &Crossovers::rs_nvls_min_bytes},
-        {"AL_AR_LL2_MAX", &Crossovers::ar_ll2_max_bytes}};
+        {"AL_AR_LL2_MAX", &Crossovers::ar_ll2_max_bytes}, {"AL_AR_LL_MAX", &Crossovers::ar_ll_max_bytes}};
     static const char* suffix[3] = {"_P2", "_P4", "_P8"};
     for (const Entry& e : entries)
       for (int row = 0; row < 3; ++row) {
@@ -152,6 +152,7 @@ std::string Tuning::describe() const {
      << "  nvls_pipeline_min_bytes " << cross[0].nvls_pipeline_min_bytes << "  " << cross[1].nvls_pipeline_min_bytes << "  " << cross[2].nvls_pipeline_min_bytes << "\n"
      << "  pipeline_min_bytes      " << cross[0].pipeline_min_bytes << "  " << cross[1].pipeline_min_bytes << "  " << cross[2].pipeline_min_bytes << "\n"
      << "  window_min_bytes        " << cross[0].window_min_bytes << "  " << cross[1].window_min_bytes << "  " << cross[2].window_min_bytes << "\n"
+     << "  ar_ll_max_bytes         " << cross[0].ar_ll_max_bytes << "  " << cross[1].ar_ll_max_bytes << "  " << cross[2].ar_ll_max_bytes << "\n"
      << "  ar_ll2_max_bytes        " << cross[0].ar_ll2_max_bytes << "  " << cross[1].ar_ll2_max_bytes << "  " << cross[2].ar_ll2_max_bytes << "\n"
      << "  rs_nvls_min_bytes       " << cross[0].rs_nvls_min_bytes << "  " << cross[1].rs_nvls_min_bytes << "  " << cross[2].rs_nvls_min_bytes << "\n"
      << "trace = " << trace << "\n"

@@ -48,6 +48,7 @@ TOOLS = {
     "benchmark_waits": ["benchmark/benchmark_waits.cpp"],
     "benchmark_events": ["benchmark/benchmark_events.cpp"],
     "stress_progress": ["benchmark/stress_progress.cpp"],
+    "barrier_skew": ["benchmark/barrier_skew.cpp"],
     "hello_world": ["examples/hello_world.cpp"],
     "allreduce": ["examples/allreduce.cpp"],
     "pingpong": ["examples/pingpong.cpp"],

@@ -23,12 +23,15 @@
 #include <fcntl.h>
 #include <poll.h>
 #include <sched.h>
+#include <sys/mman.h>
 #include <sys/socket.h>
+#include <sys/stat.h>
 #include <sys/un.h>
 #include <time.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -738,7 +741,7 @@ void set_nonblocking(int fd) {
   setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
 }
 
-void connect_world() {
+std::string connect_world() {
   g_rank = env_int("MPISHIM_RANK", "RANK", 0);
   g_size = env_int("MPISHIM_SIZE", "WORLD_SIZE", 1);
   if (g_size < 1 || g_rank < 0 || g_rank >= g_size) die("bad RANK / WORLD_SIZE");
@@ -754,9 +757,9 @@ void connect_world() {
   g_comms[2].me = 0;
   g_comms[2].ranks = {g_rank};
   g_groups[1].used = true;  // MPI_GROUP_EMPTY
-  if (g_size == 1) return;
-
   std::string job;
+  if (g_size == 1) return job;
+
   if (const char* j = getenv("MPISHIM_JOB")) job = j;
   else {
     const char* port = getenv("MASTER_PORT");
@@ -804,6 +807,71 @@ void connect_world() {
   close(lfd);
   for (int r = 0; r < g_size; ++r)
     if (r != g_rank) set_nonblocking(g_peers[(size_t)r].fd);
+  return job;
+}
+
+// ------------------------------------------------------------------------------------------
+// MPI_Barrier(MPI_COMM_WORLD) on shared memory
+// ------------------------------------------------------------------------------------------
+// Benchmarks line the ranks up with MPI_Barrier(MPI_COMM_WORLD) before every timed call.  A barrier
+// made of socket messages releases the ranks several microseconds apart, and that skew would be charged to
+// the library under test; a single-node MPI does this on shared memory.  So does this one: one cache
+// line in a POSIX shared-memory object, a counter and a generation number.  Other communicators, the
+// non-blocking form and failures to set the object up use the message schedule.
+struct ShmBarrier {
+  std::atomic<uint32_t> count;
+  std::atomic<uint32_t> generation;
+};
+ShmBarrier* g_shm_barrier = nullptr;
+
+void setup_shm_barrier(const std::string& job) {
+  if (g_size <= 1 || getenv("MPISHIM_NO_SHM")) return;
+  const std::string name = "/mpishim-" + job;
+  auto barrier_by_messages = [&] {
+    std::unique_lock<std::recursive_mutex> lk(g_mu);
+    const int id = sched_barrier(g_comms[1]);
+    finish_blocking(lk, id, "MPI_Init");
+  };
+  int fd = -1;
+  if (g_rank == 0) {
+    shm_unlink(name.c_str());
+    fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd >= 0 && ftruncate(fd, 4096) != 0) { close(fd); fd = -1; }
+  }
+  barrier_by_messages();  // the object exists (or rank 0 could not make it)
+  if (g_rank != 0) fd = shm_open(name.c_str(), O_RDWR, 0600);
+  void* mem = fd >= 0 ? mmap(nullptr, 4096, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0) : MAP_FAILED;
+  if (fd >= 0) close(fd);
+  // every rank has to have it, or nobody uses it
+  int mine = mem != MAP_FAILED ? 1 : 0, everyone = 0;
+  {
+    std::unique_lock<std::recursive_mutex> lk(g_mu);
+    const int id = sched_allreduce(g_comms[1], &mine, &everyone, 1, MPI_INT, MPI_MIN);
+    finish_blocking(lk, id, "MPI_Init");
+  }
+  if (g_rank == 0) shm_unlink(name.c_str());  // the mappings keep it alive; nothing is left behind
+  if (everyone) g_shm_barrier = (ShmBarrier*)mem;   // fresh pages of a new object are zero
+  else if (mem != MAP_FAILED) munmap(mem, 4096);
+}
+
+/** true: done; false: not available (use the message schedule). */
+bool shm_barrier_world() {
+  ShmBarrier* b = g_shm_barrier;
+  if (!b) return false;
+  const uint32_t gen = b->generation.load(std::memory_order_acquire);
+  if (b->count.fetch_add(1, std::memory_order_acq_rel) + 1 == (uint32_t)g_size) {
+    b->count.store(0, std::memory_order_relaxed);
+    b->generation.store(gen + 1, std::memory_order_release);
+    return true;
+  }
+  const double t0 = now_s();
+  for (unsigned spins = 0; b->generation.load(std::memory_order_acquire) == gen; ++spins) {
+    if (spins > 20000) {
+      sched_yield();
+      if ((spins & 1023) == 0 && now_s() - t0 > g_timeout_s) die("MPI_Barrier: a rank never arrived");
+    }
+  }
+  return true;
 }
 
 #define LOCK std::unique_lock<std::recursive_mutex> lk(g_mu)
@@ -818,8 +886,11 @@ extern "C" {
 int MPI_Init_thread(int*, char***, int, int* provided) {
   LOCK;
   if (!g_initialized) {
-    connect_world();
+    const std::string job = connect_world();
     g_initialized = true;
+    lk.unlock();
+    setup_shm_barrier(job);
+    lk.lock();
   }
   if (provided) *provided = MPI_THREAD_MULTIPLE;
   return MPI_SUCCESS;
@@ -1172,7 +1243,10 @@ static int do_alltoallv(const void* s, const int scounts[], const int sdispls[],
   COLL_RETURN(sched_alltoallv(c, s, sb, sd, r, rb, rd), "MPI_Alltoall(v)");
 }
 
-int MPI_Barrier(MPI_Comm comm) { return do_barrier(comm, nullptr); }
+int MPI_Barrier(MPI_Comm comm) {
+  if (comm == MPI_COMM_WORLD && shm_barrier_world()) return MPI_SUCCESS;
+  return do_barrier(comm, nullptr);
+}
 int MPI_Ibarrier(MPI_Comm comm, MPI_Request* req) { return do_barrier(comm, req); }
 int MPI_Bcast(void* buf, int count, MPI_Datatype dt, int root, MPI_Comm comm) { return do_bcast(buf, count, dt, root, comm, nullptr); }
 int MPI_Ibcast(void* buf, int count, MPI_Datatype dt, int root, MPI_Comm comm, MPI_Request* req) { return do_bcast(buf, count, dt, root, comm, req); }

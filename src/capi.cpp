@@ -380,8 +380,11 @@ int al_dev_latency_breakdown(void* comm, int kind, const void* send, void* recv,
     const void* sp[1] = {send};
     void* rp[1] = {recv};
     std::vector<double> col[6];
+    // The ranks start every call together: a barrier on shared memory (the control plane's socket exchange
+    // releases the ranks one after the other, and that skew would end up inside the timed interval).
+    HostCommunicator start_line(c.group());
     for (int i = 0; i < warmup + iters; ++i) {
-      c.group().barrier();
+      Barrier<HostBackend>(start_line);
       AL_CHECK_CUDA(cudaEventRecord(e0, s));
       const double h0 = get_time();
       if (al_dev_collective(comm, kind, 1, sp, rp, count, dtype, -1, -1, op, 0, 0, 0, nullptr, nullptr, nullptr, nullptr,
@@ -473,8 +476,10 @@ int al_dev_time_collective(void* comm, int kind, const void* send, void* recv, s
     AL_CHECK_CUDA(cudaEventCreate(&e1));
     const void* sp[1] = {send};
     void* rp[1] = {recv};
+    // host barrier on shared memory before every call, as in benchmark_ops (see al_dev_latency_breakdown)
+    HostCommunicator start_line(c.group());
     for (int i = 0; i < warmup + iters; ++i) {
-      c.group().barrier();
+      Barrier<HostBackend>(start_line);
       AL_CHECK_CUDA(cudaEventRecord(e0, s));
       if (al_dev_collective(comm, kind, 1, sp, rp, count, dtype, -1, -1, op, 0, 0, 0, nullptr, nullptr, nullptr, nullptr,
                             1.0, 0, 0, (void*)s, nullptr) != 0)

@@ -137,6 +137,35 @@ def test_info_and_tuning_from_python(built_lib):
         al.set_tuning("no_such_entry", 1)
 
 
+def test_crossover_table_per_rank_count(built_lib, bin_dir):
+    """The algorithm crossovers are a table with one row per communicator size: a plain name sets every row,
+    "name@p" the row of p ranks; environment variables follow the same scheme (AL_X, AL_X_P2 / _P4 / _P8)."""
+    import aluminum_b200 as al
+    names = ["ll_max_bytes", "ar_ll_max_bytes", "ar_ll2_max_bytes", "ar_oneshot_max_bytes", "ar_nvls_min_bytes",
+             "ar_pipeline_min_bytes", "nvls_pipeline_min_bytes", "pipeline_min_bytes", "window_min_bytes", "rs_nvls_min_bytes"]
+    info = al.info()
+    for n in names:
+        assert n in info, n
+        for p in (2, 4, 8):
+            assert al.get_tuning(f"{n}@{p}") >= 0
+    old = [al.get_tuning(f"ar_ll_max_bytes@{p}") for p in (2, 4, 8)]
+    assert old[0] >= old[1] >= old[2] > 0          # one-phase packets pay p-1 times the vector: the limit shrinks with p
+    al.set_tuning("ar_ll_max_bytes@4", 12345)
+    assert [al.get_tuning(f"ar_ll_max_bytes@{p}") for p in (2, 4, 8)] == [old[0], 12345, old[2]]
+    assert al.get_tuning("ar_ll_max_bytes@3") == 12345   # three ranks share the row of four
+    al.set_tuning("ar_ll_max_bytes", 777)
+    assert [al.get_tuning(f"ar_ll_max_bytes@{p}") for p in (2, 4, 8)] == [777, 777, 777]
+    for p, v in zip((2, 4, 8), old):
+        al.set_tuning(f"ar_ll_max_bytes@{p}", v)
+    for n in ("p2p_ll_max_bytes", "nvls_chunk_bytes", "max_ctas_pipelined", "window_ctas"):
+        assert al.get_tuning(n) > 0
+    r = run([bin_dir / "al_info"], env={"AL_AR_LL2_MAX": "4096", "AL_AR_LL2_MAX_P8": "8192", "AL_P2P_LL_MAX": "1024"})
+    assert r.returncode == 0, r.stderr
+    row = [l for l in r.stdout.splitlines() if "ar_ll2_max_bytes" in l][0].split()
+    assert row[1:] == ["4096", "4096", "8192"], row
+    assert "p2p_ll_max_bytes = 1024" in r.stdout
+
+
 def test_injected_missing_signal_times_out_and_recovers(bin_dir):
     env = {"AL_HOST_WAIT_TIMEOUT_S": "1", "AL_FAULT_RANK": "1", "AL_FAULT_OP": "2", "AL_FAULT_KIND": "1"}
     r = run([bin_dir / "alrun", "-n", "3", "--timeout", "120", sys.executable, W / "host_inject.py", "skip"], env=env)

@@ -12,7 +12,7 @@ This is how a cross-over point or an opt-in data path is judged on a given machi
     python benchmark/compare_settings.py --ranks 8 --nodes 2 --backend host --ops allreduce \\
         --setting two-level --setting flat:AL_HOST_TWO_LEVEL=0
 
-A setting is `name[:VAR=value[,VAR=value...]][:flag flag ...]`, e.g. `sym:AL_DEV_DIRECT=1:--symmetric`.
+A setting is `name[:VAR=value[,VAR=value...]][:flag flag ...]`, e.g. `win64:AL_WINDOW_CTAS=64:--symmetric`.
 The table is Markdown on stdout (and in --out when given).  Role: the tuning side of the
 reference's benchmark/run_benchmarks.py + plot_benchmarks.py "best implementation" heat-map
 (benchmark/plot_benchmarks.py:220-309), for one library under different settings.

@@ -5,6 +5,7 @@
 #include "Al.hpp"
 #include "al/cuda/cuda.hpp"
 #include "al/device/symmem.hpp"
+#include "al/progress.hpp"
 #include "al/tuning.hpp"
 
 int main() {
@@ -31,5 +32,15 @@ int main() {
     std::cout << "no CUDA device usable in this process\n";
   }
 #endif
+  // Where the progress thread of this process polls from (a core local to the GPU when the kernel tells which those are).
+  std::cout << "--- progress thread ---\n";
+  Al::Initialize();
+  {
+    Al::internal::ProgressEngine* pe = Al::internal::get_progress_engine();
+    pe->run();  // started on demand otherwise; run() returns once the thread has bound itself
+    std::cout << "bound to core " << pe->bound_core() << " (-1: not bound), cores reported local to the GPU: "
+              << pe->near_gpu_cores() << "\n";
+  }
+  Al::Finalize();
   return 0;
 }

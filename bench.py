@@ -376,10 +376,13 @@ def main():
     if world > 1 and arm.time_collective is not None and not a.no_collectives:
         del xd, yd
         torch.cuda.empty_cache()
-        bufs = CollBuffers(min(a.coll_max_bytes, max(COLL_SIZES)), 7 + rank)
-        torch.cuda.synchronize()
-        collectives = collectives_block(lambda k, s, w, i: arm.time_collective(bufs, k, s, w, i), world,
-                                        arm.max_over_ranks, a.coll_max_bytes)
+        try:  # the training figures above stand on their own: a failure here is reported, not fatal
+            bufs = CollBuffers(min(a.coll_max_bytes, max(COLL_SIZES)), 7 + rank)
+            torch.cuda.synchronize()
+            collectives = collectives_block(lambda k, s, w, i: arm.time_collective(bufs, k, s, w, i), world,
+                                            arm.max_over_ranks, a.coll_max_bytes)
+        except Exception as e:  # noqa: BLE001
+            collectives = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if a.timeline and a.impl == "ours" and world > 1:
         dp = arm.dp

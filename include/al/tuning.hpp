@@ -85,7 +85,8 @@ struct Tuning {
   bool window_enable = true;                   ///< AL_WINDOW: uniform reduce_scatter / allgather / alltoall / bcast on registered (or symm_alloc) buffers skip the staging area
   int window_ctas = 128;                       ///< AL_WINDOW_CTAS: CTA budget of a window kernel
   int window_multimem_ag_ranks = 16;          ///< AL_WINDOW_MULTIMEM_AG_RANKS: allgather uses multimem.st from this many ranks on (a multicast store returns to its sender too, which costs 1/(p-1) extra ingress)
-  int window_rs_min_ranks = 4;                 ///< AL_WINDOW_RS_MIN_RANKS: automatic reduce_scatter takes the window path (switch reduction) from this many ranks on
+  int window_rs_min_ranks = 5;                 ///< AL_WINDOW_RS_MIN_RANKS: automatic reduce_scatter takes the window path (switch reduction) from this many ranks on (4 ranks: the staged push measured 5-8 % faster)
+  size_t window_rs_min_bytes = size_t{32} << 20;  ///< AL_WINDOW_RS_MIN: ... and from this total size on (8 ranks: 16 MiB 51 us on the window path against 47 us staged, 64 MiB 121 against 128)
   bool window_multimem = true;                 ///< AL_WINDOW_MULTIMEM: let window kernels use multimem.st / multimem.ld_reduce when all ranks pass the same offset of one multicast-bound window
   // ---- diagnostics ------------------------------------------------------------
   bool trace = false;                          ///< AL_TRACE: record every API call

@@ -100,7 +100,7 @@ int al_info(char* buf, size_t buflen) {
   X(dev_stage_bytes) X(dev_mailbox_bytes) X(dev_wait_timeout_ms) X(dev_enable_nvls)   \
   X(max_ctas) X(max_ctas_nvls) X(max_ctas_zero_copy) X(threads_per_cta) X(debug_checks) X(debug_guard) X(stream_pool_size)    \
   X(disable_background_streams) X(host_serialize) X(host_two_level) X(host_two_level_max_bytes) X(fault_rank) X(fault_op) X(fault_kind) X(fault_delay_ms) X(fault_jitter_us) \
-  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(p2p_ll_max_bytes) X(nvls_chunk_bytes) X(max_ctas_pipelined) X(window_enable) X(window_ctas) X(window_multimem) X(window_multimem_ag_ranks) X(window_rs_min_ranks)
+  X(p2p_max_ctas) X(bulk_pipeline) X(bulk_pub_ctas) X(bulk_con_ctas) X(ll_max_ctas) X(dev_mailbox_slots) X(p2p_rendezvous_bytes) X(p2p_ll_max_bytes) X(nvls_chunk_bytes) X(max_ctas_pipelined) X(window_enable) X(window_ctas) X(window_multimem) X(window_multimem_ag_ranks) X(window_rs_min_ranks) X(window_rs_min_bytes)
 
 namespace {
 /** "ll_max_bytes" or "ll_max_bytes@4" -> member pointer and row (-1 = all rows); nullptr if not a crossover. */

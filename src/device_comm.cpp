@@ -481,7 +481,8 @@ void DeviceCommunicator::collective(const CollDesc& d, const std::vector<RankArg
             // their threads); left to itself the library takes the window path for reduce_scatter only where
             // the switch does the reduction (multicast-bound window) and there are enough ranks for that to pay.
             if (ok && d.path == CollPath::automatic)
-              ok = tn.window_multimem && I.table_host.mc[w] != nullptr && p >= tn.window_rs_min_ranks;
+              ok = tn.window_multimem && I.table_host.mc[w] != nullptr && p >= tn.window_rs_min_ranks &&
+                   total >= tn.window_rs_min_bytes;
             if (ok) Wp.send_desc[r] = make_desc(w, off);
             break;
           case DevColl::allgather: {

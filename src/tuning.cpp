@@ -68,6 +68,7 @@ void Tuning::load_from_env() {
   window_multimem = env_long("AL_WINDOW_MULTIMEM", window_multimem) != 0;
   window_multimem_ag_ranks = (int)env_long("AL_WINDOW_MULTIMEM_AG_RANKS", window_multimem_ag_ranks);
   window_rs_min_ranks = (int)env_long("AL_WINDOW_RS_MIN_RANKS", window_rs_min_ranks);
+  window_rs_min_bytes = (size_t)env_long("AL_WINDOW_RS_MIN", (long)window_rs_min_bytes);
   trace = env_long("AL_TRACE", trace) != 0;
 #ifdef AL_DEBUG_DEFAULT
   debug_checks = true;   // built with ALUMINUM_ENABLE_DEBUG: checks are on unless AL_DEBUG=0
@@ -144,6 +145,7 @@ std::string Tuning::describe() const {
      << "window_multimem = " << window_multimem << "\n"
      << "window_multimem_ag_ranks = " << window_multimem_ag_ranks << "\n"
      << "window_rs_min_ranks = " << window_rs_min_ranks << "\n"
+     << "window_rs_min_bytes = " << window_rs_min_bytes << "\n"
      << "crossovers (bytes)      2 ranks      3-4 ranks      5-8 ranks\n"
      << "  ll_max_bytes            " << cross[0].ll_max_bytes << "  " << cross[1].ll_max_bytes << "  " << cross[2].ll_max_bytes << "\n"
      << "  ar_oneshot_max_bytes    " << cross[0].ar_oneshot_max_bytes << "  " << cross[1].ar_oneshot_max_bytes << "  " << cross[2].ar_oneshot_max_bytes << "\n"

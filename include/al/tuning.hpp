@@ -76,9 +76,9 @@ struct Tuning {
   int ll_max_ctas = 64;                        ///< AL_LL_CTAS: most CTAs of a low-latency launch (256 threads, one 16-byte group each)
   Crossovers cross[3] = {
       // ll_max      one-shot max      nvls min  ar pipeline   nvls pipeline      rs/ag/a2a pipeline  window min  one-phase / two-phase packet allreduce max  rs nvls min
-      {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{256} << 10, size_t{1} << 20, 0, ~size_t{0}},                      // 2 ranks
-      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},  // 3-4 ranks
-      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{256} << 10, size_t{64} << 10, size_t{2} << 20, ~size_t{0}},    // 5-8 ranks
+      {size_t{1} << 20, size_t{2} << 20, 0, size_t{64} << 20, size_t{128} << 20, size_t{32} << 20, size_t{16} << 20, size_t{1} << 20, 0, ~size_t{0}},                       // 2 ranks
+      {size_t{256} << 10, size_t{256} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{16} << 20, size_t{256} << 10, size_t{2} << 20, ~size_t{0}},   // 3-4 ranks
+      {size_t{256} << 10, size_t{16} << 10, 0, size_t{64} << 20, size_t{64} << 20, size_t{32} << 20, size_t{16} << 20, size_t{64} << 10, size_t{2} << 20, ~size_t{0}},     // 5-8 ranks
   };
   /** Row of the table for a communicator of `p` ranks. */
   const Crossovers& crossovers(int p) const { return cross[p <= 2 ? 0 : (p <= 4 ? 1 : 2)]; }

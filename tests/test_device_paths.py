@@ -250,11 +250,14 @@ def test_window_allgather_alltoall_bcast(al, p, symmetric):
             for r in range(p):
                 assert torch.equal(recv[r], want)
         # automatic selection: large enough messages on registered buffers take the window path, small ones do not
+        old_min = al.get_tuning("window_min_bytes")
+        al.set_tuning("window_min_bytes", 256 << 10)      # the default (16 MiB) is beyond this test's sizes
         before = comm.stats()["window"]
         comm.allgather([rand(n, torch.float32, 1 + r) for r in range(p)], [o[:n * p] for o in outs])
         torch.cuda.synchronize()
         took = comm.stats()["window"] - before
-        assert took == (1 if n * p * 4 >= al.get_tuning("window_min_bytes") else 0)
+        al.set_tuning("window_min_bytes", old_min)
+        assert took == (1 if n * p * 4 >= (256 << 10) else 0)
         # a private receive buffer is refused on the forced path and staged on the automatic one
         priv = [torch.zeros(n * p, device="cuda") for _ in range(p)]
         with pytest.raises(al.AlError):

@@ -228,7 +228,8 @@ comm.barrier()
 torch.cuda.synchronize()
 
 # ---- 5. ranks that disagree about registration get a clear error, not a time-out ------------------------------
-n = 100_000
+n = 600_000                                      # 2.4 MB per pair of ranks: beyond the packet path on any number of ranks
+al.set_tuning("window_min_bytes", 256 << 10)   # left to itself the library keeps messages of this size on the staged path
 bad = al.DeviceComm()
 bad.set_timeout_ms(15000)
 sym = bad.symm_empty((n * p,), torch.float32)

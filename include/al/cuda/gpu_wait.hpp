@@ -25,9 +25,16 @@ class GPUWait {
   void wait(cudaStream_t stream);
   /** Release every stream waiting on this object (host atomic store). */
   void signal();
+  /**
+   * True once a wait of the spin-kernel fallback has given up (its time budget ran out before signal()): the
+   * stream has gone on without the host, so whatever it produced afterwards must not be trusted.  Always false
+   * where stream memory operations do the waiting (they have no time budget).
+   */
+  bool timed_out() const;
 
  private:
   int32_t* host_flag_ = nullptr;
+  int32_t* host_status_ = nullptr;  ///< pinned word the fallback kernel sets when it gives up
   CUdeviceptr dev_ptr_ = 0;
 };
 

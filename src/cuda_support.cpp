@@ -265,19 +265,28 @@ bool GPUStatusFlag::query() {
 GPUWait::GPUWait() {
   host_flag_ = sync_pool.get();
   __atomic_store_n(host_flag_, 0, __ATOMIC_SEQ_CST);
+  host_status_ = sync_pool.get();
+  __atomic_store_n(host_status_, 0, __ATOMIC_SEQ_CST);
   void* dp = nullptr;
   AL_CHECK_CUDA(cudaHostGetDevicePointer(&dp, host_flag_, 0));
   dev_ptr_ = (CUdeviceptr)dp;
 }
 
-GPUWait::~GPUWait() { sync_pool.release(host_flag_); }
+GPUWait::~GPUWait() {
+  sync_pool.release(host_flag_);
+  sync_pool.release(host_status_);
+}
+
+bool GPUWait::timed_out() const { return __atomic_load_n(host_status_, __ATOMIC_ACQUIRE) != 0; }
 
 void GPUWait::wait(cudaStream_t stream) {
   if (stream_memory_operations_supported()) {
     launch_wait_kernel(stream, 1, dev_ptr_);
   } else {
     const uint64_t budget = (uint64_t)(tuning().dev_wait_timeout_ms * 1e6);
-    launch_wait_kernel(stream, 1, (volatile int32_t*)dev_ptr_, budget, nullptr);
+    void* status_dev = nullptr;
+    AL_CHECK_CUDA(cudaHostGetDevicePointer(&status_dev, host_status_, 0));
+    launch_wait_kernel(stream, 1, (volatile int32_t*)dev_ptr_, budget, (int32_t*)status_dev);
   }
 }
 

@@ -67,7 +67,12 @@ class HTState final : public AlState {
         phase_ = 3;
         return PEAction::cont;
       default:
-        return end_flag.query() ? PEAction::complete : PEAction::cont;
+        if (!end_flag.query()) return PEAction::cont;
+        // Only the spin-kernel fallback of the stream's wait has a time budget; if it ran out, the stream copied
+        // the receive buffers back before the exchange had filled them.
+        if (wait.timed_out())
+          failure_->set("the stream stopped waiting for the host exchange (device wait time-out); the result is not valid");
+        return PEAction::complete;
     }
   }
 
